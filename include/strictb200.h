@@ -1,0 +1,213 @@
+/* strictb200 — C ABI of the B200 (sm_100a) LLM forward path behind the Strict CUDA surface.
+ *
+ * One shared library, `libstrictb200.so`, plain C linkage, plain pointers and sizes. It is
+ * what a `[DllImport("strictb200")]` class inside Strict.Compiler.Cuda binds instead of the
+ * ManagedCuda + NVRTC objects the reference uses. Every function returns a status code
+ * (0 = ok); no exception crosses the boundary; `strictb200_last_error()` gives the text of
+ * the calling thread's last failure. All kernels are compiled ahead of time for sm_100a;
+ * there is no CPU fallback: without a B200-class device `strictb200_create` fails.
+ *
+ * Threading: a context is bound to one device and one stream; calls on one context must be
+ * serialised by the caller; different contexts may be driven from different threads.
+ * Pointers named d_* are device pointers of that context's device, h_* are host pointers.
+ */
+#ifndef STRICTB200_H
+#define STRICTB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define STRICTB200_VERSION 100
+
+enum strictb200_status {
+  STRICTB200_OK = 0,
+  STRICTB200_ERR_INVALID_ARG = 1, /* null handle, bad size/alignment, unknown name */
+  STRICTB200_ERR_UNSUPPORTED = 2, /* maps to NotSupportedException (InstructionsToCuda.cs:108) */
+  STRICTB200_ERR_CUDA = 3,
+  STRICTB200_ERR_NCCL = 4,
+  STRICTB200_ERR_OOM = 5,
+  STRICTB200_ERR_TIMEOUT = 6 /* a bounded device-side wait gave up */
+};
+
+typedef struct strictb200_ctx strictb200_ctx;
+typedef struct strictb200_model strictb200_model;
+typedef struct strictb200_kv strictb200_kv;
+
+/* ---- library ---- */
+int strictb200_version(void);
+const char* strictb200_last_error(void);
+
+/* ---- context: replaces `new CudaContext(0)` (Strict.Compiler.Cuda/Kernel.cs:9) and
+ * Kernel.Dispose (Kernel.cs:13-17). destroy(NULL) is a no-op. */
+int strictb200_create(int device, strictb200_ctx** out);
+int strictb200_destroy(strictb200_ctx* ctx);
+int strictb200_synchronize(strictb200_ctx* ctx);
+/* Device memory: replaces CudaDeviceVariable<T> ctor / implicit host<->device conversions
+ * (Strict.Compiler.Cuda.Tests/CSharpToCudaTranspilerTests.cs:64,75-76,56). Copies are
+ * synchronous with respect to the host. */
+int strictb200_malloc(strictb200_ctx* ctx, size_t bytes, void** d_out);
+int strictb200_free(strictb200_ctx* ctx, void* d_ptr);
+int strictb200_memset(strictb200_ctx* ctx, void* d_ptr, int byte, size_t bytes);
+int strictb200_upload(strictb200_ctx* ctx, void* d_dst, const void* h_src, size_t bytes);
+int strictb200_download(strictb200_ctx* ctx, void* h_dst, const void* d_src, size_t bytes);
+/* Asynchronous copies on the context's stream (pinned host memory recommended). */
+int strictb200_upload_async(strictb200_ctx* ctx, void* d_dst, const void* h_src, size_t bytes);
+int strictb200_download_async(strictb200_ctx* ctx, void* h_dst, const void* d_src, size_t bytes);
+int strictb200_host_alloc(strictb200_ctx* ctx, size_t bytes, void** h_out); /* pinned */
+int strictb200_host_free(strictb200_ctx* ctx, void* h_ptr);
+/* Device timing on the context's stream: begin records an event, end records a second one,
+ * waits for it and returns the milliseconds in between. */
+int strictb200_timer_begin(strictb200_ctx* ctx);
+int strictb200_timer_end(strictb200_ctx* ctx, float* ms_out);
+/* Number of kernels this context launched since creation (library kernels only). */
+int strictb200_launch_count(strictb200_ctx* ctx, uint64_t* out);
+/* Writes `bytes` to a private buffer (> L2) so the next kernel starts with a cold L2. */
+int strictb200_flush_l2(strictb200_ctx* ctx);
+
+/* ---- element-wise surface: what the kernels emitted by InstructionsToCuda compute
+ * (Strict.Compiler.Cuda/InstructionsToCuda.cs:58-73,101-109), compiled ahead of time. */
+enum strictb200_ew_op { STRICTB200_ADD = 0, STRICTB200_SUBTRACT = 1, STRICTB200_MULTIPLY = 2, STRICTB200_DIVIDE = 3 };
+/* out[i] = a[i] op b[i], fp32, i < count. Unknown op -> ERR_UNSUPPORTED. */
+int strictb200_ew_binary(strictb200_ctx* ctx, int op, const float* d_a, const float* d_b, float* d_out, int64_t count);
+/* Register program over the instruction subset the emitter handles (InstructionsToCuda.cs:31-53).
+ * code = n_instr quadruples (opcode, a, b, c):
+ *   0 LOAD_ARRAY  r[c] = arrays[a][idx]      (LoadVariableToRegister of an array parameter)
+ *   1 LOAD_SCALAR r[c] = scalars[a]          (width / height / initialDepth, cs:97-98)
+ *   2 LOAD_CONST  r[c] = consts[a]           (LoadConstantInstruction)
+ *   3 ADD 4 SUBTRACT 5 MULTIPLY 6 DIVIDE     r[c] = r[a] op r[b]
+ *   7 RETURN      output[idx] = r[a]         (without one the output is 0.0f, cs:30)
+ * 16 registers (Strict.Bytecode/Register.cs:8-26), at most 64 instructions, 8 arrays,
+ * 8 scalars, 16 constants. h_arrays is a host array of device pointers. */
+int strictb200_ew_program(strictb200_ctx* ctx, const int32_t* h_code, int n_instr, const float* const* h_arrays,
+                          int n_arrays, const float* h_scalars, int n_scalars, const float* h_consts, int n_consts,
+                          float* d_out, int64_t count);
+
+/* ---- seeded generator (device side of the synthetic-tensor specification) ---- */
+int strictb200_gen_normal_f32(strictb200_ctx* ctx, uint64_t seed, uint64_t tensor, int64_t first, int64_t count, float std, float* d_out);
+int strictb200_gen_normal_bf16(strictb200_ctx* ctx, uint64_t seed, uint64_t tensor, int64_t first, int64_t count, float std, uint16_t* d_out);
+int strictb200_gen_tokens(strictb200_ctx* ctx, uint64_t seed, uint64_t tensor, int64_t count, uint32_t range, int32_t* d_out);
+/* rows [row0,row0+rows) x columns [col0,col0+cols) of an E4M3 weight [*,K] whose source is
+ * std*N(0,1); d_scale[r] = absmax(full row)/448 for the generated rows. */
+int strictb200_gen_weight_e4m3(strictb200_ctx* ctx, uint64_t seed, uint64_t tensor, int64_t row0, int64_t rows, int64_t K,
+                               int64_t col0, int64_t cols, float std, uint8_t* d_q, float* d_scale);
+
+/* ---- quantisation and GEMM (no reference counterpart; new surface) ---- */
+/* Per-row absmax quantisation of bf16 [M,K] to E4M3 + fp32 scale[M] (scale = absmax/448). */
+int strictb200_quantize_rows(strictb200_ctx* ctx, const uint16_t* d_x_bf16, int64_t M, int64_t K, uint8_t* d_q, float* d_scale);
+/* Y[M,N] = ((Xq[M,K] . Wq[N,K]^T) * sx[M]) * sw[N], E4M3 x E4M3 -> fp32 -> out.
+ * out_dtype: 0 bf16, 1 fp32. K % 64 == 0 (K % 128 == 0 for the tensor-memory kernels), N % 16 == 0.
+ * kernel: 0 auto, 1 skinny stream (M <= 64), 2 mma.sync tiles, 3 tcgen05/TMEM tiles. */
+int strictb200_gemm_fp8(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const uint8_t* d_xq, const float* d_sx,
+                        const uint8_t* d_wq, const float* d_sw, void* d_out, int out_dtype, int kernel);
+/* bf16 activations in, quantised per token inside; bf16 out. Uses context scratch. */
+int strictb200_gemm_fp8w(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const uint16_t* d_x_bf16, const uint8_t* d_wq,
+                         const float* d_sw, uint16_t* d_y_bf16, int kernel);
+/* fp32 Y[M,N] = X[M,K] . W[N,K]^T + bias[N] (bias may be NULL). */
+int strictb200_gemm_f32(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const float* d_x, const float* d_w,
+                        const float* d_bias, float* d_y);
+
+/* ---- norms / activations ---- */
+/* y = (x * rsqrt(mean(x^2)+eps)) * gain, bf16 in/out, fp32 statistics. If d_residual is not
+ * NULL it is first updated in place: residual = bf16(residual + x), and the norm is taken
+ * of the updated residual. */
+int strictb200_rmsnorm(strictb200_ctx* ctx, const uint16_t* d_x, uint16_t* d_residual, const float* d_gain, float eps, int64_t M,
+                       int64_t d, uint16_t* d_y);
+int strictb200_layernorm(strictb200_ctx* ctx, const float* d_x, const float* d_gain, const float* d_bias, float eps, int64_t M,
+                         int64_t d, float* d_y);
+/* y = bf16(silu(gate) * up); gate_up is [M, 2*I] with gate in columns [0,I). */
+int strictb200_swiglu(strictb200_ctx* ctx, const uint16_t* d_gate_up, int64_t M, int64_t I, uint16_t* d_y);
+int strictb200_gelu_tanh(strictb200_ctx* ctx, const float* d_x, int64_t count, float* d_y);
+/* Per-head RMS norm, rotary embedding (pairs (i, i+D/2), angle pos*theta^(-2i/D)) and cache
+ * append. qkv is bf16 [T, (Hq+2Hkv)*D]; token t belongs to sequence seq[t] at position pos[t];
+ * q_out is bf16 [T,Hq,D]; caches are bf16 [B,Hkv,maxlen,D]. */
+int strictb200_rope_qknorm_kvappend(strictb200_ctx* ctx, const uint16_t* d_qkv, const int32_t* d_seq, const int32_t* d_pos, int64_t T,
+                                    int Hq, int Hkv, int D, const float* d_qgain, const float* d_kgain, float eps, float theta,
+                                    int max_pos, uint16_t* d_q_out, uint16_t* d_kcache, uint16_t* d_vcache, int maxlen);
+
+/* ---- attention (bf16, GQA, D = 128) ---- */
+/* Causal prefill: q [B,S,Hq,D]; caches [B,Hkv,maxlen,D] already hold positions [0,lens[b]);
+ * the query at row i of sequence b has position past[b]+i (past may be NULL = 0) and the
+ * rows i < lens[b]-past[b] are computed. out [B,S,Hq,D]. */
+int strictb200_attn_prefill(strictb200_ctx* ctx, const uint16_t* d_q, const uint16_t* d_kcache, const uint16_t* d_vcache,
+                            const int32_t* d_lens, const int32_t* d_past, int B, int S, int Hq, int Hkv, int D, int maxlen,
+                            float scale, uint16_t* d_out);
+/* Split-KV decode: one query per sequence, q [B,Hq,D], keys [0,lens[b]). out [B,Hq,D].
+ * Uses context scratch for the per-split partial results. */
+int strictb200_attn_decode(strictb200_ctx* ctx, const uint16_t* d_q, const uint16_t* d_kcache, const uint16_t* d_vcache,
+                           const int32_t* d_lens, int B, int Hq, int Hkv, int D, int maxlen, float scale, uint16_t* d_out);
+
+/* ---- embedding / sampling ---- */
+int strictb200_embedding_bf16(strictb200_ctx* ctx, const uint16_t* d_table, const int32_t* d_ids, int64_t T, int64_t d, int64_t vocab,
+                              uint16_t* d_out);
+/* argmax over the last dimension of fp32 [M,N]; ties go to the lowest index. */
+int strictb200_argmax(strictb200_ctx* ctx, const float* d_x, int64_t M, int64_t N, int32_t* d_out);
+
+/* ---- model / KV-cache objects (new API in the style of the existing surface) ---- */
+enum strictb200_arch { STRICTB200_GPT2 = 0, STRICTB200_QWEN3 = 1 };
+typedef struct strictb200_model_config {
+  int32_t arch;       /* strictb200_arch */
+  int32_t n_layers, d_model, n_q_heads, n_kv_heads, head_dim, d_ff, vocab;
+  int32_t max_pos;    /* positions the model can address (learned table / RoPE table) */
+  int32_t tied;       /* LM head shares the embedding matrix */
+  float eps;          /* norm epsilon */
+  float rope_theta;
+} strictb200_model_config;
+
+int strictb200_model_create(strictb200_ctx* ctx, const strictb200_model_config* cfg, strictb200_model** out);
+int strictb200_model_destroy(strictb200_model* m);
+/* Fill every tensor from the seeded generator (std 0.02, norm gains 1, biases 0). Under
+ * tensor parallelism each rank generates only its own shard. */
+int strictb200_model_init_random(strictb200_model* m, uint64_t seed);
+/* Set / read one full (unsharded) tensor by name from / to host memory; the library slices
+ * it for this rank. Names: "embed", "wpe", "normf.g", "normf.b", "head.q", "head.s",
+ * "layers.<i>.{norm1.g,norm1.b,norm2.g,norm2.b,qnorm.g,knorm.g}", Qwen3:
+ * "layers.<i>.{wqkv,wo,wgu,wdown}.{q,s}", GPT-2: "layers.<i>.{wqkv,wo,wfc,wproj}.{w,b}".
+ * fp32 host data except ".q" (E4M3 bytes); "embed" of a Qwen3 model is given as fp32 and
+ * rounded to bf16. */
+int strictb200_model_set_tensor(strictb200_model* m, const char* name, const void* h_data, size_t bytes);
+int strictb200_model_get_tensor(strictb200_model* m, const char* name, void* h_data, size_t bytes);
+int strictb200_model_weight_bytes(strictb200_model* m, uint64_t* out);
+
+int strictb200_kv_create(strictb200_model* m, int batch, int maxlen, strictb200_kv** out);
+int strictb200_kv_destroy(strictb200_kv* kv);
+int strictb200_kv_reset(strictb200_kv* kv);
+int strictb200_kv_lens(strictb200_kv* kv, int32_t* h_lens);
+/* Fill positions [0,len) of every sequence with seeded N(0,1) keys/values and set the
+ * lengths to len (benchmark set-up of a long context without running the prefill). */
+int strictb200_kv_fill_synthetic(strictb200_kv* kv, uint64_t seed, int len);
+
+/* Prefill: h_tokens [B,S] row-major, the first h_lens[b] of each row are real. Appends to the
+ * cache, writes the greedy next token of every sequence to h_next[B] and, if not NULL, the
+ * fp32 logits [B,vocab] to h_logits. */
+int strictb200_prefill(strictb200_model* m, strictb200_kv* kv, const int32_t* h_tokens, const int32_t* h_lens, int B, int S,
+                       int32_t* h_next, float* h_logits);
+/* One decode step for every sequence of the cache: h_ids[B] in, greedy next ids out. */
+int strictb200_decode_step(strictb200_model* m, strictb200_kv* kv, const int32_t* h_ids, int32_t* h_next, float* h_logits);
+/* n_steps greedy steps entirely on the device starting from h_ids; h_out [n_steps,B]. */
+int strictb200_generate(strictb200_model* m, strictb200_kv* kv, const int32_t* h_ids, int n_steps, int32_t* h_out);
+/* Same, with ids already on the device and no host copy: d_ids[B] is read and overwritten
+ * each step (benchmark `value` leg). */
+int strictb200_decode_steps_device(strictb200_model* m, strictb200_kv* kv, int32_t* d_ids, int n_steps);
+int strictb200_kv_device_ids(strictb200_kv* kv, int32_t** d_ids_out);
+/* 1 = capture the decode step in a CUDA graph and replay it (default), 0 = plain launches. */
+int strictb200_model_set_graph(strictb200_model* m, int enabled);
+/* Algorithmic bytes one decode step reads at the cache's current lengths (weights + KV). */
+int strictb200_decode_bytes(strictb200_model* m, strictb200_kv* kv, uint64_t* out);
+
+/* ---- tensor parallelism: one context per GPU/rank, NCCL over NVLink ---- */
+/* 128-byte NCCL unique id, created on rank 0 and handed to every rank by the host. */
+int strictb200_tp_unique_id(void* h_id128);
+/* Must be called before model_create on that context. world in {1,2,4,8}. */
+int strictb200_tp_init(strictb200_ctx* ctx, int world, int rank, const void* h_id128);
+int strictb200_tp_info(strictb200_ctx* ctx, int* world, int* rank);
+/* fp32 sum all-reduce in place on the context's stream (the collective the model uses). */
+int strictb200_tp_allreduce_f32(strictb200_ctx* ctx, float* d_buf, int64_t count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STRICTB200_H */

@@ -1,0 +1,10 @@
+"""strict_b200 — host-side mirror of the Strict CUDA surface over libstrictb200.so (sm_100a).
+
+Importing the package does not load the native library; the first Context()/lib() call does,
+and raises if the library has not been built or no B200 is present (there is no CPU path).
+"""
+from .native import KernelException, lib, LIB_PATH  # noqa: F401
+from .kernel import Context, DeviceVariable, Kernel  # noqa: F401
+from .instructions_to_cuda import (CSharpToCudaTranspiler, CSharpType, InstructionsToCuda, InvalidCode, Method,  # noqa: F401
+                                   MissingReturnStatement)
+from .model import CONFIGS, GPT2, QWEN3, KvCache, Model  # noqa: F401

@@ -1,0 +1,533 @@
+// GQA attention over the bf16 KV cache (head_dim 128) and the fp32 attention of the GPT-2 path.
+//
+//  * prefill: flash-style causal kernel; one block = 64 query positions of one query head,
+//    KV tiles of 64 keys double-buffered in shared memory by cp.async, bf16 mma.sync
+//    m16n8k16 with fp32 online softmax; keys come straight from the cache, so a chunked
+//    prefill (past > 0) is the same kernel.
+//  * decode: split-KV. One block = one KV head of one sequence over one chunk of keys; the
+//    G = Hq/Hkv query heads that share the KV head are the rows of the MMA tile, so every
+//    K/V byte is read from HBM once. Each block writes (m, l, o) partials; a combine kernel
+//    merges the chunks and can emit the per-token E4M3 quantisation the next GEMM consumes.
+//
+// Shared-memory tiles hold rows of 128 bf16 (256 B = 16 chunks of 16 B); chunk c of row r
+// lives at chunk c ^ (r & 7), which makes every ldmatrix phase conflict-free.
+#include "common.cuh"
+
+namespace {
+
+constexpr int D = 128;
+constexpr int KT = 64;  // keys per tile
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t s, const void* g, bool valid) {
+  int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(g), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
+}
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) { return (uint32_t)(row * 256 + ((chunk ^ (row & 7)) << 4)); }
+
+// Copy `rows` rows of 128 bf16 (global row stride 128 elements) into a swizzled tile; rows at
+// or beyond `valid_rows` are zero-filled.
+__device__ __forceinline__ void load_tile(uint32_t tile, const bf16* src, int rows, int valid_rows, int nthreads) {
+  for (int c = threadIdx.x; c < rows * 16; c += nthreads) {
+    int r = c >> 4, cc = c & 15;
+    bool v = r < valid_rows;
+    cp_async16(tile + tile_off(r, cc), src + (int64_t)(v ? r : 0) * D + cc * 8, v);
+  }
+}
+
+// ------------------------------------------------------------------ prefill
+// grid (ceil(S/64), Hq, B), 128 threads.
+__global__ void __launch_bounds__(128) attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                                                           const int32_t* __restrict__ lens, const int32_t* __restrict__ past,
+                                                           const int32_t* __restrict__ qstart, int S, int Hq, int Hkv, int maxlen,
+                                                           float scale_log2, bf16* __restrict__ out) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * 64;
+  const int len = lens[b], pst = past ? past[b] : 0;
+  const int n_new = len - pst;
+  if (q0 >= n_new) return;
+  const int64_t row0 = qstart ? qstart[b] : (int64_t)b * S;  // first row of this sequence in q / out
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int hk = h / (Hq / Hkv);
+  const uint32_t sQ = smem_u32(smem), sK = sQ + 64 * 256, sV = sK + 2 * KT * 256;
+  const bf16* kbase = kc + ((int64_t)b * Hkv + hk) * maxlen * D;
+  const bf16* vbase = vc + ((int64_t)b * Hkv + hk) * maxlen * D;
+  // last key any row of this block may see
+  const int kv_end = min(len, pst + q0 + 64);
+  const int ntiles = (kv_end + KT - 1) / KT;
+
+  // Q tile: rows q0..q0+63 of head h; global row stride Hq*D
+  for (int c = threadIdx.x; c < 64 * 16; c += 128) {
+    int r = c >> 4, cc = c & 15;
+    bool v = q0 + r < n_new;
+    cp_async16(sQ + tile_off(r, cc), q + ((row0 + (v ? q0 + r : 0)) * Hq + h) * D + cc * 8, v);
+  }
+  load_tile(sK, kbase, KT, min(KT, len), 128);
+  load_tile(sV, vbase, KT, min(KT, len), 128);
+  cp_async_commit();
+
+  uint32_t qf[8][4];
+  float o[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; j++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) o[j][i] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int qpos0 = pst + q0 + warp * 16 + g;  // position of row g; row g+8 is qpos0+8
+  const int mi = lane >> 3, r8 = lane & 7;
+
+  for (int t = 0; t < ntiles; t++) {
+    if (t + 1 < ntiles) {
+      int k0 = (t + 1) * KT;
+      load_tile(sK + ((t + 1) & 1) * KT * 256, kbase + (int64_t)k0 * D, KT, min(KT, len - k0), 128);
+      load_tile(sV + ((t + 1) & 1) * KT * 256, vbase + (int64_t)k0 * D, KT, min(KT, len - k0), 128);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (t == 0) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ks++) ldsm_x4(sQ + tile_off(warp * 16 + (mi & 1) * 8 + r8, 2 * ks + (mi >> 1)), qf[ks]);
+    }
+    const uint32_t tK = sK + (t & 1) * KT * 256, tV = sV + (t & 1) * KT * 256;
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) s[j][i] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 8; ks++) {
+#pragma unroll
+      for (int jp = 0; jp < 4; jp++) {
+        uint32_t kb[4];
+        ldsm_x4(tK + tile_off(jp * 16 + (mi >> 1) * 8 + r8, 2 * ks + (mi & 1)), kb);
+        mma_bf16(s[2 * jp], qf[ks], kb[0], kb[1]);
+        mma_bf16(s[2 * jp + 1], qf[ks], kb[2], kb[3]);
+      }
+    }
+    // scale, mask, online softmax
+    const int kbase_pos = t * KT;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        int kpos = kbase_pos + 8 * j + 2 * tig + (i & 1);
+        int qpos = qpos0 + ((i >> 1) << 3);
+        float v = s[j][i] * scale_log2;
+        v = (kpos > qpos || kpos >= len) ? -INFINITY : v;
+        s[j][i] = v;
+        mx[i >> 1] = fmaxf(mx[i >> 1], v);
+      }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      float m_new = fmaxf(m_run[r], mx[r]);
+      m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+      corr[r] = exp2f(m_run[r] - m_use[r]);
+      m_run[r] = m_new;
+    }
+    float ls[2] = {0.f, 0.f};
+    uint32_t pf[4][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
+      float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
+      ls[0] += p0 + p1;
+      ls[1] += p2 + p3;
+      pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+      pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; r++) l_run[r] = l_run[r] * corr[r] + ls[r];
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      o[j][0] *= corr[0]; o[j][1] *= corr[0];
+      o[j][2] *= corr[1]; o[j][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; kk++) {
+#pragma unroll
+      for (int jj = 0; jj < 8; jj++) {
+        uint32_t vb[4];
+        ldsm_x4_t(tV + tile_off(kk * 16 + (mi & 1) * 8 + r8, 2 * jj + (mi >> 1)), vb);
+        mma_bf16(o[2 * jj], pf[kk], vb[0], vb[1]);
+        mma_bf16(o[2 * jj + 1], pf[kk], vb[2], vb[3]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+    int row = q0 + warp * 16 + g + r * 8;
+    if (row < n_new) {
+      float inv = 1.0f / l_run[r];
+      bf16* dst = out + ((row0 + row) * Hq + h) * D;
+#pragma unroll
+      for (int j = 0; j < 16; j++) *(uint32_t*)(dst + 8 * j + 2 * tig) = pack_bf16(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ decode (split-KV)
+// grid (nsplit, Hkv, B), 128 threads. Warp w owns keys [16w,16w+16) of every 64-key tile.
+// scratch: o_part [B][Hq][nsplit][128] then ml_part [B][Hq][nsplit][2].
+__global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                                                          const int32_t* __restrict__ lens, int len_add, int B, int Hq, int Hkv, int maxlen,
+                                                          int chunk, int nsplit, float scale_log2, float* __restrict__ o_part,
+                                                          float* __restrict__ ml_part) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int len = min(lens[b] + len_add, maxlen);
+  const int k_begin = split * chunk;
+  if (k_begin >= len) return;
+  const int k_end = min(len, k_begin + chunk);
+  const int G = Hq / Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const uint32_t sK = smem_u32(smem), sV = sK + 2 * KT * 256;
+  const bf16* kbase = kc + ((int64_t)b * Hkv + hk) * maxlen * D;
+  const bf16* vbase = vc + ((int64_t)b * Hkv + hk) * maxlen * D;
+  const int ntiles = (k_end - k_begin + KT - 1) / KT;
+
+  load_tile(sK, kbase + (int64_t)k_begin * D, KT, min(KT, k_end - k_begin), 128);
+  load_tile(sV, vbase + (int64_t)k_begin * D, KT, min(KT, k_end - k_begin), 128);
+  cp_async_commit();
+
+  // Q fragments straight from global: rows = the G query heads of this KV head (zero beyond)
+  uint32_t qf[8][4];
+  {
+    const bf16* q0 = q + ((int64_t)b * Hq + hk * G) * D;
+#pragma unroll
+    for (int ks = 0; ks < 8; ks++) {
+      int d0 = ks * 16 + 2 * tig;
+      qf[ks][0] = g < G ? *(const uint32_t*)(q0 + g * D + d0) : 0u;
+      qf[ks][1] = g + 8 < G ? *(const uint32_t*)(q0 + (g + 8) * D + d0) : 0u;
+      qf[ks][2] = g < G ? *(const uint32_t*)(q0 + g * D + d0 + 8) : 0u;
+      qf[ks][3] = g + 8 < G ? *(const uint32_t*)(q0 + (g + 8) * D + d0 + 8) : 0u;
+    }
+  }
+  float o[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; j++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) o[j][i] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int mi = lane >> 3, r8 = lane & 7;
+
+  for (int t = 0; t < ntiles; t++) {
+    if (t + 1 < ntiles) {
+      int k0 = k_begin + (t + 1) * KT;
+      load_tile(sK + ((t + 1) & 1) * KT * 256, kbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
+      load_tile(sV + ((t + 1) & 1) * KT * 256, vbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t tK = sK + (t & 1) * KT * 256, tV = sV + (t & 1) * KT * 256;
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < 8; ks++) {
+      uint32_t kb[4];
+      ldsm_x4(tK + tile_off(warp * 16 + (mi >> 1) * 8 + r8, 2 * ks + (mi & 1)), kb);
+      mma_bf16(s[0], qf[ks], kb[0], kb[1]);
+      mma_bf16(s[1], qf[ks], kb[2], kb[3]);
+    }
+    const int kpos0 = k_begin + t * KT + warp * 16;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 2; j++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        int kpos = kpos0 + 8 * j + 2 * tig + (i & 1);
+        float v = kpos >= k_end ? -INFINITY : s[j][i] * scale_log2;
+        s[j][i] = v;
+        mx[i >> 1] = fmaxf(mx[i >> 1], v);
+      }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      float m_new = fmaxf(m_run[r], mx[r]);
+      m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+      corr[r] = exp2f(m_run[r] - m_use[r]);
+      m_run[r] = m_new;
+    }
+    uint32_t pf[4];
+    {
+      float p[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        p[j][0] = exp2f(s[j][0] - m_use[0]); p[j][1] = exp2f(s[j][1] - m_use[0]);
+        p[j][2] = exp2f(s[j][2] - m_use[1]); p[j][3] = exp2f(s[j][3] - m_use[1]);
+      }
+      l_run[0] = l_run[0] * corr[0] + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
+      l_run[1] = l_run[1] * corr[1] + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
+      pf[0] = pack_bf16(p[0][0], p[0][1]); pf[1] = pack_bf16(p[0][2], p[0][3]);
+      pf[2] = pack_bf16(p[1][0], p[1][1]); pf[3] = pack_bf16(p[1][2], p[1][3]);
+    }
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      o[j][0] *= corr[0]; o[j][1] *= corr[0];
+      o[j][2] *= corr[1]; o[j][3] *= corr[1];
+    }
+#pragma unroll
+    for (int jj = 0; jj < 8; jj++) {
+      uint32_t vb[4];
+      ldsm_x4_t(tV + tile_off(warp * 16 + (mi & 1) * 8 + r8, 2 * jj + (mi >> 1)), vb);
+      mma_bf16(o[2 * jj], pf, vb[0], vb[1]);
+      mma_bf16(o[2 * jj + 1], pf, vb[2], vb[3]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  // merge the four warps through shared memory (tiles are free after the last barrier)
+  float* so = (float*)smem;                       // [4 warps][16 rows][128]
+  float* sml = so + 4 * 16 * D;                   // [4 warps][16 rows][2]
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+    int row = g + 8 * r;
+    if (row < G) {
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        so[(warp * 16 + row) * D + 8 * j + 2 * tig] = o[j][2 * r];
+        so[(warp * 16 + row) * D + 8 * j + 2 * tig + 1] = o[j][2 * r + 1];
+      }
+      if (tig == 0) { sml[(warp * 16 + row) * 2] = m_run[r]; sml[(warp * 16 + row) * 2 + 1] = l_run[r]; }
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < G * D; e += 128) {
+    int row = e / D, d = e - row * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; w++) M = fmaxf(M, sml[(w * 16 + row) * 2]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      float mw = sml[(w * 16 + row) * 2];
+      float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += sml[(w * 16 + row) * 2 + 1] * f;
+      O += so[(w * 16 + row) * D + d] * f;
+    }
+    int64_t idx = ((int64_t)b * Hq + hk * G + row) * nsplit + split;
+    o_part[idx * D + d] = O;
+    if (d == 0) { ml_part[idx * 2] = M; ml_part[idx * 2 + 1] = L; }
+  }
+}
+
+// grid B, 256 threads: merge the chunks of every head of one token; optional E4M3 quantisation
+// of the whole token row [Hq*128] (the o_proj input).
+__global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
+                                                           const int32_t* __restrict__ lens, int len_add, int Hq, int maxlen, int chunk,
+                                                           int nsplit, bf16* __restrict__ out, uint8_t* __restrict__ q_out,
+                                                           float* __restrict__ qscale) {
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  const int len = min(lens[b] + len_add, maxlen);
+  const int ns = (len + chunk - 1) / chunk;
+  float amax = 0.f;
+  for (int e = threadIdx.x; e < Hq * D; e += 256) {
+    int h = e / D, d = e - h * D;
+    int64_t base = ((int64_t)b * Hq + h) * nsplit;
+    float M = -INFINITY;
+    for (int s = 0; s < ns; s++) M = fmaxf(M, ml_part[(base + s) * 2]);
+    float L = 0.f, O = 0.f;
+    for (int s = 0; s < ns; s++) {
+      float f = exp2f(ml_part[(base + s) * 2] - M);
+      L += ml_part[(base + s) * 2 + 1] * f;
+      O += o_part[(base + s) * D + d] * f;
+    }
+    float v = ns > 0 ? round_bf16(O / L) : 0.f;
+    out[((int64_t)b * Hq + h) * D + d] = __float2bfloat16_rn(v);
+    amax = fmaxf(amax, fabsf(v));
+  }
+  if (!q_out) return;
+  amax = block_max(amax, red);
+  float inv = 1.0f, sc = 1.0f;
+  if (amax > 0.f) { inv = __fdiv_rn(448.0f, amax); sc = __fdiv_rn(amax, 448.0f); }
+  if (threadIdx.x == 0) qscale[b] = sc;
+  __syncthreads();  // the row written above is re-read below by other threads of the block
+  for (int e = threadIdx.x * 4; e < Hq * D; e += 1024) {
+    const bf16* src = out + (int64_t)b * Hq * D + e;
+    uint2 u = *(const uint2*)src;
+    float v0 = __uint_as_float(u.x << 16), v1 = __uint_as_float(u.x & 0xFFFF0000u);
+    float v2 = __uint_as_float(u.y << 16), v3 = __uint_as_float(u.y & 0xFFFF0000u);
+    *(uint32_t*)(q_out + (int64_t)b * Hq * D + e) =
+        f32x4_to_e4m3x4(__fmul_rn(v0, inv), __fmul_rn(v1, inv), __fmul_rn(v2, inv), __fmul_rn(v3, inv));
+  }
+}
+
+// ------------------------------------------------------------------ fp32 attention (GPT-2 path)
+__global__ void kv_append_f32_kernel(const float* __restrict__ qkv, float* __restrict__ kc, float* __restrict__ vc,
+                                     const int32_t* __restrict__ seq, const int32_t* __restrict__ pos, const int32_t* __restrict__ lens, int H,
+                                     int Dh, int maxlen) {
+  int64_t t = blockIdx.x;
+  int b = seq ? seq[t] : (int)t;
+  int p = pos ? pos[t] : lens[b];
+  if (p < 0 || p >= maxlen) return;
+  int hd = H * Dh;
+  for (int e = threadIdx.x; e < hd; e += blockDim.x) {
+    int h = e / Dh, d = e - h * Dh;
+    int64_t dst = (((int64_t)b * H + h) * maxlen + p) * Dh + d;
+    kc[dst] = qkv[t * 3 * hd + hd + e];
+    vc[dst] = qkv[t * 3 * hd + 2 * hd + e];
+  }
+}
+// grid (H, T), 128 threads; scores of one (token, head) live in shared memory.
+__global__ void __launch_bounds__(128) attn_f32_kernel(const float* __restrict__ qkv, const float* __restrict__ kc, const float* __restrict__ vc,
+                                                       const int32_t* __restrict__ seq, const int32_t* __restrict__ pos,
+                                                       const int32_t* __restrict__ lens, int H, int Dh, int maxlen, float scale,
+                                                       float* __restrict__ out) {
+  extern __shared__ float sc[];  // [maxlen] scores, then [Dh] query
+  __shared__ float red[32];
+  int h = blockIdx.x;
+  int64_t t = blockIdx.y;
+  int b = seq ? seq[t] : (int)t;
+  int p = pos ? pos[t] : lens[b];
+  if (p < 0 || p >= maxlen) return;
+  int n = p + 1;
+  float* qs = sc + maxlen;
+  int hd = H * Dh;
+  for (int d = threadIdx.x; d < Dh; d += blockDim.x) qs[d] = qkv[t * 3 * hd + h * Dh + d];
+  __syncthreads();
+  const float* kb = kc + ((int64_t)b * H + h) * maxlen * Dh;
+  const float* vb = vc + ((int64_t)b * H + h) * maxlen * Dh;
+  float mx = -INFINITY;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const float4* kr = (const float4*)(kb + (int64_t)j * Dh);
+    float acc = 0.f;
+    for (int d4 = 0; d4 < Dh / 4; d4++) {
+      float4 kv = kr[d4];
+      acc += kv.x * qs[4 * d4] + kv.y * qs[4 * d4 + 1] + kv.z * qs[4 * d4 + 2] + kv.w * qs[4 * d4 + 3];
+    }
+    acc *= scale;
+    sc[j] = acc;
+    mx = fmaxf(mx, acc);
+  }
+  mx = block_max(mx, red);
+  float l = 0.f;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    float e = expf(sc[j] - mx);
+    sc[j] = e;
+    l += e;
+  }
+  l = block_sum(l, red);
+  __syncthreads();
+  float inv = 1.0f / l;
+  for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < n; j++) acc += sc[j] * vb[(int64_t)j * Dh + d];
+    out[t * hd + h * Dh + d] = acc * inv;
+  }
+}
+
+}  // namespace
+
+int k_attn_prefill(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16* vc, const int32_t* lens, const int32_t* past,
+                   const int32_t* qstart, int B, int S, int Hq, int Hkv, int Dh, int maxlen, float scale, bf16* out) {
+  if (Dh != D) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: head_dim must be 128");
+  static bool attr = false;
+  size_t smem = 64 * 256 + 4 * KT * 256;
+  if (!attr) {
+    SB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = true;
+  }
+  if (Hq > 65535 || B > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: too many heads or sequences");
+  dim3 grid((S + 63) / 64, Hq, B);
+  attn_prefill_kernel<<<grid, 128, smem, ctx->stream>>>(q, kc, vc, lens, past, qstart, S, Hq, Hkv, maxlen, scale * LOG2E, out);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}
+
+// Keys per block: sized so that a full cache yields about six blocks per SM.
+static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
+  int64_t total = (int64_t)maxlen * B * Hkv;
+  int64_t c = total / ((int64_t)ctx->sm_count * 6);
+  c = (c + KT - 1) / KT * KT;
+  if (c < 256) c = 256;
+  if (c > maxlen) c = (maxlen + KT - 1) / KT * KT;
+  return (int)c;
+}
+int sb_attn_decode_splits(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
+  int c = decode_chunk(ctx, B, Hkv, maxlen);
+  return (maxlen + c - 1) / c;
+}
+size_t sb_attn_decode_scratch(int B, int Hq, int Dh, int nsplit) { return (size_t)B * Hq * nsplit * (Dh + 2) * sizeof(float); }
+
+int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16* vc, const int32_t* lens, int len_add, int B, int Hq, int Hkv,
+                  int Dh, int maxlen, float scale, int nsplit, float* scratch, bf16* out, uint8_t* q_out, float* qscale_out) {
+  if (Dh != D) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: head_dim must be 128");
+  if (Hq / Hkv > 16) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: at most 16 query heads per KV head");
+  if ((Hq * D) % 4) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: bad head count");
+  int chunk = decode_chunk(ctx, B, Hkv, maxlen);
+  if ((maxlen + chunk - 1) / chunk != nsplit) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: split count does not match the cache size");
+  static bool attr = false;
+  size_t smem = 4 * KT * 256;  // 64 KB; also covers the 34 KB merge area
+  if (!attr) {
+    SB_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = true;
+  }
+  float* o_part = scratch;
+  float* ml_part = scratch + (size_t)B * Hq * nsplit * D;
+  if (Hkv > 65535 || B > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: too many heads or sequences");
+  dim3 grid(nsplit, Hkv, B);
+  attn_decode_kernel<<<grid, 128, smem, ctx->stream>>>(q, kc, vc, lens, len_add, B, Hq, Hkv, maxlen, chunk, nsplit, scale * LOG2E, o_part, ml_part);
+  SB_LAUNCHED(ctx);
+  attn_combine_kernel<<<B, 256, 0, ctx->stream>>>(o_part, ml_part, lens, len_add, Hq, maxlen, chunk, nsplit, out, q_out, qscale_out);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}
+
+int k_attn_f32(strictb200_ctx* ctx, const float* qkv, float* kc, float* vc, const int32_t* seq, const int32_t* pos, const int32_t* lens,
+               int64_t T, int H, int Dh, int maxlen, float scale, float* out) {
+  if (Dh % 4) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: head_dim must be a multiple of 4");
+  size_t smem = ((size_t)maxlen + Dh) * sizeof(float);
+  if (smem > 200 * 1024) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: fp32 path supports at most ~50k positions");
+  static size_t attr_smem = 48 * 1024;
+  if (smem > attr_smem) {
+    SB_CUDA(cudaFuncSetAttribute(attn_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_smem = smem;
+  }
+  kv_append_f32_kernel<<<(unsigned)T, 256, 0, ctx->stream>>>(qkv, kc, vc, seq, pos, lens, H, Dh, maxlen);
+  SB_LAUNCHED(ctx);
+  if (T > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: too many rows for the fp32 path");
+  dim3 grid(H, (unsigned)T);
+  attn_f32_kernel<<<grid, 128, smem, ctx->stream>>>(qkv, kc, vc, seq, pos, lens, H, Dh, maxlen, scale, out);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}

@@ -1,0 +1,214 @@
+// Internal declarations shared by the translation units of libstrictb200.so.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/strictb200.h"
+
+struct TpState;  // tp.cpp
+
+struct strictb200_ctx {
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  uint64_t launches = 0;
+  // scratch for op-level entry points (quantised activations, split partials)
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  void* flush_buf = nullptr;
+  size_t flush_bytes = 0;
+  int tp_world = 1, tp_rank = 0;
+  TpState* tp = nullptr;
+};
+
+void sb_set_error(const std::string& msg);
+int sb_fail(int code, const std::string& msg);
+int sb_ws(strictb200_ctx* ctx, size_t bytes, void** out);  // grow-only context scratch
+
+#define SB_CUDA(expr)                                                                          \
+  do {                                                                                         \
+    cudaError_t _e = (expr);                                                                   \
+    if (_e != cudaSuccess)                                                                     \
+      return sb_fail(_e == cudaErrorMemoryAllocation ? STRICTB200_ERR_OOM : STRICTB200_ERR_CUDA, \
+                     std::string(#expr) + ": " + cudaGetErrorString(_e));                      \
+  } while (0)
+#define SB_TRY(expr)            \
+  do {                          \
+    int _s = (expr);            \
+    if (_s != STRICTB200_OK) return _s; \
+  } while (0)
+#define SB_REQUIRE(cond, msg) \
+  do {                        \
+    if (!(cond)) return sb_fail(STRICTB200_ERR_INVALID_ARG, std::string(msg) + " (" #cond ")"); \
+  } while (0)
+#define SB_ENTER(ctx)                                                  \
+  do {                                                                 \
+    if (!(ctx)) return sb_fail(STRICTB200_ERR_INVALID_ARG, "null context"); \
+    SB_CUDA(cudaSetDevice((ctx)->device));                             \
+  } while (0)
+// after a kernel launch
+#define SB_LAUNCHED(ctx)          \
+  do {                            \
+    (ctx)->launches++;            \
+    SB_CUDA(cudaGetLastError());  \
+  } while (0)
+
+// ------------------------------------------------------------------ launchers (internal API)
+// Every launcher enqueues on ctx->stream and returns a status.
+typedef __nv_bfloat16 bf16;
+
+// elementwise.cu
+int k_ew_binary(strictb200_ctx*, int op, const float* a, const float* b, float* out, int64_t n);
+int k_ew_program(strictb200_ctx*, const int32_t* h_code, int n_instr, const float* const* h_arrays, int n_arrays,
+                 const float* h_scalars, int n_scalars, const float* h_consts, int n_consts, float* out, int64_t n);
+// gen.cu
+int k_gen_normal_f32(strictb200_ctx*, uint64_t key, int64_t first, int64_t count, float std_, float* out);
+int k_gen_normal_bf16(strictb200_ctx*, uint64_t key, int64_t first, int64_t count, float std_, bf16* out);
+int k_gen_tokens(strictb200_ctx*, uint64_t key, int64_t count, uint32_t range, int32_t* out);
+int k_gen_weight_e4m3(strictb200_ctx*, uint64_t key, int64_t row0, int64_t rows, int64_t K, int64_t col0, int64_t cols,
+                      float std_, uint8_t* q, int64_t ldq, float* scale);
+uint64_t sb_stream_key(uint64_t seed, uint64_t tensor);
+// norm.cu
+struct QuantOut { uint8_t* q; float* scale; };  // optional fused E4M3 output of a row-wise op
+int k_quantize_rows(strictb200_ctx*, const bf16* x, int64_t M, int64_t K, int64_t ldx, uint8_t* q, float* scale);
+int k_quantize_rows_f32(strictb200_ctx*, const float* x, int64_t M, int64_t K, uint8_t* q, float* scale);
+// Row op of the residual stream. For every token row:
+//   y_in  = part ? bf16(sum over groups g of (sum over splits s of part[g][s][row]) * sx[g][row] * sw[col]) : x_in
+//   resid = residual ? bf16(residual + y_in) (stored back) : y_in
+//   n     = (resid * r) * gain ; written as bf16 (y) and/or quantised E4M3 (q, scale)
+struct RowNormArgs {
+  const float* x_f32 = nullptr;      // [M,d] fp32 input rounded to bf16 first (after an all-reduce)
+  const bf16* x_in = nullptr;        // [M,d] (used when part and x_f32 are null)
+  const float* part = nullptr;       // [groups][splits][M,d] fp32 raw accumulators
+  int groups = 1, splits = 1;
+  const float* sx = nullptr;         // [groups][M]
+  const float* sw = nullptr;         // [d]
+  bf16* residual = nullptr;          // [M,d] in/out, may be null
+  const float* gain = nullptr;       // [d]
+  float eps = 1e-6f;
+  bf16* y = nullptr;                 // [M,d] normalised bf16 output, may be null
+  uint8_t* q = nullptr;              // [M,d] quantised output, may be null
+  float* qscale = nullptr;           // [M]
+  bf16* y_raw = nullptr;             // [M,d] bf16(y_in) before the residual add, may be null
+};
+int k_rownorm(strictb200_ctx*, const RowNormArgs& a, int64_t M, int64_t d);
+int k_reduce_scale(strictb200_ctx*, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N, float* out);
+int k_layernorm(strictb200_ctx*, const float* x, const float* g, const float* b, float eps, int64_t M, int64_t d, float* y);
+int k_add_f32(strictb200_ctx*, float* x, const float* y, int64_t n);
+int k_swiglu(strictb200_ctx*, const bf16* gate_up, int64_t M, int64_t I, bf16* y, uint8_t* q, float* qscale);
+int k_gelu_tanh(strictb200_ctx*, const float* x, int64_t n, float* y);
+// rope.cu
+struct RopeArgs {
+  const bf16* qkv = nullptr;      // [T, nqkv] bf16 (used when part == nullptr)
+  const float* part = nullptr;    // [splits][T, nqkv] raw accumulators
+  int splits = 1;
+  const float* sx = nullptr;      // [T]
+  const float* sw = nullptr;      // [nqkv]
+  const int32_t* seq = nullptr;   // [T] sequence of each row (null: row t is sequence t)
+  const int32_t* pos = nullptr;   // [T] position of each row (null: pos = lens[seq])
+  const int32_t* lens = nullptr;  // [B] current lengths (decode)
+  const float* cos_t = nullptr;   // [max_pos, D/2]
+  const float* sin_t = nullptr;
+  const float* qgain = nullptr;
+  const float* kgain = nullptr;
+  float eps = 1e-6f;
+  int Hq = 0, Hkv = 0, D = 128, maxlen = 0, max_pos = 0;
+  bf16* q_out = nullptr;          // [T,Hq,D]
+  bf16* kcache = nullptr;         // [B,Hkv,maxlen,D]
+  bf16* vcache = nullptr;
+};
+int k_rope_qknorm_kvappend(strictb200_ctx*, const RopeArgs& a, int64_t T);
+int sb_rope_table(strictb200_ctx*, int max_pos, int D, float theta, float** d_cos, float** d_sin);
+// gemm_fp8.cu
+struct GemmArgs {
+  int64_t M = 0, N = 0, K = 0;
+  const uint8_t* xq = nullptr;  // [M,K], row stride ldx
+  int64_t ldx = 0;
+  const float* sx = nullptr;    // [M]
+  const uint8_t* wq = nullptr;  // [N,K], row stride ldw
+  int64_t ldw = 0;
+  const float* sw = nullptr;    // [N]
+  void* out = nullptr;          // [M,N] bf16 or fp32 (when splits == 1)
+  int out_f32 = 0;
+  float* part = nullptr;        // [splits][M,N] raw accumulators (when splits > 1 or raw)
+  int splits = 1;
+  int raw = 0;                  // 1: always write raw accumulators to part, even for splits == 1
+  int kernel = 0;               // 0 auto, 1 skinny, 2 mma.sync tiles, 3 tcgen05
+};
+int k_gemm_fp8(strictb200_ctx*, const GemmArgs& a);
+int sb_gemm_pick_splits(strictb200_ctx*, int64_t M, int64_t N, int64_t K);
+// gemm_f32.cu
+int k_gemm_f32(strictb200_ctx*, int64_t M, int64_t N, int64_t K, const float* x, const float* w, const float* bias, float* y,
+               int accumulate);
+// attention.cu
+int k_attn_prefill(strictb200_ctx*, const bf16* q, const bf16* kc, const bf16* vc, const int32_t* lens, const int32_t* past,
+                   const int32_t* qstart, int B, int S, int Hq, int Hkv, int D, int maxlen, float scale, bf16* out);
+size_t sb_attn_decode_scratch(int B, int Hq, int D, int nsplit);
+int sb_attn_decode_splits(strictb200_ctx*, int B, int Hkv, int maxlen);
+int k_attn_decode(strictb200_ctx*, const bf16* q, const bf16* kc, const bf16* vc, const int32_t* lens, int len_add, int B, int Hq,
+                  int Hkv, int D, int maxlen, float scale, int nsplit, float* scratch, bf16* out, uint8_t* q_out, float* qscale_out);
+int k_attn_f32(strictb200_ctx*, const float* qkv, float* kc, float* vc, const int32_t* seq, const int32_t* pos, const int32_t* lens,
+               int64_t T, int H, int D, int maxlen, float scale, float* out);
+// sampling.cu
+int k_embedding_bf16(strictb200_ctx*, const bf16* table, const int32_t* ids, int64_t T, int64_t d, int64_t vocab, bf16* out);
+int k_embedding_f32(strictb200_ctx*, const float* wte, const float* wpe, const int32_t* ids, const int32_t* pos, const int32_t* lens,
+                    int64_t T, int64_t d, int64_t vocab, int max_pos, float* out);
+int k_argmax(strictb200_ctx*, const float* x, int64_t M, int64_t N, int64_t ldx, int32_t* out, float* val_out);
+int k_gather_rows(strictb200_ctx*, const void* src, const int32_t* rows, int64_t n_rows, int64_t row_bytes, void* dst);
+int k_add_i32(strictb200_ctx*, int32_t* x, const int32_t* inc, int32_t c, int64_t n);
+int k_f32_to_bf16(strictb200_ctx*, const float* x, int64_t n, bf16* y);
+int k_bf16_to_f32(strictb200_ctx*, const bf16* x, int64_t n, float* y);
+// tp.cpp
+int sb_tp_allreduce_f32(strictb200_ctx*, float* buf, int64_t count);
+int sb_tp_allgather(strictb200_ctx*, const void* send, void* recv, int64_t bytes_per_rank);
+void sb_tp_destroy(strictb200_ctx*);
+
+// ------------------------------------------------------------------ device helpers
+#ifdef __CUDACC__
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide reductions over blockDim.x threads (multiple of 32, <= 1024). `red` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < nw ? red[l] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < nw ? red[l] : -INFINITY;
+  return warp_max(t);
+}
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) { return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+__device__ __forceinline__ float round_bf16(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+// E4M3 encode, round-to-nearest-even, saturating to +-448 (cvt.rn.satfinite.e4m3x2.f32).
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(r) : "f"(lo), "f"(hi));
+  return (uint32_t)r;
+}
+__device__ __forceinline__ uint32_t f32x4_to_e4m3x4(float a, float b, float c, float d) {
+  return f32x2_to_e4m3x2(a, b) | (f32x2_to_e4m3x2(c, d) << 16);
+}
+#endif

@@ -1,0 +1,310 @@
+// Row-wise kernels of the residual stream: per-token E4M3 quantisation, fused
+// (split-K reduce + dequant) + residual add + RMSNorm + quantise, LayerNorm, SwiGLU, GELU.
+// All are HBM/L2 streams: one block per token row, 128-bit loads, warp-shuffle reductions.
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROW_THREADS = 256;
+constexpr int MAX_CHUNKS = 8;  // 8 values per chunk per thread -> d <= 256*8*8 = 16384
+
+__device__ __forceinline__ void load8_bf16(const bf16* p, float* v) {
+  uint4 u = *(const uint4*)p;
+  uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void store8_bf16(bf16* p, const float* v) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) w[i] = f32_to_bf16_bits(v[2 * i]) | (f32_to_bf16_bits(v[2 * i + 1]) << 16);
+  *(uint4*)p = make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ void store8_e4m3(uint8_t* p, const float* v, float inv) {
+  uint32_t lo = f32x4_to_e4m3x4(__fmul_rn(v[0], inv), __fmul_rn(v[1], inv), __fmul_rn(v[2], inv), __fmul_rn(v[3], inv));
+  uint32_t hi = f32x4_to_e4m3x4(__fmul_rn(v[4], inv), __fmul_rn(v[5], inv), __fmul_rn(v[6], inv), __fmul_rn(v[7], inv));
+  *(uint2*)p = make_uint2(lo, hi);
+}
+
+// bf16 [M,K] (row stride ldx) -> E4M3 [M,K] + scale[M]
+__global__ void __launch_bounds__(ROW_THREADS) quantize_rows_kernel(const bf16* __restrict__ x, int64_t K, int64_t ldx,
+                                                                    uint8_t* __restrict__ q, float* __restrict__ scale) {
+  __shared__ float red[32];
+  int64_t row = blockIdx.x;
+  const bf16* xr = x + row * ldx;
+  float amax = 0.f;
+  for (int64_t k = (int64_t)threadIdx.x * 8; k < K; k += ROW_THREADS * 8) {
+    float v[8];
+    load8_bf16(xr + k, v);
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+  }
+  amax = block_max(amax, red);
+  float inv = 1.0f, sc = 1.0f;
+  if (amax > 0.f) { inv = __fdiv_rn(448.0f, amax); sc = __fdiv_rn(amax, 448.0f); }
+  if (threadIdx.x == 0) scale[row] = sc;
+  for (int64_t k = (int64_t)threadIdx.x * 8; k < K; k += ROW_THREADS * 8) {
+    float v[8];
+    load8_bf16(xr + k, v);
+    store8_e4m3(q + row * K + k, v, inv);
+  }
+}
+
+__global__ void __launch_bounds__(ROW_THREADS) quantize_rows_f32_kernel(const float* __restrict__ x, int64_t K, uint8_t* __restrict__ q,
+                                                                        float* __restrict__ scale) {
+  __shared__ float red[32];
+  int64_t row = blockIdx.x;
+  const float* xr = x + row * K;
+  float amax = 0.f;
+  for (int64_t k = threadIdx.x; k < K; k += ROW_THREADS) amax = fmaxf(amax, fabsf(xr[k]));
+  amax = block_max(amax, red);
+  float inv = 1.0f, sc = 1.0f;
+  if (amax > 0.f) { inv = __fdiv_rn(448.0f, amax); sc = __fdiv_rn(amax, 448.0f); }
+  if (threadIdx.x == 0) scale[row] = sc;
+  for (int64_t k = (int64_t)threadIdx.x * 2; k < K; k += ROW_THREADS * 2) {
+    uint32_t e = f32x2_to_e4m3x2(__fmul_rn(xr[k], inv), __fmul_rn(xr[k + 1], inv));
+    *(uint16_t*)(q + row * K + k) = (uint16_t)e;
+  }
+}
+
+struct RowNormDev {
+  const float* x_f32;
+  const bf16* x_in;
+  const float* part;
+  int groups, splits;
+  const float* sx;
+  const float* sw;
+  bf16* residual;
+  const float* gain;
+  float eps;
+  bf16* y;
+  uint8_t* q;
+  float* qscale;
+  bf16* y_raw;
+};
+
+__global__ void __launch_bounds__(ROW_THREADS) rownorm_kernel(RowNormDev a, int64_t M, int64_t d) {
+  __shared__ float red[32];
+  int64_t row = blockIdx.x;
+  float v[MAX_CHUNKS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < MAX_CHUNKS; c++) {
+    int64_t k = ((int64_t)c * ROW_THREADS + threadIdx.x) * 8;
+    if (k < d) {
+      float* t = v[c];
+      if (a.part) {
+        float tot[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) tot[i] = 0.f;
+        float4 w0 = *(const float4*)(a.sw + k), w1 = *(const float4*)(a.sw + k + 4);
+        float sw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        for (int g = 0; g < a.groups; g++) {
+          float acc[8];
+#pragma unroll
+          for (int i = 0; i < 8; i++) acc[i] = 0.f;
+          for (int s = 0; s < a.splits; s++) {
+            const float* p = a.part + (((int64_t)(g * a.splits + s) * M + row) * d + k);
+            float4 p0 = *(const float4*)p, p1 = *(const float4*)(p + 4);
+            acc[0] += p0.x; acc[1] += p0.y; acc[2] += p0.z; acc[3] += p0.w;
+            acc[4] += p1.x; acc[5] += p1.y; acc[6] += p1.z; acc[7] += p1.w;
+          }
+          float sxr = a.sx[(int64_t)g * M + row];
+#pragma unroll
+          for (int i = 0; i < 8; i++) tot[i] += __fmul_rn(__fmul_rn(acc[i], sxr), sw[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) t[i] = round_bf16(tot[i]);
+      } else if (a.x_f32) {
+        float4 p0 = *(const float4*)(a.x_f32 + row * d + k), p1 = *(const float4*)(a.x_f32 + row * d + k + 4);
+        t[0] = round_bf16(p0.x); t[1] = round_bf16(p0.y); t[2] = round_bf16(p0.z); t[3] = round_bf16(p0.w);
+        t[4] = round_bf16(p1.x); t[5] = round_bf16(p1.y); t[6] = round_bf16(p1.z); t[7] = round_bf16(p1.w);
+      } else {
+        load8_bf16(a.x_in + row * d + k, t);
+      }
+      if (a.y_raw) store8_bf16(a.y_raw + row * d + k, t);
+      if (a.residual) {
+        float r[8];
+        load8_bf16(a.residual + row * d + k, r);
+#pragma unroll
+        for (int i = 0; i < 8; i++) t[i] = round_bf16(__fadd_rn(r[i], t[i]));
+        store8_bf16(a.residual + row * d + k, t);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; i++) ss += t[i] * t[i];
+    }
+  }
+  if (!a.gain) return;
+  ss = block_sum(ss, red);
+  float ms = __fdiv_rn(ss, (float)d);
+  float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, a.eps)));
+  float amax = 0.f;
+#pragma unroll
+  for (int c = 0; c < MAX_CHUNKS; c++) {
+    int64_t k = ((int64_t)c * ROW_THREADS + threadIdx.x) * 8;
+    if (k < d) {
+      float4 g0 = *(const float4*)(a.gain + k), g1 = *(const float4*)(a.gain + k + 4);
+      float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        v[c][i] = __fmul_rn(__fmul_rn(v[c][i], r), g[i]);
+        amax = fmaxf(amax, fabsf(v[c][i]));
+      }
+      if (a.y) store8_bf16(a.y + row * d + k, v[c]);
+    }
+  }
+  if (!a.q) return;
+  amax = block_max(amax, red);
+  float inv = 1.0f, sc = 1.0f;
+  if (amax > 0.f) { inv = __fdiv_rn(448.0f, amax); sc = __fdiv_rn(amax, 448.0f); }
+  if (threadIdx.x == 0) a.qscale[row] = sc;
+#pragma unroll
+  for (int c = 0; c < MAX_CHUNKS; c++) {
+    int64_t k = ((int64_t)c * ROW_THREADS + threadIdx.x) * 8;
+    if (k < d) store8_e4m3(a.q + row * d + k, v[c], inv);
+  }
+}
+
+__global__ void __launch_bounds__(ROW_THREADS) layernorm_kernel(const float* __restrict__ x, const float* __restrict__ g,
+                                                                const float* __restrict__ b, float eps, int64_t d, float* __restrict__ y) {
+  __shared__ float red[32];
+  int64_t row = blockIdx.x;
+  const float* xr = x + row * d;
+  float s = 0.f;
+  for (int64_t k = threadIdx.x; k < d; k += ROW_THREADS) s += xr[k];
+  float mean = __fdiv_rn(block_sum(s, red), (float)d);
+  float vs = 0.f;
+  for (int64_t k = threadIdx.x; k < d; k += ROW_THREADS) { float t = xr[k] - mean; vs += t * t; }
+  float var = __fdiv_rn(block_sum(vs, red), (float)d);
+  float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+  for (int64_t k = threadIdx.x; k < d; k += ROW_THREADS)
+    y[row * d + k] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(xr[k], mean), r), g[k]), b[k]);
+}
+
+__global__ void add_f32_kernel(float* __restrict__ x, const float* __restrict__ y, int64_t n) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] = __fadd_rn(x[i], y[i]);
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+}
+
+// gate_up [M, 2I] bf16 -> h = bf16(silu(gate)*up); optional E4M3 quantisation of h per row.
+__global__ void __launch_bounds__(ROW_THREADS) swiglu_kernel(const bf16* __restrict__ gu, int64_t I, bf16* __restrict__ y,
+                                                             uint8_t* __restrict__ q, float* __restrict__ qscale) {
+  __shared__ float red[32];
+  int64_t row = blockIdx.x;
+  const bf16* gr = gu + row * 2 * I;
+  float amax = 0.f;
+  for (int64_t k = (int64_t)threadIdx.x * 8; k < I; k += ROW_THREADS * 8) {
+    float g[8], u[8], h[8];
+    load8_bf16(gr + k, g);
+    load8_bf16(gr + I + k, u);
+#pragma unroll
+    for (int i = 0; i < 8; i++) { h[i] = round_bf16(silu_mul(g[i], u[i])); amax = fmaxf(amax, fabsf(h[i])); }
+    if (y) store8_bf16(y + row * I + k, h);
+  }
+  if (!q) return;
+  amax = block_max(amax, red);
+  float inv = 1.0f, sc = 1.0f;
+  if (amax > 0.f) { inv = __fdiv_rn(448.0f, amax); sc = __fdiv_rn(amax, 448.0f); }
+  if (threadIdx.x == 0) qscale[row] = sc;
+  for (int64_t k = (int64_t)threadIdx.x * 8; k < I; k += ROW_THREADS * 8) {
+    float g[8], u[8], h[8];
+    load8_bf16(gr + k, g);
+    load8_bf16(gr + I + k, u);
+#pragma unroll
+    for (int i = 0; i < 8; i++) h[i] = round_bf16(silu_mul(g[i], u[i]));
+    store8_e4m3(q + row * I + k, h, inv);
+  }
+}
+
+__global__ void gelu_tanh_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ y) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float v = x[i];
+    float u = __fmul_rn(0.797884583f, __fadd_rn(v, __fmul_rn(0.044715f, __fmul_rn(__fmul_rn(v, v), v))));
+    y[i] = __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanhf(u)));
+  }
+}
+
+int stream_grid(strictb200_ctx* ctx, int64_t n, int threads) {
+  int64_t b = (n + threads - 1) / threads, cap = (int64_t)ctx->sm_count * 8;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+
+int k_quantize_rows(strictb200_ctx* ctx, const bf16* x, int64_t M, int64_t K, int64_t ldx, uint8_t* q, float* scale) {
+  if (K % 8 || ldx % 8) return sb_fail(STRICTB200_ERR_INVALID_ARG, "quantize_rows: K and the row stride must be multiples of 8");
+  quantize_rows_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(x, K, ldx, q, scale);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}
+int k_quantize_rows_f32(strictb200_ctx* ctx, const float* x, int64_t M, int64_t K, uint8_t* q, float* scale) {
+  if (K % 2) return sb_fail(STRICTB200_ERR_INVALID_ARG, "quantize_rows_f32: K must be even");
+  quantize_rows_f32_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(x, K, q, scale);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}
+int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
+  if (d % 8 || d > (int64_t)ROW_THREADS * 8 * MAX_CHUNKS)
+    return sb_fail(STRICTB200_ERR_INVALID_ARG, "rownorm: d must be a multiple of 8 and at most 16384");
+  RowNormDev v{a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual, a.gain, a.eps, a.y, a.q, a.qscale, a.y_raw};
+  rownorm_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(v, M, d);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}
+int k_layernorm(strictb200_ctx* ctx, const float* x, const float* g, const float* b, float eps, int64_t M, int64_t d, float* y) {
+  layernorm_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(x, g, b, eps, d, y);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}
+int k_add_f32(strictb200_ctx* ctx, float* x, const float* y, int64_t n) {
+  add_f32_kernel<<<stream_grid(ctx, n, 256), 256, 0, ctx->stream>>>(x, y, n);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}
+int k_swiglu(strictb200_ctx* ctx, const bf16* gate_up, int64_t M, int64_t I, bf16* y, uint8_t* q, float* qscale) {
+  if (I % 8) return sb_fail(STRICTB200_ERR_INVALID_ARG, "swiglu: I must be a multiple of 8");
+  swiglu_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(gate_up, I, y, q, qscale);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}
+int k_gelu_tanh(strictb200_ctx* ctx, const float* x, int64_t n, float* y) {
+  gelu_tanh_kernel<<<stream_grid(ctx, n, 256), 256, 0, ctx->stream>>>(x, n, y);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}
+
+// out[m,n] = (sum_s part[s][m,n]) * sx[m] * sw[n]  (fp32; the input of a cross-rank all-reduce)
+namespace {
+__global__ void reduce_scale_kernel(const float* __restrict__ part, int splits, const float* __restrict__ sx, const float* __restrict__ sw,
+                                    int64_t M, int64_t N, float* __restrict__ out) {
+  int64_t total = M * N / 4, stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    int64_t m = (i * 4) / N, n = (i * 4) - m * N;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; s++) {
+      float4 p = *(const float4*)(part + ((int64_t)s * M + m) * N + n);
+      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    float a = sx[m];
+    float4 w = *(const float4*)(sw + n);
+    float4 r;
+    r.x = __fmul_rn(__fmul_rn(acc.x, a), w.x); r.y = __fmul_rn(__fmul_rn(acc.y, a), w.y);
+    r.z = __fmul_rn(__fmul_rn(acc.z, a), w.z); r.w = __fmul_rn(__fmul_rn(acc.w, a), w.w);
+    *(float4*)(out + m * N + n) = r;
+  }
+}
+}  // namespace
+int k_reduce_scale(strictb200_ctx* ctx, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N, float* out) {
+  if (N % 4) return sb_fail(STRICTB200_ERR_INVALID_ARG, "reduce_scale: N must be a multiple of 4");
+  reduce_scale_kernel<<<stream_grid(ctx, M * N / 4, 256), 256, 0, ctx->stream>>>(part, splits, sx, sw, M, N, out);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}

@@ -1,0 +1,128 @@
+// Per-head RMS norm of q and k, rotary embedding, and append of k/v to the cache, fused with
+// the dequantising reduction of the qkv GEMM's split-K partials. One block per token row, one
+// warp per head: a lane owns 4 of the 128 dims, the rotary partner (i, i+64) lives in lane^16.
+#include <cmath>
+#include <vector>
+
+#include "common.cuh"
+
+namespace {
+
+struct RopeDev {
+  const bf16* qkv;
+  const float* part;
+  int splits;
+  const float* sx;
+  const float* sw;
+  const int32_t* seq;
+  const int32_t* pos;
+  const int32_t* lens;
+  const float* cos_t;
+  const float* sin_t;
+  const float* qgain;
+  const float* kgain;
+  float eps;
+  int Hq, Hkv, maxlen, max_pos;
+  bf16* q_out;
+  bf16* kcache;
+  bf16* vcache;
+};
+
+__global__ void __launch_bounds__(256) rope_kernel(RopeDev a, int64_t T) {
+  constexpr int D = 128;
+  int64_t t = blockIdx.x;
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  int b = a.seq ? a.seq[t] : (int)t;
+  int p = a.pos ? a.pos[t] : a.lens[b];
+  if (p < 0 || p >= a.maxlen || p >= a.max_pos) return;  // host validates; never index outside the cache
+  int nheads = a.Hq + 2 * a.Hkv;
+  int64_t nqkv = (int64_t)nheads * D;
+  for (int h = warp; h < nheads; h += nwarps) {
+    int64_t col = (int64_t)h * D + lane * 4;
+    float x[4];
+    if (a.part) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < a.splits; s++) {
+        float4 v = *(const float4*)(a.part + ((int64_t)s * T + t) * nqkv + col);
+        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+      }
+      float sxr = a.sx[t];
+      float4 w = *(const float4*)(a.sw + col);
+      x[0] = round_bf16(__fmul_rn(__fmul_rn(acc[0], sxr), w.x));
+      x[1] = round_bf16(__fmul_rn(__fmul_rn(acc[1], sxr), w.y));
+      x[2] = round_bf16(__fmul_rn(__fmul_rn(acc[2], sxr), w.z));
+      x[3] = round_bf16(__fmul_rn(__fmul_rn(acc[3], sxr), w.w));
+    } else {
+      uint2 u = *(const uint2*)(a.qkv + t * nqkv + col);
+      x[0] = __uint_as_float(u.x << 16); x[1] = __uint_as_float(u.x & 0xFFFF0000u);
+      x[2] = __uint_as_float(u.y << 16); x[3] = __uint_as_float(u.y & 0xFFFF0000u);
+    }
+    bool is_v = h >= a.Hq + a.Hkv;
+    float o[4];
+    if (!is_v) {
+      const float* g = h < a.Hq ? a.qgain : a.kgain;
+      float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+      float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)D), a.eps)));
+      float4 gv = *(const float4*)(g + lane * 4);
+      float n[4] = {__fmul_rn(__fmul_rn(x[0], r), gv.x), __fmul_rn(__fmul_rn(x[1], r), gv.y), __fmul_rn(__fmul_rn(x[2], r), gv.z),
+                    __fmul_rn(__fmul_rn(x[3], r), gv.w)};
+      int i0 = (lane & 15) * 4;
+      float4 c = *(const float4*)(a.cos_t + (int64_t)p * (D / 2) + i0);
+      float4 s = *(const float4*)(a.sin_t + (int64_t)p * (D / 2) + i0);
+      float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float other = __shfl_xor_sync(0xffffffffu, n[j], 16);
+        // first half: n_i*c - n_{i+64}*s ; second half: n_{i+64}*c + n_i*s
+        o[j] = lane < 16 ? __fsub_rn(__fmul_rn(n[j], cs[j]), __fmul_rn(other, sn[j]))
+                         : __fadd_rn(__fmul_rn(n[j], cs[j]), __fmul_rn(other, sn[j]));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; j++) o[j] = x[j];
+    }
+    uint2 w;
+    w.x = f32_to_bf16_bits(o[0]) | (f32_to_bf16_bits(o[1]) << 16);
+    w.y = f32_to_bf16_bits(o[2]) | (f32_to_bf16_bits(o[3]) << 16);
+    if (h < a.Hq) {
+      *(uint2*)(a.q_out + (t * a.Hq + h) * D + lane * 4) = w;
+    } else {
+      int hk = is_v ? h - a.Hq - a.Hkv : h - a.Hq;
+      bf16* cache = is_v ? a.vcache : a.kcache;
+      *(uint2*)(cache + (((int64_t)b * a.Hkv + hk) * a.maxlen + p) * D + lane * 4) = w;
+    }
+  }
+}
+
+}  // namespace
+
+int k_rope_qknorm_kvappend(strictb200_ctx* ctx, const RopeArgs& a, int64_t T) {
+  if (a.D != 128) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "rope: head_dim must be 128");
+  RopeDev v{a.qkv, a.part, a.splits, a.sx, a.sw, a.seq, a.pos, a.lens, a.cos_t, a.sin_t, a.qgain, a.kgain,
+            a.eps, a.Hq, a.Hkv, a.maxlen, a.max_pos, a.q_out, a.kcache, a.vcache};
+  rope_kernel<<<(unsigned)T, 256, 0, ctx->stream>>>(v, T);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}
+
+// cos/sin of pos * theta^(-2i/D), evaluated in double on the host and rounded to fp32: part of
+// the model constants (like the weights), not of the per-token path.
+int sb_rope_table(strictb200_ctx* ctx, int max_pos, int D, float theta, float** d_cos, float** d_sin) {
+  int h = D / 2;
+  std::vector<float> c((size_t)max_pos * h), s((size_t)max_pos * h);
+  std::vector<double> inv(h);
+  for (int i = 0; i < h; i++) inv[i] = std::pow((double)theta, -2.0 * (double)i / (double)D);
+  for (int p = 0; p < max_pos; p++)
+    for (int i = 0; i < h; i++) {
+      double ang = (double)p * inv[i];
+      c[(size_t)p * h + i] = (float)std::cos(ang);
+      s[(size_t)p * h + i] = (float)std::sin(ang);
+    }
+  size_t bytes = c.size() * sizeof(float);
+  SB_CUDA(cudaMalloc((void**)d_cos, bytes));
+  SB_CUDA(cudaMalloc((void**)d_sin, bytes));
+  SB_CUDA(cudaMemcpyAsync(*d_cos, c.data(), bytes, cudaMemcpyHostToDevice, ctx->stream));
+  SB_CUDA(cudaMemcpyAsync(*d_sin, s.data(), bytes, cudaMemcpyHostToDevice, ctx->stream));
+  SB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return STRICTB200_OK;
+}
