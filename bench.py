@@ -1,0 +1,285 @@
+"""Headline benchmark: Qwen3-8B-architecture FP8 greedy decode, batch 32, context 2048, tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One process per GPU (torchrun for N > 1, tensor-parallel over NCCL). A step is one decode step
+of all 32 sequences. `value` is timed on the device with the token ids resident in HBM
+(CUDA-graph replay of the step); `e2e` goes through the public decode_step call with host ids
+in and host ids out every step. The workload streams ~17.8 GB per step, far beyond the 126 MB
+L2, so no flush is needed between steps. Weights, prompts and the reference arm's tensors are
+synthetic (seeded generator), random-initialised, of the architecture's exact shapes.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCH, PROMPT, NEW_TOKENS = 32, 2048, 256
+SEED = 5
+METRIC = "qwen3_8b_fp8_decode_tokens_per_s"
+WORKLOAD = "qwen3-8b fp8 greedy decode, batch 32, prompt 2048 (BASELINE.json configs[4])"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device, self.proc, self.lines = device, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------- CPU arm
+def cpu_reference(steps, warmup):
+    """The reference has no implementation of this path; its stand-in is this repository's CPU
+    oracle (kind "port"). Bounded sample of one decode step at batch 32: the four E4M3 linears
+    of ONE layer + decode attention of one layer at context 2048 + the LM head are timed on all
+    host threads; a full step is 36 identical layers + the head."""
+    from oracle import oracle as O
+    import strict_b200 as sb
+    O.build()
+    cfg = sb.CONFIGS["qwen3-8b"]
+    d, D, Hq, Hkv, I, V, Ln = cfg["d_model"], cfg["head_dim"], cfg["n_q_heads"], cfg["n_kv_heads"], cfg["d_ff"], cfg["vocab"], cfg["n_layers"]
+    nq, nkv = Hq * D, Hkv * D
+    shapes = {"qkv": (nq + 2 * nkv, d), "o": (d, nq), "gate_up": (2 * I, d), "down": (d, I)}
+    W = {k: O.gen_qlinear(SEED, 100 + i, n, kk) for i, (k, (n, kk)) in enumerate(shapes.items())}
+    head = O.gen_qlinear(SEED, 3, V, d)
+    rng = np.random.default_rng(0)
+    acts = {k: O.round_bf16(rng.standard_normal((BATCH, kk)).astype(np.float32)) for k, (n, kk) in shapes.items()}
+    q = rng.standard_normal((BATCH, Hq, D)).astype(np.float32)
+    kc = rng.standard_normal((BATCH, Hkv, PROMPT, D)).astype(np.float32)
+    vc = rng.standard_normal((BATCH, Hkv, PROMPT, D)).astype(np.float32)
+    lens = np.full(BATCH, PROMPT, np.int32)
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        for k in shapes:
+            O.linear_fp8w(acts[k], W[k][0], W[k][1])
+        O.attn_decode(q, kc, vc, lens, 1.0 / np.sqrt(D))
+        t1 = time.perf_counter()
+        O.linear_fp8w(acts["qkv"], head[0], head[1])
+        t2 = time.perf_counter()
+        if it >= warmup:
+            times.append((t1 - t0) * Ln + (t2 - t1))
+    step_s = float(np.mean(times))
+    return {"value": BATCH / step_s, "unit": "tokens/s", "cores": O.num_threads(), "kind": "port",
+            "sample": f"per step: one layer's 4 linears + decode attention (ctx {PROMPT}) + LM head at batch {BATCH}, timed on "
+                      f"{O.num_threads()} threads; full step = {Ln} x layer + head; {steps} steps after {warmup} warm-up"}, step_s
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    base, step_s = cpu_reference(max(1, args.steps), max(0, args.warmup))
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 x fp8_e4m3 -> f32", "data": "synthetic", "config": {"workload": WORKLOAD, "timing": "host wall clock"},
+            "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------- GPU arm
+def run_ours(args, rank, world, local_rank):
+    import strict_b200 as sb
+    from strict_b200 import native as N
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if dist:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if not dist:
+            return x
+        import torch
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ctx = sb.Context(local_rank)
+    if world > 1:
+        import torch
+        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            h = np.zeros(128, np.uint8)
+            N.check(N.lib().strictb200_tp_unique_id(N.ptr(h)))
+            uid.copy_(torch.from_numpy(h))
+        dist.broadcast(uid, 0)
+        ctx.tp_init(world, rank, N.ptr(np.ascontiguousarray(uid.cpu().numpy())))
+    cfg = sb.CONFIGS["qwen3-8b"]
+    model = sb.Model(ctx, cfg).init_random(SEED)
+    total_steps = 2 * (max(args.warmup, 3) + args.steps) + 16
+    kv = model.new_cache(BATCH, PROMPT + total_steps + 8)
+    # prompts: 32 x 2048 uniform ids from the seeded generator; real prefill fills the cache
+    toks = np.empty((BATCH, PROMPT), np.int32)
+    d_tok = sb.DeviceVariable(ctx, BATCH * PROMPT, np.int32)
+    N.check(N.lib().strictb200_gen_tokens(ctx.h, SEED + 1, 1, BATCH * PROMPT, cfg["vocab"], d_tok.p))
+    toks[:] = d_tok.to_host().reshape(BATCH, PROMPT)
+    d_tok.free()
+    t0 = time.perf_counter()
+    first, _ = kv.prefill(toks)
+    ctx.synchronize()
+    prefill_s = time.perf_counter() - t0
+
+    # ---- value: device-resident ids, graph replay
+    ids_dev = first.copy()
+    kv.decode_step(ids_dev)  # plain-launch step (one-time set-up), leaves next ids on the device
+    kv.decode_steps_device(max(args.warmup, 3))  # includes the graph capture
+    ctx.synchronize()
+    bytes_step = kv.decode_bytes()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = ctx.launch_count()
+    ctx.synchronize()
+    barrier()
+    ctx.timer_begin()
+    kv.decode_steps_device(args.steps)
+    ms = ctx.timer_end()
+    barrier()
+    launches = ctx.launch_count() - launches0
+    ms = max_over_ranks(ms)
+    clocks = sampler.stop() if rank == 0 else None
+    value = BATCH * args.steps / (ms / 1e3)
+
+    # ---- e2e: host ids in, host ids out, every step, through the public decode_step call
+    h_in = np.zeros(BATCH, np.int32)
+    h_out = np.zeros(BATCH, np.int32)
+    nxt, _ = kv.decode_step(first)
+    for _ in range(max(args.warmup, 3)):
+        nxt, _ = kv.decode_step(nxt)
+    ctx.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    h_in[:] = nxt
+    for _ in range(args.steps):
+        kv.decode_step(h_in, out=h_out)
+        h_in[:] = h_out
+    ctx.synchronize()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    e2e = {"value": BATCH * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": BATCH * 4, "d2h_bytes_per_step": BATCH * 4,
+           "ms_per_step": e2e_s / args.steps * 1e3}
+
+    # ---- per-kernel-class device times of the same step (plain launches, CUDA events on the launch stream)
+    prof = kv.profile_decode(4)
+    lens_now = kv.lens()
+    Hkv_l, D, Ln = cfg["n_kv_heads"] // world, cfg["head_dim"], cfg["n_layers"]
+    d, I_l, nq_l = cfg["d_model"], cfg["d_ff"] // world, cfg["n_q_heads"] // world * D
+    alg = {  # algorithmic bytes per call of each class (weights or KV streamed once)
+        "gemm_qkv": (nq_l + 2 * Hkv_l * D) * d, "gemm_o": d * nq_l, "gemm_gate_up": 2 * I_l * d, "gemm_down": d * I_l,
+        "head": cfg["vocab"] // world * d, "attn_decode": int(lens_now.sum()) * Hkv_l * D * 2 * 2,
+    }
+    hbm, peak_kind = peaks()
+    kernels = {}
+    for k, (tot, calls) in prof.items():
+        if calls:
+            e = {"ms_per_call": tot / calls, "calls_per_step": calls / 4, "share": None}
+            if k in alg:
+                e["gbs"] = alg[k] / (tot / calls * 1e-3) / 1e9
+                e["frac"] = e["gbs"] / hbm
+            kernels[k] = e
+    tot_ms = sum(v[0] for v in prof.values())
+    for k in kernels:
+        kernels[k]["share"] = prof[k][0] / tot_ms
+    dom = max((k for k in kernels if k in alg), key=lambda k: prof[k][0])
+    roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gbs"], "peak": hbm, "unit": "GB/s", "frac": kernels[dom]["frac"],
+                "traffic": None, "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": alg[dom],
+                "step": {"algorithmic_bytes": bytes_step, "achieved": bytes_step / (ms / args.steps * 1e-3) / 1e9,
+                         "frac": bytes_step / (ms / args.steps * 1e-3) / 1e9 / hbm}}
+    if rank != 0:
+        return
+    base, _ = cpu_reference(2, 1) if world == 1 else (None, None)
+    line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 x fp8_e4m3 -> f32 (activations as two E4M3 terms on the FP8 tensor cores; bf16 KV)", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batch": BATCH, "context": int(lens_now.mean()), "parallelism": f"tp{world}",
+                       "l2": "inputs larger than L2 (17.8 GB streamed per step)", "prefill_s": prefill_s, "cuda_graph": True},
+            "roofline": roofline, "kernels": kernels, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks}
+    if base:
+        line["cpu_baseline"] = base
+    print(json.dumps(line), flush=True)
+    kv.dispose()
+    model.dispose()
+    ctx.dispose()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if args.gpus > 1 and world == 1:
+            # convenience: relaunch under torchrun when started as plain python with --gpus N
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1",
+                   "--master-port", os.environ.get("MASTER_PORT", "29517"), os.path.abspath(__file__)] + sys.argv[1:]
+            sys.exit(subprocess.call(cmd))
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -95,15 +95,21 @@ int strictb200_gen_tokens(strictb200_ctx* ctx, uint64_t seed, uint64_t tensor, i
 int strictb200_gen_weight_e4m3(strictb200_ctx* ctx, uint64_t seed, uint64_t tensor, int64_t row0, int64_t rows, int64_t K,
                                int64_t col0, int64_t cols, float std, uint8_t* d_q, float* d_scale);
 
-/* ---- quantisation and GEMM (no reference counterpart; new surface) ---- */
-/* Per-row absmax quantisation of bf16 [M,K] to E4M3 + fp32 scale[M] (scale = absmax/448). */
-int strictb200_quantize_rows(strictb200_ctx* ctx, const uint16_t* d_x_bf16, int64_t M, int64_t K, uint8_t* d_q, float* d_scale);
-/* Y[M,N] = ((Xq[M,K] . Wq[N,K]^T) * sx[M]) * sw[N], E4M3 x E4M3 -> fp32 -> out.
- * out_dtype: 0 bf16, 1 fp32. K % 64 == 0 (K % 128 == 0 for the tensor-memory kernels), N % 16 == 0.
- * kernel: 0 auto, 1 skinny stream (M <= 64), 2 mma.sync tiles, 3 tcgen05/TMEM tiles. */
-int strictb200_gemm_fp8(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const uint8_t* d_xq, const float* d_sx,
+/* ---- activation split and GEMM (no reference counterpart; new surface) ----
+ * A linear layer is y = (x . W^T) * sw with bf16 x, E4M3 W and one fp32 scale per output
+ * channel. To feed the FP8 tensor cores without dequantising weights in the kernel, a bf16 row
+ * is carried as two E4M3 terms with a power-of-two scale, x = s*(hi + lo/16), which is exact
+ * for every element at or above absmax/14336. The split buffer holds tokens in groups of 8:
+ * group g occupies rows [16g,16g+16) of width K, 8 hi rows then 8 lo rows, so it has
+ * 16*ceil(M/8) rows in total. */
+int strictb200_quantize_rows(strictb200_ctx* ctx, const uint16_t* d_x_bf16, int64_t M, int64_t K, uint8_t* d_split, float* d_scale);
+/* Y[M,N] = ((X . Wq[N,K]^T) * sx[M]) * sw[N] with X given as the split of M rows (above);
+ * fp32 accumulation. out_dtype: 0 bf16, 1 fp32. K % 64 == 0 (K % 128 == 0 for the
+ * tensor-memory kernel), N % 16 == 0.
+ * kernel: 0 auto, 1 skinny stream (M <= 32), 2 mma.sync tiles, 3 tcgen05/TMEM tiles. */
+int strictb200_gemm_fp8(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const uint8_t* d_split, const float* d_sx,
                         const uint8_t* d_wq, const float* d_sw, void* d_out, int out_dtype, int kernel);
-/* bf16 activations in, quantised per token inside; bf16 out. Uses context scratch. */
+/* bf16 activations in (split inside, using context scratch); bf16 out. */
 int strictb200_gemm_fp8w(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const uint16_t* d_x_bf16, const uint8_t* d_wq,
                          const float* d_sw, uint16_t* d_y_bf16, int kernel);
 /* fp32 Y[M,N] = X[M,K] . W[N,K]^T + bias[N] (bias may be NULL). */
@@ -195,6 +201,25 @@ int strictb200_decode_steps_device(strictb200_model* m, strictb200_kv* kv, int32
 int strictb200_kv_device_ids(strictb200_kv* kv, int32_t** d_ids_out);
 /* 1 = capture the decode step in a CUDA graph and replay it (default), 0 = plain launches. */
 int strictb200_model_set_graph(strictb200_model* m, int enabled);
+/* Kernel classes of the Qwen3 decode step, for strictb200_profile_decode. */
+enum strictb200_kernel_class {
+  STRICTB200_K_EMBED = 0,     /* embedding gather, length update */
+  STRICTB200_K_GEMM_QKV = 1,
+  STRICTB200_K_ROPE = 2,      /* split-K reduce + QK-norm + RoPE + cache append */
+  STRICTB200_K_ATTN = 3,      /* split-KV attention + combine + quantise */
+  STRICTB200_K_GEMM_O = 4,
+  STRICTB200_K_ROWNORM = 5,   /* split-K reduce + residual + RMSNorm + quantise */
+  STRICTB200_K_GEMM_GU = 6,
+  STRICTB200_K_SWIGLU = 7,
+  STRICTB200_K_GEMM_DOWN = 8,
+  STRICTB200_K_HEAD = 9,      /* LM head GEMM + argmax */
+  STRICTB200_K_ALLREDUCE = 10,
+  STRICTB200_K_COUNT = 11
+};
+/* Runs n_steps greedy decode steps as plain launches with a pair of CUDA events around every
+ * call, and returns the summed device milliseconds and the number of calls per kernel class
+ * (arrays of at least STRICTB200_K_COUNT entries). Advances the cache like decode does. */
+int strictb200_profile_decode(strictb200_model* m, strictb200_kv* kv, int n_steps, float* h_ms, uint64_t* h_calls, int n_classes);
 /* Algorithmic bytes one decode step reads at the cache's current lengths (weights + KV). */
 int strictb200_decode_bytes(strictb200_model* m, strictb200_kv* kv, uint64_t* out);
 

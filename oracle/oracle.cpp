@@ -12,15 +12,18 @@
 // known answers of Strict.Compiler.Cuda.Tests/CSharpToCudaTranspilerTests.cs:46-57.
 //
 // Numerics contract of the FP8 (Qwen3) path, which the device kernels also follow:
-//  * hidden states, q/k/v, attention output and MLP activations are bf16 between ops;
-//  * every linear layer takes its input quantised per token to E4M3 with the scale
-//    absmax/448 (q = e4m3(x * (448/absmax)); an all-zero row uses scale 1), weights are
-//    E4M3 with one fp32 scale per output channel; products are summed exactly (double
-//    here, fp32 tensor-core accumulators on the device) and y = (acc*s_x)*s_w;
-//  * under tensor parallelism the rows entering o_proj and down_proj are quantised per
-//    token *per rank slice* and the per-rank fp32 partial results are summed in rank order;
-//  * RMSNorm: r = 1/sqrt(mean(x^2)+eps); y = (x*r)*g in fp32; a norm that feeds a linear
-//    layer is quantised from those fp32 values without a bf16 rounding in between;
+//  * the residual stream is fp32 (a linear layer's fp32 result is added to it unrounded); norm
+//    outputs, q/k/v, attention output and MLP activations are bf16 between ops;
+//  * a linear layer computes y = (sum_k x_k * w_k) * s_w with bf16 inputs x, E4M3 weights w and
+//    one fp32 scale per output channel: every product is exact, the sum is fp32 or better, the
+//    output is rounded to bf16 (logits stay fp32). So that the FP8 tensor cores can take the
+//    activations directly, a bf16 row is carried as TWO E4M3 terms with a power-of-two scale,
+//    x = s * (hi + lo/16): s = 2^e is the smallest power of two with absmax/s <= 448,
+//    hi = e4m3(x/s), lo = e4m3(16*(x/s - hi)). The split is exact for every element at or above
+//    absmax/14336 (|x/s| >= 2^-6) and deterministic below; this file applies the same split
+//    (or_split_rows);
+//  * tensor parallelism changes only the order of the fp32 sums, so it has no oracle mode;
+//  * RMSNorm: r = 1/sqrt(mean(x^2)+eps); y = bf16((x*r)*g), statistics in fp32 or better;
 //  * RoPE pairs (i, i+D/2), angle = pos * theta^(-2i/D), cos/sin evaluated in double and
 //    rounded to fp32; q/k are RMS-normalised per head first; results rounded to bf16;
 //  * softmax in fp32 or better, scale 1/sqrt(D) applied to the fp32 score;
@@ -55,25 +58,41 @@ struct LutInit {
 
 // ---------------------------------------------------------------- primitives
 
-// Per-row absmax quantisation of fp32 values to E4M3. scale = absmax/448.
-void quant_rows(const float* x, int64_t M, int64_t K, int64_t ldx, uint8_t* q, float* scale) {
+// Power-of-two row scale: the smallest 2^e with absmax/2^e <= 448 (e = 0 for an all-zero row).
+int scale_exponent(float amax) {
+  if (!(amax >= 7.888609e-31f)) return 0;  // below 2^-100: treated as zero
+  uint32_t b = f_bits(amax);
+  int E = (int)((b >> 23) & 255) - 126;    // amax = f * 2^E, f in [0.5, 1)
+  return (b & 0x7FFFFFu) <= 0x600000u ? E - 9 : E - 8;  // f <= 0.875 = 448 / 2^9
+}
+
+// Two-term E4M3 split of bf16-valued rows: x = s*(hi + lo/16). Writes hi/lo code bytes (may be
+// null) and the dequantised value hi + lo/16 (may be null).
+void split_rows(const float* x, int64_t M, int64_t K, int64_t ldx, uint8_t* hi, uint8_t* lo, float* eff, float* scale) {
 #pragma omp parallel for schedule(static)
   for (int64_t m = 0; m < M; m++) {
     const float* r = x + m * ldx;
     float amax = 0.f;
     for (int64_t k = 0; k < K; k++) amax = std::max(amax, std::fabs(r[k]));
-    float inv = 1.0f, s = 1.0f;
-    if (amax > 0.f) { inv = 448.0f / amax; s = amax / 448.0f; }
-    for (int64_t k = 0; k < K; k++) q[m * K + k] = f32_to_e4m3(r[k] * inv);
-    scale[m] = s;
+    int e = scale_exponent(amax);
+    float inv = std::ldexp(1.0f, -e);
+    scale[m] = std::ldexp(1.0f, e);
+    for (int64_t k = 0; k < K; k++) {
+      float v = r[k] * inv;
+      uint8_t h = f32_to_e4m3(v);
+      float hv = E4M3_LUT[h];
+      uint8_t l = f32_to_e4m3(16.0f * (v - hv));
+      if (hi) hi[m * K + k] = h;
+      if (lo) lo[m * K + k] = l;
+      if (eff) eff[m * K + k] = hv + 0.0625f * E4M3_LUT[l];
+    }
   }
 }
 
-// out[m,n] (+)= (float(sum_k a[m,k]*w[n,k]) * sa[m]) * sw[n]; products exact, sum in double.
-void gemm_q(const uint8_t* aq, const float* sa, const uint8_t* wq, int64_t ldw, const float* sw,
-            int64_t M, int64_t N, int64_t K, float* out, int64_t ldo, bool accumulate) {
-  std::vector<float> af((size_t)M * K);
-  for (int64_t i = 0; i < M * K; i++) af[i] = E4M3_LUT[aq[i]];
+// out[m,n] = (float(sum_k a[m,k]*w[n,k]) * sa[m]) * sw[n]; a = dequantised split activations
+// (exact in fp32), w = E4M3 codes; products exact, sum in double.
+void gemm_q(const float* af, const float* sa, const uint8_t* wq, int64_t ldw, const float* sw,
+            int64_t M, int64_t N, int64_t K, float* out, int64_t ldo) {
 #pragma omp parallel
   {
     std::vector<float> wf(K);
@@ -82,15 +101,14 @@ void gemm_q(const uint8_t* aq, const float* sa, const uint8_t* wq, int64_t ldw, 
       const uint8_t* wr = wq + n * ldw;
       for (int64_t k = 0; k < K; k++) wf[k] = E4M3_LUT[wr[k]];
       for (int64_t m = 0; m < M; m++) {
-        const float* a = af.data() + m * K;
+        const float* a = af + m * K;
         double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         int64_t k = 0;
         for (; k + 8 <= K; k += 8)
-          for (int j = 0; j < 8; j++) acc[j] += (double)(a[k + j] * wf[k + j]);
-        for (; k < K; k++) acc[0] += (double)(a[k] * wf[k]);
+          for (int j = 0; j < 8; j++) acc[j] += (double)a[k + j] * (double)wf[k + j];
+        for (; k < K; k++) acc[0] += (double)a[k] * (double)wf[k];
         double t = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
-        float y = ((float)t * sa[m]) * sw[n];
-        if (accumulate) out[m * ldo + n] += y; else out[m * ldo + n] = y;
+        out[m * ldo + n] = ((float)t * sa[m]) * sw[n];
       }
     }
   }
@@ -205,7 +223,6 @@ struct Layer {
 
 struct Model {
   Config c;
-  int tp;
   std::vector<Layer> L;
   std::vector<float> embed;  // Qwen: bf16 values held as fp32; GPT-2: fp32  [V,d]
   std::vector<float> wpe;    // GPT-2 [max_pos,d]
@@ -250,17 +267,30 @@ enum { T_NORM1 = 0, T_Q = 1, T_K = 2, T_V = 3, T_QN = 4, T_KN = 5, T_O = 6, T_NO
 enum { G_EMBED = 1, G_WPE = 2, G_HEAD = 3, G_NORMF = 4 };
 uint64_t layer_tensor(int l, int kind) { return 16ull * (uint64_t)(l + 1) + (uint64_t)kind; }
 
+// Per-row absmax quantisation of a weight matrix given as fp32 values (the tied LM head).
+void quant_weight_rows(const float* x, int64_t M, int64_t K, uint8_t* q, float* scale) {
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; m++) {
+    const float* r = x + m * K;
+    float amax = 0.f;
+    for (int64_t k = 0; k < K; k++) amax = std::max(amax, std::fabs(r[k]));
+    float inv = 1.0f, sc = 1.0f;
+    if (amax > 0.f) { inv = 448.0f / amax; sc = amax / 448.0f; }
+    for (int64_t k = 0; k < K; k++) q[m * K + k] = f32_to_e4m3(r[k] * inv);
+    scale[m] = sc;
+  }
+}
 void quant_head_from_embed(Model* m) {
   const Config& c = m->c;
   m->head.N = c.vocab; m->head.K = c.d_model;
   m->head.q.resize((size_t)c.vocab * c.d_model);
   m->head.s.resize(c.vocab);
-  quant_rows(m->embed.data(), c.vocab, c.d_model, c.d_model, m->head.q.data(), m->head.s.data());
+  quant_weight_rows(m->embed.data(), c.vocab, c.d_model, m->head.q.data(), m->head.s.data());
 }
 
-Model* model_create(const Config& c, uint64_t seed, int tp) {
+Model* model_create(const Config& c, uint64_t seed) {
   Model* m = new Model;
-  m->c = c; m->tp = tp;
+  m->c = c;
   const float SD = 0.02f;
   int64_t d = c.d_model, D = c.head_dim, I = c.d_ff;
   int64_t nq = (int64_t)c.n_q_heads * D, nkv = (int64_t)c.n_kv_heads * D;
@@ -315,16 +345,11 @@ Model* model_create(const Config& c, uint64_t seed, int tp) {
   return m;
 }
 
-// Linear layer on fp32 rows x[T, K] (row stride K): quantise per token (per rank slice of
-// K when `split` > 1), multiply, sum the per-slice fp32 partials in slice order.
-void qlinear(const QLinear& w, const float* x, int64_t T, int split, float* out) {
-  int64_t K = w.K, N = w.N, Ks = K / split;
-  std::vector<uint8_t> aq((size_t)T * Ks);
-  std::vector<float> sa(T);
-  for (int g = 0; g < split; g++) {
-    quant_rows(x + g * Ks, T, Ks, K, aq.data(), sa.data());
-    gemm_q(aq.data(), sa.data(), w.q.data() + g * Ks, K, w.s.data(), T, N, Ks, out, N, g > 0);
-  }
+// Linear layer on bf16-valued rows x[T, K]: exact products with the E4M3 weights.
+void qlinear(const QLinear& w, const float* x, int64_t T, float* out) {
+  std::vector<float> eff((size_t)T * w.K), sa(T);
+  split_rows(x, T, w.K, w.K, nullptr, nullptr, eff.data(), sa.data());
+  gemm_q(eff.data(), sa.data(), w.q.data(), w.K, w.s.data(), T, w.N, w.K, out, w.N);
 }
 
 float* kv_at(std::vector<float>& buf, const Model* m, const State* st, int l, int b, int h) {
@@ -359,11 +384,11 @@ void forward(Model* m, State* st, const int* tokens, const int* n_new, int B, in
     // --- attention block
 #pragma omp parallel for
     for (int64_t t = 0; t < T; t++) {
-      if (qw) rmsnorm_row(&x[t * d], ly.norm1_g.data(), d, c.eps, &a[t * d]);
+      if (qw) { rmsnorm_row(&x[t * d], ly.norm1_g.data(), d, c.eps, &a[t * d]); for (int64_t i = 0; i < d; i++) a[t * d + i] = round_bf16(a[t * d + i]); }
       else layernorm_row(&x[t * d], ly.norm1_g.data(), ly.norm1_b.data(), d, c.eps, &a[t * d]);
     }
     if (qw) {
-      qlinear(ly.wqkv, a.data(), T, 1, qkv.data());
+      qlinear(ly.wqkv, a.data(), T, qkv.data());
       for (auto& v : qkv) v = round_bf16(v);
     } else gemm_f32(a.data(), ly.fqkv.w.data(), ly.fqkv.b.data(), T, nqkv, d, qkv.data());
     // q/k post-processing + cache append
@@ -398,8 +423,8 @@ void forward(Model* m, State* st, const int* tokens, const int* n_new, int B, in
       }
     }
     if (qw) {
-      qlinear(ly.wo, att.data(), T, m->tp, y.data());
-      for (int64_t i = 0; i < T * d; i++) x[i] = round_bf16(x[i] + round_bf16(y[i]));
+      qlinear(ly.wo, att.data(), T, y.data());
+      for (int64_t i = 0; i < T * d; i++) x[i] = x[i] + y[i];
     } else {
       gemm_f32(att.data(), ly.fo.w.data(), ly.fo.b.data(), T, d, nq, y.data());
       for (int64_t i = 0; i < T * d; i++) x[i] = x[i] + y[i];
@@ -407,18 +432,18 @@ void forward(Model* m, State* st, const int* tokens, const int* n_new, int B, in
     // --- MLP block
 #pragma omp parallel for
     for (int64_t t = 0; t < T; t++) {
-      if (qw) rmsnorm_row(&x[t * d], ly.norm2_g.data(), d, c.eps, &a[t * d]);
+      if (qw) { rmsnorm_row(&x[t * d], ly.norm2_g.data(), d, c.eps, &a[t * d]); for (int64_t i = 0; i < d; i++) a[t * d + i] = round_bf16(a[t * d + i]); }
       else layernorm_row(&x[t * d], ly.norm2_g.data(), ly.norm2_b.data(), d, c.eps, &a[t * d]);
     }
     if (qw) {
       gu.resize((size_t)T * 2 * I);
-      qlinear(ly.wgu, a.data(), T, 1, gu.data());
+      qlinear(ly.wgu, a.data(), T, gu.data());
 #pragma omp parallel for
       for (int64_t t = 0; t < T; t++)
         for (int64_t i = 0; i < I; i++)
           hact[t * I + i] = round_bf16(silu_mul(round_bf16(gu[t * 2 * I + i]), round_bf16(gu[t * 2 * I + I + i])));
-      qlinear(ly.wdown, hact.data(), T, m->tp, y.data());
-      for (int64_t i = 0; i < T * d; i++) x[i] = round_bf16(x[i] + round_bf16(y[i]));
+      qlinear(ly.wdown, hact.data(), T, y.data());
+      for (int64_t i = 0; i < T * d; i++) x[i] = x[i] + y[i];
     } else {
       gu.resize((size_t)T * I);
       gemm_f32(a.data(), ly.ffc.w.data(), ly.ffc.b.data(), T, I, d, gu.data());
@@ -434,7 +459,7 @@ void forward(Model* m, State* st, const int* tokens, const int* n_new, int B, in
     for (int b = 0; b < B; b++) {
       if (n_new[b] > 0) {
         const float* src = &x[(t + n_new[b] - 1) * d];
-        if (qw) rmsnorm_row(src, m->normf_g.data(), d, c.eps, &last[b * d]);
+        if (qw) { rmsnorm_row(src, m->normf_g.data(), d, c.eps, &last[b * d]); for (int64_t i = 0; i < d; i++) last[b * d + i] = round_bf16(last[b * d + i]); }
         else layernorm_row(src, m->normf_g.data(), m->normf_b.data(), d, c.eps, &last[b * d]);
       }
       t += n_new[b];
@@ -442,7 +467,7 @@ void forward(Model* m, State* st, const int* tokens, const int* n_new, int B, in
     }
   }
   if (logits) {
-    if (qw) qlinear(m->head, last.data(), B, 1, logits);
+    if (qw) qlinear(m->head, last.data(), B, logits);
     else gemm_f32(last.data(), m->embed.data(), nullptr, B, c.vocab, d, logits);
   }
 }
@@ -556,9 +581,16 @@ int or_ew_program(const int32_t* code, int n_instr, const float* const* arrays, 
 }
 
 // ---- primitives (fp32 buffers hold the values; callers round to bf16 where the contract says)
-void or_quant_rows(const float* x, int64_t M, int64_t K, uint8_t* q, float* scale) { quant_rows(x, M, K, K, q, scale); }
-void or_gemm_fp8(const uint8_t* aq, const float* sa, const uint8_t* wq, const float* sw, int64_t M,
-                 int64_t N, int64_t K, float* out) { gemm_q(aq, sa, wq, K, sw, M, N, K, out, N, false); }
+void or_split_rows(const float* x, int64_t M, int64_t K, uint8_t* hi, uint8_t* lo, float* eff, float* scale) {
+  split_rows(x, M, K, K, hi, lo, eff, scale);
+}
+void or_quant_weight_rows(const float* x, int64_t M, int64_t K, uint8_t* q, float* scale) { quant_weight_rows(x, M, K, q, scale); }
+// y = (x . W^T) * sw for bf16-valued x [M,K] and E4M3 W [N,K]; fp32 result (unrounded)
+void or_linear_fp8w(const float* x, const uint8_t* wq, const float* sw, int64_t M, int64_t N, int64_t K, float* out) {
+  std::vector<float> eff((size_t)M * K), sa(M);
+  split_rows(x, M, K, K, nullptr, nullptr, eff.data(), sa.data());
+  gemm_q(eff.data(), sa.data(), wq, K, sw, M, N, K, out, N);
+}
 void or_gemm_f32(const float* x, const float* w, const float* b, int64_t M, int64_t N, int64_t K, float* out) { gemm_f32(x, w, b, M, N, K, out); }
 void or_rmsnorm(const float* x, const float* g, int64_t M, int64_t d, float eps, float* y) {
 #pragma omp parallel for
@@ -628,12 +660,12 @@ void or_argmax(const float* x, int64_t M, int64_t N, int32_t* out) {
 }
 
 // ---- model
-void* or_model_create(const int32_t* icfg, float eps, float rope_theta, uint64_t seed, int tp) {
+void* or_model_create(const int32_t* icfg, float eps, float rope_theta, uint64_t seed) {
   Config c;
   c.arch = icfg[0]; c.n_layers = icfg[1]; c.d_model = icfg[2]; c.n_q_heads = icfg[3];
   c.n_kv_heads = icfg[4]; c.head_dim = icfg[5]; c.d_ff = icfg[6]; c.vocab = icfg[7];
   c.max_pos = icfg[8]; c.tied = icfg[9]; c.eps = eps; c.rope_theta = rope_theta;
-  return model_create(c, seed, tp);
+  return model_create(c, seed);
 }
 void or_model_free(void* m) { delete (Model*)m; }
 // Returns a pointer into the model's storage (fp32 or E4M3 bytes); the caller may read or

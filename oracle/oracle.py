@@ -34,7 +34,7 @@ def lib():
         L.or_stream_key.restype = C.c_uint64
         L.or_stream_key.argtypes = [C.c_uint64, C.c_uint64]
         L.or_model_create.restype = C.c_void_p
-        L.or_model_create.argtypes = [C.c_void_p, C.c_float, C.c_float, C.c_uint64, C.c_int]
+        L.or_model_create.argtypes = [C.c_void_p, C.c_float, C.c_float, C.c_uint64]
         L.or_model_free.argtypes = [C.c_void_p]
         L.or_model_tensor.restype = C.c_int64
         L.or_model_tensor.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p]
@@ -131,21 +131,47 @@ def ew_program(code, arrays, scalars, consts, n):
 
 
 # ------------------------------------------------------------------ primitives
-def quant_rows(x):
+def split_rows(x):
+    """Two-term E4M3 split of bf16-valued rows: returns (hi codes, lo codes, hi+lo/16 as fp32, scale)."""
+    x = _f32(x)
+    M, K = x.shape
+    hi = np.empty((M, K), np.uint8)
+    lo = np.empty((M, K), np.uint8)
+    eff = np.empty((M, K), np.float32)
+    s = np.empty(M, np.float32)
+    lib().or_split_rows(_p(x), C.c_int64(M), C.c_int64(K), _p(hi), _p(lo), _p(eff), _p(s))
+    return hi, lo, eff, s
+
+
+def split_rows_device_layout(x):
+    """The split in the row order the device kernels use: tokens in groups of 8, each group as
+    8 hi rows followed by 8 lo rows; rows of padding tokens are zero."""
+    hi, lo, _, s = split_rows(x)
+    M, K = hi.shape
+    G = (M + 7) // 8
+    out = np.zeros((G * 16, K), np.uint8)
+    for m in range(M):
+        out[16 * (m // 8) + m % 8] = hi[m]
+        out[16 * (m // 8) + 8 + m % 8] = lo[m]
+    return out, s
+
+
+def quant_weight_rows(x):
     x = _f32(x)
     M, K = x.shape
     q = np.empty((M, K), np.uint8)
     s = np.empty(M, np.float32)
-    lib().or_quant_rows(_p(x), C.c_int64(M), C.c_int64(K), _p(q), _p(s))
+    lib().or_quant_weight_rows(_p(x), C.c_int64(M), C.c_int64(K), _p(q), _p(s))
     return q, s
 
 
-def gemm_fp8(aq, sa, wq, sw):
-    M, K = aq.shape
+def linear_fp8w(x, wq, sw):
+    """(x . W^T) * sw with bf16-valued x and E4M3 weights; fp32, unrounded."""
+    x = _f32(x)
+    M, K = x.shape
     N = wq.shape[0]
     out = np.empty((M, N), np.float32)
-    lib().or_gemm_fp8(_p(np.ascontiguousarray(aq)), _p(_f32(sa)), _p(np.ascontiguousarray(wq)), _p(_f32(sw)),
-                      C.c_int64(M), C.c_int64(N), C.c_int64(K), _p(out))
+    lib().or_linear_fp8w(_p(x), _p(np.ascontiguousarray(wq)), _p(_f32(sw)), C.c_int64(M), C.c_int64(N), C.c_int64(K), _p(out))
     return out
 
 
@@ -239,11 +265,11 @@ class Model:
     """CPU restatement of a GPT-2 / Qwen3 stack. cfg keys: arch, n_layers, d_model, n_q_heads,
     n_kv_heads, head_dim, d_ff, vocab, max_pos, tied, eps, rope_theta."""
 
-    def __init__(self, cfg, seed, tp=1):
+    def __init__(self, cfg, seed):
         self.cfg = dict(cfg)
         icfg = np.array([cfg["arch"], cfg["n_layers"], cfg["d_model"], cfg["n_q_heads"], cfg["n_kv_heads"],
                          cfg["head_dim"], cfg["d_ff"], cfg["vocab"], cfg["max_pos"], cfg["tied"]], np.int32)
-        self.h = lib().or_model_create(_p(icfg), C.c_float(cfg["eps"]), C.c_float(cfg["rope_theta"]), C.c_uint64(seed), C.c_int(tp))
+        self.h = lib().or_model_create(_p(icfg), C.c_float(cfg["eps"]), C.c_float(cfg["rope_theta"]), C.c_uint64(seed))
         self.states = []
 
     def tensor(self, name, dtype):

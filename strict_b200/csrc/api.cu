@@ -259,7 +259,7 @@ int strictb200_gemm_fp8w(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, c
   if (!M) return STRICTB200_OK;
   SB_REQUIRE(x && wq && sw && y, "null pointer");
   void* ws;
-  size_t qbytes = ((size_t)M * K + 255) & ~(size_t)255;
+  size_t qbytes = ((size_t)sb_qrows(M) * K + 255) & ~(size_t)255;
   SB_TRY(sb_ws(ctx, qbytes + (size_t)M * 4, &ws));
   uint8_t* xq = (uint8_t*)ws;
   float* sx = (float*)((char*)ws + qbytes);

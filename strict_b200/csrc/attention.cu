@@ -7,7 +7,7 @@
 //  * decode: split-KV. One block = one KV head of one sequence over one chunk of keys; the
 //    G = Hq/Hkv query heads that share the KV head are the rows of the MMA tile, so every
 //    K/V byte is read from HBM once. Each block writes (m, l, o) partials; a combine kernel
-//    merges the chunks and can emit the per-token E4M3 quantisation the next GEMM consumes.
+//    merges the chunks and can emit the two-term E4M3 split of the token row the next GEMM consumes.
 //
 // Shared-memory tiles hold rows of 128 bf16 (256 B = 16 chunks of 16 B); chunk c of row r
 // lives at chunk c ^ (r & 7), which makes every ldmatrix phase conflict-free.
@@ -41,6 +41,15 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
+}
+// The softmax weights enter the P.V product as two bf16 terms, p = hi + lo (16 mantissa bits):
+// a single bf16 P is off by up to 2^-9, which is enough to move the bf16-rounded attention
+// output by an ulp on a few percent of its elements, and the E4M3 quantisation that follows
+// turns each such ulp into a 6-12 % step. V is exact in bf16, so two MMAs recover the product.
+__device__ __forceinline__ void split_bf16(float a, float b, uint32_t& hi, uint32_t& lo) {
+  float ah = round_bf16(a), bh = round_bf16(b);
+  hi = pack_bf16(ah, bh);
+  lo = pack_bf16(a - ah, b - bh);
 }
 __device__ __forceinline__ uint32_t tile_off(int row, int chunk) { return (uint32_t)(row * 256 + ((chunk ^ (row & 7)) << 4)); }
 
@@ -151,15 +160,15 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const bf16* __restric
       m_run[r] = m_new;
     }
     float ls[2] = {0.f, 0.f};
-    uint32_t pf[4][4];
+    uint32_t pf[4][4], pl[4][4];  // P = hi + lo, two bf16 terms (see split_bf16)
 #pragma unroll
     for (int j = 0; j < 8; j++) {
       float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
       float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
       ls[0] += p0 + p1;
       ls[1] += p2 + p3;
-      pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
-      pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+      split_bf16(p0, p1, pf[j >> 1][(j & 1) * 2], pl[j >> 1][(j & 1) * 2]);
+      split_bf16(p2, p3, pf[j >> 1][(j & 1) * 2 + 1], pl[j >> 1][(j & 1) * 2 + 1]);
     }
 #pragma unroll
     for (int r = 0; r < 2; r++) l_run[r] = l_run[r] * corr[r] + ls[r];
@@ -176,6 +185,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const bf16* __restric
         ldsm_x4_t(tV + tile_off(kk * 16 + (mi & 1) * 8 + r8, 2 * jj + (mi >> 1)), vb);
         mma_bf16(o[2 * jj], pf[kk], vb[0], vb[1]);
         mma_bf16(o[2 * jj + 1], pf[kk], vb[2], vb[3]);
+        mma_bf16(o[2 * jj], pl[kk], vb[0], vb[1]);
+        mma_bf16(o[2 * jj + 1], pl[kk], vb[2], vb[3]);
       }
     }
     __syncthreads();
@@ -283,7 +294,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
       corr[r] = exp2f(m_run[r] - m_use[r]);
       m_run[r] = m_new;
     }
-    uint32_t pf[4];
+    uint32_t pf[4], pl[4];
     {
       float p[2][4];
 #pragma unroll
@@ -293,8 +304,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
       }
       l_run[0] = l_run[0] * corr[0] + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
       l_run[1] = l_run[1] * corr[1] + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
-      pf[0] = pack_bf16(p[0][0], p[0][1]); pf[1] = pack_bf16(p[0][2], p[0][3]);
-      pf[2] = pack_bf16(p[1][0], p[1][1]); pf[3] = pack_bf16(p[1][2], p[1][3]);
+      split_bf16(p[0][0], p[0][1], pf[0], pl[0]); split_bf16(p[0][2], p[0][3], pf[1], pl[1]);
+      split_bf16(p[1][0], p[1][1], pf[2], pl[2]); split_bf16(p[1][2], p[1][3], pf[3], pl[3]);
     }
 #pragma unroll
     for (int j = 0; j < 16; j++) {
@@ -307,6 +318,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
       ldsm_x4_t(tV + tile_off(warp * 16 + (mi & 1) * 8 + r8, 2 * jj + (mi >> 1)), vb);
       mma_bf16(o[2 * jj], pf, vb[0], vb[1]);
       mma_bf16(o[2 * jj + 1], pf, vb[2], vb[3]);
+      mma_bf16(o[2 * jj], pl, vb[0], vb[1]);
+      mma_bf16(o[2 * jj + 1], pl, vb[2], vb[3]);
     }
     __syncthreads();
   }
@@ -350,8 +363,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
   }
 }
 
-// grid B, 256 threads: merge the chunks of every head of one token; optional E4M3 quantisation
-// of the whole token row [Hq*128] (the o_proj input).
+// grid B, 256 threads: merge the chunks of every head of one token; optional two-term E4M3
+// split of the whole token row [Hq*128] (the o_proj input).
 __global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                                                            const int32_t* __restrict__ lens, int len_add, int Hq, int maxlen, int chunk,
                                                            int nsplit, bf16* __restrict__ out, uint8_t* __restrict__ q_out,
@@ -378,17 +391,17 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restri
   }
   if (!q_out) return;
   amax = block_max(amax, red);
-  float inv = 1.0f, sc = 1.0f;
-  if (amax > 0.f) { inv = __fdiv_rn(448.0f, amax); sc = __fdiv_rn(amax, 448.0f); }
-  if (threadIdx.x == 0) qscale[b] = sc;
+  int ex = sb_scale_exponent(amax);
+  float inv = sb_pow2(-ex);
+  if (threadIdx.x == 0) qscale[b] = sb_pow2(ex);
   __syncthreads();  // the row written above is re-read below by other threads of the block
-  for (int e = threadIdx.x * 4; e < Hq * D; e += 1024) {
-    const bf16* src = out + (int64_t)b * Hq * D + e;
-    uint2 u = *(const uint2*)src;
-    float v0 = __uint_as_float(u.x << 16), v1 = __uint_as_float(u.x & 0xFFFF0000u);
-    float v2 = __uint_as_float(u.y << 16), v3 = __uint_as_float(u.y & 0xFFFF0000u);
-    *(uint32_t*)(q_out + (int64_t)b * Hq * D + e) =
-        f32x4_to_e4m3x4(__fmul_rn(v0, inv), __fmul_rn(v1, inv), __fmul_rn(v2, inv), __fmul_rn(v3, inv));
+  for (int e = threadIdx.x * 8; e < Hq * D; e += 2048) {
+    uint4 u = *(const uint4*)(out + (int64_t)b * Hq * D + e);
+    uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 4; i++) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+    sb_store_split8(q_out, (int64_t)Hq * D, b, e, v, inv);
   }
 }
 

@@ -1,6 +1,7 @@
 // Internal declarations shared by the translation units of libstrictb200.so.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -9,7 +10,8 @@
 
 #include "../../include/strictb200.h"
 
-struct TpState;  // tp.cpp
+struct TpState;     // tp.cpp
+struct SbProfiler;  // model.cu
 
 struct strictb200_ctx {
   int device = 0;
@@ -24,6 +26,7 @@ struct strictb200_ctx {
   size_t flush_bytes = 0;
   int tp_world = 1, tp_rank = 0;
   TpState* tp = nullptr;
+  SbProfiler* prof = nullptr;
 };
 
 void sb_set_error(const std::string& msg);
@@ -74,27 +77,34 @@ int k_gen_weight_e4m3(strictb200_ctx*, uint64_t key, int64_t row0, int64_t rows,
                       float std_, uint8_t* q, int64_t ldq, float* scale);
 uint64_t sb_stream_key(uint64_t seed, uint64_t tensor);
 // norm.cu
-struct QuantOut { uint8_t* q; float* scale; };  // optional fused E4M3 output of a row-wise op
+// Activations enter the FP8 GEMMs as two E4M3 terms, x = s*(hi + lo/16) with s a power of two.
+// Row layout of the split buffer: tokens in groups of 8; group g occupies rows [16g, 16g+16):
+// 8 hi rows then 8 lo rows, so that the hi and lo accumulators of a token land in the same
+// thread (mma.sync n-tile pairs) / adjacent accumulator columns (tensor memory).
+inline int64_t sb_qrows(int64_t M) { return 16 * ((M + 7) / 8); }
 int k_quantize_rows(strictb200_ctx*, const bf16* x, int64_t M, int64_t K, int64_t ldx, uint8_t* q, float* scale);
-int k_quantize_rows_f32(strictb200_ctx*, const float* x, int64_t M, int64_t K, uint8_t* q, float* scale);
+// Single-term absmax/448 quantisation of weight rows (the tied LM head).
+int k_quantize_weight_rows(strictb200_ctx*, const bf16* x, int64_t M, int64_t K, int64_t ldx, uint8_t* q, float* scale);
 // Row op of the residual stream. For every token row:
-//   y_in  = part ? bf16(sum over groups g of (sum over splits s of part[g][s][row]) * sx[g][row] * sw[col]) : x_in
-//   resid = residual ? bf16(residual + y_in) (stored back) : y_in
-//   n     = (resid * r) * gain ; written as bf16 (y) and/or quantised E4M3 (q, scale)
+//   y_in  = part ? sum over groups g of (sum over splits s of part[g][s][row]) * sx[g][row] * sw[col]   (fp32)
+//         : x_f32 ? x_f32 : x_in (bf16)
+//   resid = residual_f32 ? residual_f32 + y_in (fp32, stored back)
+//         : residual ? bf16(residual + y_in) (stored back) : y_in
+//   n     = bf16((resid * r) * gain) ; written as bf16 (y) and/or as the two-term E4M3 split (q, qscale)
 struct RowNormArgs {
-  const float* x_f32 = nullptr;      // [M,d] fp32 input rounded to bf16 first (after an all-reduce)
+  const float* x_f32 = nullptr;      // [M,d] fp32 input (e.g. after an all-reduce)
   const bf16* x_in = nullptr;        // [M,d] (used when part and x_f32 are null)
   const float* part = nullptr;       // [groups][splits][M,d] fp32 raw accumulators
   int groups = 1, splits = 1;
   const float* sx = nullptr;         // [groups][M]
   const float* sw = nullptr;         // [d]
-  bf16* residual = nullptr;          // [M,d] in/out, may be null
-  const float* gain = nullptr;       // [d]
+  float* residual_f32 = nullptr;     // [M,d] fp32 residual stream, in/out, may be null
+  bf16* residual = nullptr;          // [M,d] bf16 residual, in/out, may be null
+  const float* gain = nullptr;       // [d]; null: only the residual update is done
   float eps = 1e-6f;
   bf16* y = nullptr;                 // [M,d] normalised bf16 output, may be null
-  uint8_t* q = nullptr;              // [M,d] quantised output, may be null
+  uint8_t* q = nullptr;              // split output [sb_qrows(M), d], may be null
   float* qscale = nullptr;           // [M]
-  bf16* y_raw = nullptr;             // [M,d] bf16(y_in) before the residual add, may be null
 };
 int k_rownorm(strictb200_ctx*, const RowNormArgs& a, int64_t M, int64_t d);
 int k_reduce_scale(strictb200_ctx*, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N, float* out);
@@ -127,7 +137,7 @@ int sb_rope_table(strictb200_ctx*, int max_pos, int D, float theta, float** d_co
 // gemm_fp8.cu
 struct GemmArgs {
   int64_t M = 0, N = 0, K = 0;
-  const uint8_t* xq = nullptr;  // [M,K], row stride ldx
+  const uint8_t* xq = nullptr;  // split activations [sb_qrows(M), K], row stride ldx
   int64_t ldx = 0;
   const float* sx = nullptr;    // [M]
   const uint8_t* wq = nullptr;  // [N,K], row stride ldw
@@ -156,6 +166,7 @@ int k_attn_f32(strictb200_ctx*, const float* qkv, float* kc, float* vc, const in
                int64_t T, int H, int D, int maxlen, float scale, float* out);
 // sampling.cu
 int k_embedding_bf16(strictb200_ctx*, const bf16* table, const int32_t* ids, int64_t T, int64_t d, int64_t vocab, bf16* out);
+int k_embedding_bf16_f32(strictb200_ctx*, const bf16* table, const int32_t* ids, int64_t T, int64_t d, int64_t vocab, float* out);
 int k_embedding_f32(strictb200_ctx*, const float* wte, const float* wpe, const int32_t* ids, const int32_t* pos, const int32_t* lens,
                     int64_t T, int64_t d, int64_t vocab, int max_pos, float* out);
 int k_argmax(strictb200_ctx*, const float* x, int64_t M, int64_t N, int64_t ldx, int32_t* out, float* val_out);
@@ -210,5 +221,42 @@ __device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
 }
 __device__ __forceinline__ uint32_t f32x4_to_e4m3x4(float a, float b, float c, float d) {
   return f32x2_to_e4m3x2(a, b) | (f32x2_to_e4m3x2(c, d) << 16);
+}
+// E4M3 pair -> two floats (exact; through f16x2).
+__device__ __forceinline__ float2 e4m3x2_to_f32x2(uint32_t pair) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)pair));
+  return __half22float2(*reinterpret_cast<__half2*>(&h2));
+}
+// Exponent e of the power-of-two row scale: the smallest 2^e with amax/2^e <= 448.
+__device__ __forceinline__ int sb_scale_exponent(float amax) {
+  if (!(amax >= 7.888609e-31f)) return 0;
+  uint32_t b = __float_as_uint(amax);
+  int E = (int)((b >> 23) & 255) - 126;
+  return (b & 0x7FFFFFu) <= 0x600000u ? E - 9 : E - 8;
+}
+__device__ __forceinline__ float sb_pow2(int e) { return __uint_as_float((uint32_t)(e + 127) << 23); }
+// Two-term split of 8 values already divided by the row scale: hi = e4m3(v), lo = e4m3(16*(v-hi)).
+__device__ __forceinline__ void sb_split8(const float* v, uint2* hi, uint2* lo) {
+  uint32_t h[4], l[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    h[i] = f32x2_to_e4m3x2(v[2 * i], v[2 * i + 1]);
+    float2 hv = e4m3x2_to_f32x2(h[i]);
+    l[i] = f32x2_to_e4m3x2(__fmul_rn(16.0f, __fsub_rn(v[2 * i], hv.x)), __fmul_rn(16.0f, __fsub_rn(v[2 * i + 1], hv.y)));
+  }
+  *hi = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+  *lo = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+}
+// Store the split of 8 consecutive columns of token row m into the split buffer q [*, K].
+__device__ __forceinline__ void sb_store_split8(uint8_t* q, int64_t K, int64_t m, int64_t k, const float* v, float inv) {
+  float t[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) t[i] = __fmul_rn(v[i], inv);
+  uint2 hi, lo;
+  sb_split8(t, &hi, &lo);
+  int64_t row = 16 * (m >> 3) + (m & 7);
+  *(uint2*)(q + row * K + k) = hi;
+  *(uint2*)(q + (row + 8) * K + k) = lo;
 }
 #endif

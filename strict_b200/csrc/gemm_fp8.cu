@@ -1,7 +1,11 @@
-// E4M3 x E4M3 GEMM, Y[M,N] = ((Xq . Wq^T) * sx[M]) * sw[N], fp32 accumulation.
+// bf16-activation x E4M3-weight GEMM on the FP8 tensor cores, Y[M,N] = ((X . Wq^T) * sx[M]) * sw[N],
+// fp32 accumulation. The bf16 activations arrive as two E4M3 terms, X = sx*(hi + lo/16) with sx
+// a power of two (norm.cu), laid out in groups of 8 hi rows + 8 lo rows: the MMA runs over
+// 2M operand rows and the epilogue adds acc_hi + acc_lo/16, so every product is exact and no
+// weight is ever dequantised in the kernel.
 //
 // Three kernels, chosen by shape:
-//  * skinny (M <= 64, decode): an HBM stream over the weights. Each warp owns 16 output
+//  * skinny (M <= 32, decode): an HBM stream over the weights. Each warp owns 16 output
 //    channels and walks K with 128-bit loads straight from global memory into mma.sync
 //    m16n8k32 A-fragments (weights are the A operand, tokens the B operand, so no row of
 //    the 16x32 tile is padding); the token block is staged once per K-chunk in shared memory.
@@ -41,7 +45,7 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
 struct GemmDev {
-  int M, N, K;
+  int M, Mq, N, K;  // Mq = 16*ceil(M/8) rows of the split activation buffer
   const uint8_t* xq;
   int64_t ldx;
   const float* sx;
@@ -60,7 +64,7 @@ constexpr int SK_WARPS = 8;
 constexpr int SK_ROWS = SK_WARPS * 16;  // output channels per block
 constexpr int SK_PF = 8;                // 64-byte units of weights in flight per thread
 
-template <int NT>  // NT tiles of 8 tokens
+template <int NT>  // NT tiles of 8 operand rows = NT*4 tokens (hi tile, lo tile alternating)
 __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(GemmDev a, int kc_max) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
@@ -93,7 +97,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(GemmDev a, i
     const int chunks_per_row = kc_len / 16;
     for (int c = threadIdx.x; c < MP * chunks_per_row; c += blockDim.x) {
       int r = c / chunks_per_row, cc = c - r * chunks_per_row;
-      bool valid = r < a.M;
+      bool valid = r < a.Mq;
       const uint8_t* src = a.xq + (int64_t)(valid ? r : 0) * a.ldx + k_begin + kc0 + 16 * cc;
       cp_async16(smem + r * stride + 16 * cc, src, valid);
     }
@@ -124,19 +128,21 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(GemmDev a, i
     u_base += kc_len / 64;
   }
   if (!rows_ok) return;
-  // epilogue. acc[j][0]: (channel n0+g, token 8j+2tig) [1]: token+1  [2],[3]: channel n0+g+8
+  // epilogue. Tile pair (2jp, 2jp+1) = hi and lo rows of tokens 8jp..8jp+7.
+  // acc[.][0]: (channel n0+g, token 8jp+2tig) [1]: token+1  [2],[3]: channel n0+g+8
   const bool raw = a.raw || a.splits > 1;
 #pragma unroll
-  for (int j = 0; j < NT; j++) {
+  for (int jp = 0; jp < NT / 2; jp++) {
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-      int tok = 8 * j + 2 * tig + (i & 1);
+      int tok = 8 * jp + 2 * tig + (i & 1);
       int n = n0 + g + ((i >> 1) << 3);
       if (tok < a.M) {
+        float v = __fadd_rn(acc[2 * jp][i], __fmul_rn(0.0625f, acc[2 * jp + 1][i]));
         if (raw) {
-          a.part[((int64_t)blockIdx.y * a.M + tok) * a.N + n] = acc[j][i];
+          a.part[((int64_t)blockIdx.y * a.M + tok) * a.N + n] = v;
         } else {
-          float y = __fmul_rn(__fmul_rn(acc[j][i], a.sx[tok]), a.sw[n]);
+          float y = __fmul_rn(__fmul_rn(v, a.sx[tok]), a.sw[n]);
           if (a.out_f32) ((float*)a.out)[(int64_t)tok * a.N + n] = y;
           else ((bf16*)a.out)[(int64_t)tok * a.N + n] = __float2bfloat16_rn(y);
         }
@@ -153,7 +159,7 @@ constexpr int TL_BN = 128, TL_BM = 128, TL_STAGES = 4;
 
 __global__ void __launch_bounds__(256) gemm_tiles_kernel(GemmDev a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  // stage layout: W tile [128 rows][64 B] then X tile [128 tokens][64 B]; consecutive rows are
+  // stage layout: W tile [128 rows][64 B] then X tile [128 operand rows = 64 tokens][64 B]; consecutive rows are
   // 64 B apart, so the two rows a quarter-warp reads form one conflict-free 128-byte line.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int wn = warp & 3, wm = warp >> 2;  // 4 warps along N (32 channels each), 2 along M (64 tokens each)
@@ -178,7 +184,7 @@ __global__ void __launch_bounds__(256) gemm_tiles_kernel(GemmDev a) {
       int r = c >> 2, cc = c & 3;
       bool vw = n0 + r < a.N;
       cp_async16(ws + r * 64 + cc * 16, a.wq + (int64_t)(vw ? n0 + r : 0) * a.ldw + k_begin + u * 64 + cc * 16, vw);
-      bool vx = m0 + r < a.M;
+      bool vx = m0 + r < a.Mq;
       cp_async16(xs + r * 64 + cc * 16, a.xq + (int64_t)(vx ? m0 + r : 0) * a.ldx + k_begin + u * 64 + cc * 16, vx);
     }
   };
@@ -215,16 +221,17 @@ __global__ void __launch_bounds__(256) gemm_tiles_kernel(GemmDev a) {
 #pragma unroll
   for (int mi = 0; mi < 2; mi++)
 #pragma unroll
-    for (int j = 0; j < 8; j++)
+    for (int jp = 0; jp < 4; jp++)
 #pragma unroll
       for (int i = 0; i < 4; i++) {
-        int tok = m0 + wm * 64 + 8 * j + 2 * tig + (i & 1);
+        int tok = ((m0 + wm * 64 + 16 * jp) >> 1) + 2 * tig + (i & 1);  // operand rows 16g.. hold tokens 8g..
         int n = n0 + wn * 32 + mi * 16 + g + ((i >> 1) << 3);
         if (tok < a.M && n < a.N) {
+          float v = __fadd_rn(acc[mi][2 * jp][i], __fmul_rn(0.0625f, acc[mi][2 * jp + 1][i]));
           if (raw) {
-            a.part[((int64_t)blockIdx.z * a.M + tok) * a.N + n] = acc[mi][j][i];
+            a.part[((int64_t)blockIdx.z * a.M + tok) * a.N + n] = v;
           } else {
-            float y = __fmul_rn(__fmul_rn(acc[mi][j][i], a.sx[tok]), a.sw[n]);
+            float y = __fmul_rn(__fmul_rn(v, a.sx[tok]), a.sw[n]);
             if (a.out_f32) ((float*)a.out)[(int64_t)tok * a.N + n] = y;
             else ((bf16*)a.out)[(int64_t)tok * a.N + n] = __float2bfloat16_rn(y);
           }
@@ -256,7 +263,7 @@ int launch_skinny(strictb200_ctx* ctx, const GemmDev& d) {
 
 // Number of K splits for a skinny GEMM so that the grid covers the SMs about twice.
 int sb_gemm_pick_splits(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K) {
-  if (M > 64) return 1;
+  if (M > 32) return 1;
   int64_t tiles = (N + SK_ROWS - 1) / SK_ROWS;
   int s = 1;
   while (tiles * s < (int64_t)ctx->sm_count * 3 / 2 && s < 16 && K % (2 * s * 64) == 0 && K / (2 * s) >= 512) s *= 2;
@@ -271,18 +278,17 @@ int k_gemm_fp8(strictb200_ctx* ctx, const GemmArgs& g) {
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: operands and row strides must be 16-byte aligned");
   if (g.M > INT32_MAX || g.N > INT32_MAX || g.K > INT32_MAX) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: dimension too large");
   int kernel = g.kernel;
-  if (kernel == 0) kernel = g.M <= 64 ? 1 : 3;
+  if (kernel == 0) kernel = g.M <= 32 ? 1 : 3;
   if (kernel == 3) {
     int st = k_gemm_fp8_tmem(ctx, g);
     if (st != STRICTB200_ERR_UNSUPPORTED || g.kernel == 3) return st;
     kernel = 2;  // shapes the tensor-memory kernel does not cover (K % 128 != 0)
   }
-  GemmDev d{(int)g.M, (int)g.N, (int)g.K, g.xq, g.ldx, g.sx, g.wq, g.ldw, g.sw, g.out, g.out_f32, g.part, g.splits, g.raw};
+  GemmDev d{(int)g.M, (int)sb_qrows(g.M), (int)g.N, (int)g.K, g.xq, g.ldx, g.sx, g.wq, g.ldw, g.sw, g.out, g.out_f32, g.part, g.splits, g.raw};
   if (kernel == 1) {
-    if (g.M > 64) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: the skinny kernel takes at most 64 rows");
-    if (g.M <= 8) return launch_skinny<1>(ctx, d);
-    if (g.M <= 16) return launch_skinny<2>(ctx, d);
-    if (g.M <= 32) return launch_skinny<4>(ctx, d);
+    if (g.M > 32) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: the skinny kernel takes at most 32 rows");
+    if (g.M <= 8) return launch_skinny<2>(ctx, d);
+    if (g.M <= 16) return launch_skinny<4>(ctx, d);
     return launch_skinny<8>(ctx, d);
   }
   static bool attr = false;
@@ -291,7 +297,7 @@ int k_gemm_fp8(strictb200_ctx* ctx, const GemmArgs& g) {
     SB_CUDA(cudaFuncSetAttribute(gemm_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr = true;
   }
-  dim3 grid((unsigned)((g.N + TL_BN - 1) / TL_BN), (unsigned)((g.M + TL_BM - 1) / TL_BM), g.splits);
+  dim3 grid((unsigned)((g.N + TL_BN - 1) / TL_BN), (unsigned)((d.Mq + TL_BM - 1) / TL_BM), g.splits);
   if (grid.y > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: M too large for the tile kernel");
   gemm_tiles_kernel<<<grid, 256, smem, ctx->stream>>>(d);
   SB_LAUNCHED(ctx);

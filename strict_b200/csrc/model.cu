@@ -115,7 +115,7 @@ int alloc_fw(strictb200_model* m, FW& w, int64_t N, int64_t K) {
 
 // ------------------------------------------------------------------ decode buffers
 struct DecBuf {
-  bf16* x;         // [B,d] residual stream
+  float* x;        // [B,d] fp32 residual stream
   uint8_t* aq;     // [B, max(d, Hq_l*D, I_l)] quantised GEMM input
   float* sa;       // [B]
   float* part;     // split-K partials, max over the layer's GEMMs
@@ -159,8 +159,8 @@ void carve_decode(strictb200_kv* kv, char* base, DecBuf* out, size_t* total) {
   if (c.arch == STRICTB200_QWEN3) {
     int64_t nq = (int64_t)m->Hq_l * D, nqkv = nq + 2 * (int64_t)m->Hkv_l * D;
     int64_t amax = std::max<int64_t>(d, std::max<int64_t>(nq, m->I_l));
-    b.x = cv.take<bf16>(B * d);
-    b.aq = cv.take<uint8_t>(B * amax);
+    b.x = cv.take<float>(B * d);
+    b.aq = cv.take<uint8_t>(sb_qrows(B) * amax);
     b.sa = cv.take<float>(B);
     size_t p1 = (size_t)plan_splits(m, B, nqkv, d) * B * nqkv;
     size_t p2 = (size_t)plan_splits(m, B, d, nq) * B * d;
@@ -254,6 +254,34 @@ bf16* kv_v(strictb200_kv* kv, int l) { return (bf16*)kv->v + (size_t)l * kv->lay
 float* kv_kf(strictb200_kv* kv, int l) { return (float*)kv->k + (size_t)l * kv->layer_stride; }
 float* kv_vf(strictb200_kv* kv, int l) { return (float*)kv->v + (size_t)l * kv->layer_stride; }
 
+// ------------------------------------------------------------------ per-class device timing
+// When ctx->prof is set, every call of the decode body is bracketed by a pair of CUDA events
+// tagged with its kernel class; strictb200_profile_decode sums them up afterwards.
+struct ProfSpan { int cls; cudaEvent_t a, b; };
+}  // namespace
+struct SbProfiler {
+  std::vector<ProfSpan> spans;
+  std::vector<cudaEvent_t> pool;
+  size_t used = 0;
+  cudaEvent_t get() {
+    if (used == pool.size()) { cudaEvent_t e; cudaEventCreate(&e); pool.push_back(e); }
+    return pool[used++];
+  }
+};
+namespace {
+template <typename F>
+int prof(strictb200_ctx* ctx, int cls, F&& f) {
+  SbProfiler* p = ctx->prof;
+  if (!p) return f();
+  ProfSpan sp{cls, p->get(), p->get()};
+  cudaEventRecord(sp.a, ctx->stream);
+  int st = f();
+  cudaEventRecord(sp.b, ctx->stream);
+  p->spans.push_back(sp);
+  return st;
+}
+#define PROF(cls, expr) SB_TRY(prof(ctx, cls, [&]() -> int { return (expr); }))
+
 // ------------------------------------------------------------------ Qwen3 decode step body
 // Everything below is enqueued on the stream with device-resident state only, so the whole
 // body can be captured into a CUDA graph.
@@ -264,65 +292,65 @@ int qwen_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
   const int64_t nq = (int64_t)m->Hq_l * D, nqkv = nq + 2 * (int64_t)m->Hkv_l * D;
   const float scale = 1.0f / sqrtf((float)D);
   const bool tp = m->world > 1;
-  SB_TRY(k_embedding_bf16(ctx, m->embed, kv->d_ids, B, d, c.vocab, b.x));
+  PROF(STRICTB200_K_EMBED, k_embedding_bf16_f32(ctx, m->embed, kv->d_ids, B, d, c.vocab, b.x));
   {
     RowNormArgs a;
-    a.x_in = b.x; a.gain = m->L[0].norm1_g; a.eps = c.eps; a.q = b.aq; a.qscale = b.sa;
-    SB_TRY(k_rownorm(ctx, a, B, d));
+    a.x_f32 = b.x; a.gain = m->L[0].norm1_g; a.eps = c.eps; a.q = b.aq; a.qscale = b.sa;
+    PROF(STRICTB200_K_ROWNORM, k_rownorm(ctx, a, B, d));
   }
   for (int l = 0; l < c.n_layers; l++) {
     LayerW& w = m->L[l];
     // qkv projection -> raw split-K partials, consumed by the rope kernel
     int s1 = plan_splits(m, B, nqkv, d);
-    SB_TRY(run_gemm(m, B, w.wqkv, b.aq, b.sa, nullptr, 0, b.part, s1, 1));
+    PROF(STRICTB200_K_GEMM_QKV, run_gemm(m, B, w.wqkv, b.aq, b.sa, nullptr, 0, b.part, s1, 1));
     {
       RopeArgs r;
       r.part = b.part; r.splits = s1; r.sx = b.sa; r.sw = w.wqkv.s; r.lens = kv->d_lens;
       r.cos_t = m->rope_cos; r.sin_t = m->rope_sin; r.qgain = w.qn_g; r.kgain = w.kn_g; r.eps = c.eps;
       r.Hq = m->Hq_l; r.Hkv = m->Hkv_l; r.D = (int)D; r.maxlen = kv->maxlen; r.max_pos = c.max_pos;
       r.q_out = b.qb; r.kcache = kv_k(kv, l); r.vcache = kv_v(kv, l);
-      SB_TRY(k_rope_qknorm_kvappend(ctx, r, B));
+      PROF(STRICTB200_K_ROPE, k_rope_qknorm_kvappend(ctx, r, B));
     }
     // split-KV attention over len+1 keys; the combine emits the quantised o_proj input
-    SB_TRY(k_attn_decode(ctx, b.qb, kv_k(kv, l), kv_v(kv, l), kv->d_lens, 1, (int)B, m->Hq_l, m->Hkv_l, (int)D, kv->maxlen, scale,
-                         kv->nsplit, b.attn_ws, b.att, b.aq, b.sa));
+    PROF(STRICTB200_K_ATTN, k_attn_decode(ctx, b.qb, kv_k(kv, l), kv_v(kv, l), kv->d_lens, 1, (int)B, m->Hq_l, m->Hkv_l, (int)D, kv->maxlen,
+                                          scale, kv->nsplit, b.attn_ws, b.att, b.aq, b.sa));
     // o_proj -> partials -> (all-reduce) -> residual + norm2 + quantise
     int s2 = plan_splits(m, B, d, nq);
-    SB_TRY(run_gemm(m, B, w.wo, b.aq, b.sa, nullptr, 0, b.part, s2, 1));
+    PROF(STRICTB200_K_GEMM_O, run_gemm(m, B, w.wo, b.aq, b.sa, nullptr, 0, b.part, s2, 1));
     {
       RowNormArgs a;
       if (tp) {
-        SB_TRY(k_reduce_scale(ctx, b.part, s2, b.sa, w.wo.s, B, d, b.red));
-        SB_TRY(sb_tp_allreduce_f32(ctx, b.red, B * d));
+        PROF(STRICTB200_K_ROWNORM, k_reduce_scale(ctx, b.part, s2, b.sa, w.wo.s, B, d, b.red));
+        PROF(STRICTB200_K_ALLREDUCE, sb_tp_allreduce_f32(ctx, b.red, B * d));
         a.x_f32 = b.red;
       } else {
         a.part = b.part; a.splits = s2; a.sx = b.sa; a.sw = w.wo.s;
       }
-      a.residual = b.x; a.gain = w.norm2_g; a.eps = c.eps; a.q = b.aq; a.qscale = b.sa;
-      SB_TRY(k_rownorm(ctx, a, B, d));
+      a.residual_f32 = b.x; a.gain = w.norm2_g; a.eps = c.eps; a.q = b.aq; a.qscale = b.sa;
+      PROF(STRICTB200_K_ROWNORM, k_rownorm(ctx, a, B, d));
     }
     // gate/up -> bf16, SwiGLU + quantise, down -> partials -> residual + next norm + quantise
-    SB_TRY(run_gemm(m, B, w.wgu, b.aq, b.sa, b.gu, 0, nullptr, 1, 0));
-    SB_TRY(k_swiglu(ctx, b.gu, B, m->I_l, nullptr, b.aq, b.sa));
+    PROF(STRICTB200_K_GEMM_GU, run_gemm(m, B, w.wgu, b.aq, b.sa, b.gu, 0, nullptr, 1, 0));
+    PROF(STRICTB200_K_SWIGLU, k_swiglu(ctx, b.gu, B, m->I_l, nullptr, b.aq, b.sa));
     int s4 = plan_splits(m, B, d, m->I_l);
-    SB_TRY(run_gemm(m, B, w.wdown, b.aq, b.sa, nullptr, 0, b.part, s4, 1));
+    PROF(STRICTB200_K_GEMM_DOWN, run_gemm(m, B, w.wdown, b.aq, b.sa, nullptr, 0, b.part, s4, 1));
     {
       RowNormArgs a;
       if (tp) {
-        SB_TRY(k_reduce_scale(ctx, b.part, s4, b.sa, w.wdown.s, B, d, b.red));
-        SB_TRY(sb_tp_allreduce_f32(ctx, b.red, B * d));
+        PROF(STRICTB200_K_ROWNORM, k_reduce_scale(ctx, b.part, s4, b.sa, w.wdown.s, B, d, b.red));
+        PROF(STRICTB200_K_ALLREDUCE, sb_tp_allreduce_f32(ctx, b.red, B * d));
         a.x_f32 = b.red;
       } else {
         a.part = b.part; a.splits = s4; a.sx = b.sa; a.sw = w.wdown.s;
       }
-      a.residual = b.x;
+      a.residual_f32 = b.x;
       a.gain = l + 1 < c.n_layers ? m->L[l + 1].norm1_g : m->normf_g;
       a.eps = c.eps; a.q = b.aq; a.qscale = b.sa;
-      SB_TRY(k_rownorm(ctx, a, B, d));
+      PROF(STRICTB200_K_ROWNORM, k_rownorm(ctx, a, B, d));
     }
   }
-  SB_TRY(head_and_pick(m, B, b.aq, b.sa, b, kv->d_next, nullptr, (int)B));
-  SB_TRY(k_add_i32(ctx, kv->d_lens, nullptr, 1, B));
+  PROF(STRICTB200_K_HEAD, head_and_pick(m, B, b.aq, b.sa, b, kv->d_next, nullptr, (int)B));
+  PROF(STRICTB200_K_EMBED, k_add_i32(ctx, kv->d_lens, nullptr, 1, B));
   return STRICTB200_OK;
 }
 
@@ -430,9 +458,9 @@ int qwen_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb
   const bool tp = m->world > 1;
   ChunkBufs cb;
   cb.ctx = ctx;
-  bf16 *x, *qkv, *qb, *att, *gu, *y;
+  bf16 *qkv, *qb, *att, *gu;
   uint8_t* aq;
-  float *sa, *red = nullptr;
+  float *x, *y, *sa;
   int64_t amax = std::max<int64_t>(d, std::max<int64_t>(nq, m->I_l));
   SB_TRY(cb.get(&x, T * d));
   SB_TRY(cb.get(&qkv, T * nqkv));
@@ -440,13 +468,12 @@ int qwen_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb
   SB_TRY(cb.get(&att, T * nq));
   SB_TRY(cb.get(&gu, T * 2 * m->I_l));
   SB_TRY(cb.get(&y, T * d));
-  SB_TRY(cb.get(&aq, T * amax));
+  SB_TRY(cb.get(&aq, sb_qrows(T) * amax));
   SB_TRY(cb.get(&sa, T));
-  if (tp) SB_TRY(cb.get(&red, T * d));
-  SB_TRY(k_embedding_bf16(ctx, m->embed, d_tok, T, d, c.vocab, x));
+  SB_TRY(k_embedding_bf16_f32(ctx, m->embed, d_tok, T, d, c.vocab, x));
   {
     RowNormArgs a;
-    a.x_in = x; a.gain = m->L[0].norm1_g; a.eps = c.eps; a.q = aq; a.qscale = sa;
+    a.x_f32 = x; a.gain = m->L[0].norm1_g; a.eps = c.eps; a.q = aq; a.qscale = sa;
     SB_TRY(k_rownorm(ctx, a, T, d));
   }
   // caches of this chunk's sequences start at sequence b0
@@ -468,42 +495,30 @@ int qwen_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb
     SB_TRY(k_quantize_rows(ctx, att, T, nq, nq, aq, sa));
     {
       RowNormArgs a;
-      if (tp) {
-        SB_TRY(run_gemm(m, T, w.wo, aq, sa, red, 1, nullptr, 1, 0));
-        SB_TRY(sb_tp_allreduce_f32(ctx, red, T * d));
-        a.x_f32 = red;
-      } else {
-        SB_TRY(run_gemm(m, T, w.wo, aq, sa, y, 0, nullptr, 1, 0));
-        a.x_in = y;
-      }
-      a.residual = x; a.gain = w.norm2_g; a.eps = c.eps; a.q = aq; a.qscale = sa;
+      SB_TRY(run_gemm(m, T, w.wo, aq, sa, y, 1, nullptr, 1, 0));
+      if (tp) SB_TRY(sb_tp_allreduce_f32(ctx, y, T * d));
+      a.x_f32 = y; a.residual_f32 = x; a.gain = w.norm2_g; a.eps = c.eps; a.q = aq; a.qscale = sa;
       SB_TRY(k_rownorm(ctx, a, T, d));
     }
     SB_TRY(run_gemm(m, T, w.wgu, aq, sa, gu, 0, nullptr, 1, 0));
     SB_TRY(k_swiglu(ctx, gu, T, m->I_l, nullptr, aq, sa));
     {
       RowNormArgs a;
-      if (tp) {
-        SB_TRY(run_gemm(m, T, w.wdown, aq, sa, red, 1, nullptr, 1, 0));
-        SB_TRY(sb_tp_allreduce_f32(ctx, red, T * d));
-        a.x_f32 = red;
-      } else {
-        SB_TRY(run_gemm(m, T, w.wdown, aq, sa, y, 0, nullptr, 1, 0));
-        a.x_in = y;
-      }
-      a.residual = x;
+      SB_TRY(run_gemm(m, T, w.wdown, aq, sa, y, 1, nullptr, 1, 0));
+      if (tp) SB_TRY(sb_tp_allreduce_f32(ctx, y, T * d));
+      a.x_f32 = y; a.residual_f32 = x;
       if (l + 1 < c.n_layers) { a.gain = m->L[l + 1].norm1_g; a.q = aq; a.qscale = sa; }
       a.eps = c.eps;
       SB_TRY(k_rownorm(ctx, a, T, d));
     }
   }
   // last real row of every sequence -> final norm -> head -> greedy pick
-  bf16* last;
+  float* last;
   SB_TRY(cb.get(&last, (size_t)nb * d));
-  SB_TRY(k_gather_rows(ctx, x, d_last_rows, nb, d * 2, last));
+  SB_TRY(k_gather_rows(ctx, x, d_last_rows, nb, d * 4, last));
   {
     RowNormArgs a;
-    a.x_in = last; a.gain = m->normf_g; a.eps = c.eps; a.q = aq; a.qscale = sa;
+    a.x_f32 = last; a.gain = m->normf_g; a.eps = c.eps; a.q = aq; a.qscale = sa;
     SB_TRY(k_rownorm(ctx, a, nb, d));
   }
   DecBuf hb{};
@@ -745,7 +760,7 @@ int strictb200_model_init_random(strictb200_model* m, uint64_t seed) {
   } else {
     SB_TRY(k_gen_normal_bf16(ctx, key(G_EMBED), 0, (int64_t)c.vocab * d, SD, m->embed));
     if (c.tied) {
-      SB_TRY(k_quantize_rows(ctx, m->embed + (int64_t)r * m->V_l * d, m->V_l, d, d, m->head.q, m->head.s));
+      SB_TRY(k_quantize_weight_rows(ctx, m->embed + (int64_t)r * m->V_l * d, m->V_l, d, d, m->head.q, m->head.s));
     } else {
       SB_TRY(k_gen_weight_e4m3(ctx, key(G_HEAD), (int64_t)r * m->V_l, m->V_l, d, 0, d, SD, m->head.q, d, m->head.s));
     }
@@ -795,7 +810,7 @@ int strictb200_model_set_tensor(strictb200_model* m, const char* name, const voi
   }
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
   if (std::string(name) == "embed" && m->c.arch == STRICTB200_QWEN3 && m->c.tied) {
-    SB_TRY(k_quantize_rows(ctx, m->embed + (int64_t)m->rank * m->V_l * m->c.d_model, m->V_l, m->c.d_model, m->c.d_model, m->head.q, m->head.s));
+    SB_TRY(k_quantize_weight_rows(ctx, m->embed + (int64_t)m->rank * m->V_l * m->c.d_model, m->V_l, m->c.d_model, m->c.d_model, m->head.q, m->head.s));
     SB_CUDA(cudaStreamSynchronize(ctx->stream));
   }
   return STRICTB200_OK;
@@ -1074,6 +1089,38 @@ int strictb200_generate(strictb200_model* m, strictb200_kv* kv, const int32_t* h
   SB_TRY(strictb200_decode_steps_device(m, kv, nullptr, n_steps));
   SB_CUDA(cudaMemcpyAsync(h_out, kv->d_hist, (size_t)n_steps * kv->B * 4, cudaMemcpyDeviceToHost, ctx->stream));
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return STRICTB200_OK;
+}
+
+int strictb200_profile_decode(strictb200_model* m, strictb200_kv* kv, int n_steps, float* ms_out, uint64_t* calls_out, int n_classes) {
+  if (!m || !kv || !ms_out || !calls_out) return sb_fail(STRICTB200_ERR_INVALID_ARG, "null argument");
+  strictb200_ctx* ctx = m->ctx;
+  SB_ENTER(ctx);
+  SB_REQUIRE(kv->m == m && n_steps > 0 && n_classes >= STRICTB200_K_COUNT, "bad arguments");
+  if (m->c.arch != STRICTB200_QWEN3) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "per-class timing covers the Qwen3 decode step");
+  for (int i = 0; i < n_classes; i++) { ms_out[i] = 0.f; calls_out[i] = 0; }
+  SbProfiler prof;
+  int saved = m->use_graph;
+  m->use_graph = 0;
+  ctx->prof = &prof;
+  int st = STRICTB200_OK;
+  for (int s = 0; s < n_steps && st == STRICTB200_OK; s++) {
+    st = decode_enqueue(m, kv);
+    if (st == STRICTB200_OK && cudaMemcpyAsync(kv->d_ids, kv->d_next, (size_t)kv->B * 4, cudaMemcpyDeviceToDevice, ctx->stream) != cudaSuccess)
+      st = sb_fail(STRICTB200_ERR_CUDA, "copy of the next ids failed");
+  }
+  ctx->prof = nullptr;
+  m->use_graph = saved;
+  cudaError_t e = cudaStreamSynchronize(ctx->stream);
+  if (st == STRICTB200_OK && e == cudaSuccess) {
+    for (const ProfSpan& sp : prof.spans) {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess) { ms_out[sp.cls] += ms; calls_out[sp.cls]++; }
+    }
+  }
+  for (cudaEvent_t ev : prof.pool) cudaEventDestroy(ev);
+  if (st != STRICTB200_OK) return st;
+  if (e != cudaSuccess) return sb_fail(STRICTB200_ERR_CUDA, cudaGetErrorString(e));
   return STRICTB200_OK;
 }
 

@@ -1,4 +1,4 @@
-// Row-wise kernels of the residual stream: per-token E4M3 quantisation, fused
+// Row-wise kernels of the residual stream: two-term E4M3 split of bf16 rows, fused
 // (split-K reduce + dequant) + residual add + RMSNorm + quantise, LayerNorm, SwiGLU, GELU.
 // All are HBM/L2 streams: one block per token row, 128-bit loads, warp-shuffle reductions.
 #include "common.cuh"
@@ -29,9 +29,33 @@ __device__ __forceinline__ void store8_e4m3(uint8_t* p, const float* v, float in
   *(uint2*)p = make_uint2(lo, hi);
 }
 
-// bf16 [M,K] (row stride ldx) -> E4M3 [M,K] + scale[M]
+// bf16 [M,K] (row stride ldx) -> two-term E4M3 split [sb_qrows(M),K] + power-of-two scale[M]
 __global__ void __launch_bounds__(ROW_THREADS) quantize_rows_kernel(const bf16* __restrict__ x, int64_t K, int64_t ldx,
                                                                     uint8_t* __restrict__ q, float* __restrict__ scale) {
+  __shared__ float red[32];
+  int64_t row = blockIdx.x;
+  const bf16* xr = x + row * ldx;
+  float amax = 0.f;
+  for (int64_t k = (int64_t)threadIdx.x * 8; k < K; k += ROW_THREADS * 8) {
+    float v[8];
+    load8_bf16(xr + k, v);
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+  }
+  amax = block_max(amax, red);
+  int e = sb_scale_exponent(amax);
+  float inv = sb_pow2(-e);
+  if (threadIdx.x == 0) scale[row] = sb_pow2(e);
+  for (int64_t k = (int64_t)threadIdx.x * 8; k < K; k += ROW_THREADS * 8) {
+    float v[8];
+    load8_bf16(xr + k, v);
+    sb_store_split8(q, K, row, k, v, inv);
+  }
+}
+
+// bf16 weight rows -> single E4M3 term with scale absmax/448 (the tied LM head)
+__global__ void __launch_bounds__(ROW_THREADS) quantize_weight_rows_kernel(const bf16* __restrict__ x, int64_t K, int64_t ldx,
+                                                                           uint8_t* __restrict__ q, float* __restrict__ scale) {
   __shared__ float red[32];
   int64_t row = blockIdx.x;
   const bf16* xr = x + row * ldx;
@@ -53,23 +77,6 @@ __global__ void __launch_bounds__(ROW_THREADS) quantize_rows_kernel(const bf16* 
   }
 }
 
-__global__ void __launch_bounds__(ROW_THREADS) quantize_rows_f32_kernel(const float* __restrict__ x, int64_t K, uint8_t* __restrict__ q,
-                                                                        float* __restrict__ scale) {
-  __shared__ float red[32];
-  int64_t row = blockIdx.x;
-  const float* xr = x + row * K;
-  float amax = 0.f;
-  for (int64_t k = threadIdx.x; k < K; k += ROW_THREADS) amax = fmaxf(amax, fabsf(xr[k]));
-  amax = block_max(amax, red);
-  float inv = 1.0f, sc = 1.0f;
-  if (amax > 0.f) { inv = __fdiv_rn(448.0f, amax); sc = __fdiv_rn(amax, 448.0f); }
-  if (threadIdx.x == 0) scale[row] = sc;
-  for (int64_t k = (int64_t)threadIdx.x * 2; k < K; k += ROW_THREADS * 2) {
-    uint32_t e = f32x2_to_e4m3x2(__fmul_rn(xr[k], inv), __fmul_rn(xr[k + 1], inv));
-    *(uint16_t*)(q + row * K + k) = (uint16_t)e;
-  }
-}
-
 struct RowNormDev {
   const float* x_f32;
   const bf16* x_in;
@@ -77,13 +84,13 @@ struct RowNormDev {
   int groups, splits;
   const float* sx;
   const float* sw;
+  float* residual_f32;
   bf16* residual;
   const float* gain;
   float eps;
   bf16* y;
   uint8_t* q;
   float* qscale;
-  bf16* y_raw;
 };
 
 __global__ void __launch_bounds__(ROW_THREADS) rownorm_kernel(RowNormDev a, int64_t M, int64_t d) {
@@ -117,16 +124,22 @@ __global__ void __launch_bounds__(ROW_THREADS) rownorm_kernel(RowNormDev a, int6
           for (int i = 0; i < 8; i++) tot[i] += __fmul_rn(__fmul_rn(acc[i], sxr), sw[i]);
         }
 #pragma unroll
-        for (int i = 0; i < 8; i++) t[i] = round_bf16(tot[i]);
+        for (int i = 0; i < 8; i++) t[i] = tot[i];
       } else if (a.x_f32) {
         float4 p0 = *(const float4*)(a.x_f32 + row * d + k), p1 = *(const float4*)(a.x_f32 + row * d + k + 4);
-        t[0] = round_bf16(p0.x); t[1] = round_bf16(p0.y); t[2] = round_bf16(p0.z); t[3] = round_bf16(p0.w);
-        t[4] = round_bf16(p1.x); t[5] = round_bf16(p1.y); t[6] = round_bf16(p1.z); t[7] = round_bf16(p1.w);
+        t[0] = p0.x; t[1] = p0.y; t[2] = p0.z; t[3] = p0.w;
+        t[4] = p1.x; t[5] = p1.y; t[6] = p1.z; t[7] = p1.w;
       } else {
         load8_bf16(a.x_in + row * d + k, t);
       }
-      if (a.y_raw) store8_bf16(a.y_raw + row * d + k, t);
-      if (a.residual) {
+      if (a.residual_f32) {
+        float* rp = a.residual_f32 + row * d + k;
+        float4 r0 = *(const float4*)rp, r1 = *(const float4*)(rp + 4);
+        t[0] = __fadd_rn(r0.x, t[0]); t[1] = __fadd_rn(r0.y, t[1]); t[2] = __fadd_rn(r0.z, t[2]); t[3] = __fadd_rn(r0.w, t[3]);
+        t[4] = __fadd_rn(r1.x, t[4]); t[5] = __fadd_rn(r1.y, t[5]); t[6] = __fadd_rn(r1.z, t[6]); t[7] = __fadd_rn(r1.w, t[7]);
+        *(float4*)rp = make_float4(t[0], t[1], t[2], t[3]);
+        *(float4*)(rp + 4) = make_float4(t[4], t[5], t[6], t[7]);
+      } else if (a.residual) {
         float r[8];
         load8_bf16(a.residual + row * d + k, r);
 #pragma unroll
@@ -150,7 +163,7 @@ __global__ void __launch_bounds__(ROW_THREADS) rownorm_kernel(RowNormDev a, int6
       float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
       for (int i = 0; i < 8; i++) {
-        v[c][i] = __fmul_rn(__fmul_rn(v[c][i], r), g[i]);
+        v[c][i] = round_bf16(__fmul_rn(__fmul_rn(v[c][i], r), g[i]));
         amax = fmaxf(amax, fabsf(v[c][i]));
       }
       if (a.y) store8_bf16(a.y + row * d + k, v[c]);
@@ -158,13 +171,13 @@ __global__ void __launch_bounds__(ROW_THREADS) rownorm_kernel(RowNormDev a, int6
   }
   if (!a.q) return;
   amax = block_max(amax, red);
-  float inv = 1.0f, sc = 1.0f;
-  if (amax > 0.f) { inv = __fdiv_rn(448.0f, amax); sc = __fdiv_rn(amax, 448.0f); }
-  if (threadIdx.x == 0) a.qscale[row] = sc;
+  int e = sb_scale_exponent(amax);
+  float inv = sb_pow2(-e);
+  if (threadIdx.x == 0) a.qscale[row] = sb_pow2(e);
 #pragma unroll
   for (int c = 0; c < MAX_CHUNKS; c++) {
     int64_t k = ((int64_t)c * ROW_THREADS + threadIdx.x) * 8;
-    if (k < d) store8_e4m3(a.q + row * d + k, v[c], inv);
+    if (k < d) sb_store_split8(a.q, d, row, k, v[c], inv);
   }
 }
 
@@ -210,16 +223,16 @@ __global__ void __launch_bounds__(ROW_THREADS) swiglu_kernel(const bf16* __restr
   }
   if (!q) return;
   amax = block_max(amax, red);
-  float inv = 1.0f, sc = 1.0f;
-  if (amax > 0.f) { inv = __fdiv_rn(448.0f, amax); sc = __fdiv_rn(amax, 448.0f); }
-  if (threadIdx.x == 0) qscale[row] = sc;
+  int e = sb_scale_exponent(amax);
+  float inv = sb_pow2(-e);
+  if (threadIdx.x == 0) qscale[row] = sb_pow2(e);
   for (int64_t k = (int64_t)threadIdx.x * 8; k < I; k += ROW_THREADS * 8) {
     float g[8], u[8], h[8];
     load8_bf16(gr + k, g);
     load8_bf16(gr + I + k, u);
 #pragma unroll
     for (int i = 0; i < 8; i++) h[i] = round_bf16(silu_mul(g[i], u[i]));
-    store8_e4m3(q + row * I + k, h, inv);
+    sb_store_split8(q, I, row, k, h, inv);
   }
 }
 
@@ -245,16 +258,16 @@ int k_quantize_rows(strictb200_ctx* ctx, const bf16* x, int64_t M, int64_t K, in
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }
-int k_quantize_rows_f32(strictb200_ctx* ctx, const float* x, int64_t M, int64_t K, uint8_t* q, float* scale) {
-  if (K % 2) return sb_fail(STRICTB200_ERR_INVALID_ARG, "quantize_rows_f32: K must be even");
-  quantize_rows_f32_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(x, K, q, scale);
+int k_quantize_weight_rows(strictb200_ctx* ctx, const bf16* x, int64_t M, int64_t K, int64_t ldx, uint8_t* q, float* scale) {
+  if (K % 8 || ldx % 8) return sb_fail(STRICTB200_ERR_INVALID_ARG, "quantize_weight_rows: K and the row stride must be multiples of 8");
+  quantize_weight_rows_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(x, K, ldx, q, scale);
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }
 int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   if (d % 8 || d > (int64_t)ROW_THREADS * 8 * MAX_CHUNKS)
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "rownorm: d must be a multiple of 8 and at most 16384");
-  RowNormDev v{a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual, a.gain, a.eps, a.y, a.q, a.qscale, a.y_raw};
+  RowNormDev v{a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale};
   rownorm_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(v, M, d);
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;

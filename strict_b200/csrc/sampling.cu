@@ -13,6 +13,20 @@ __global__ void embedding_bf16_kernel(const bf16* __restrict__ table, const int3
   for (int64_t i = threadIdx.x; i < d / 8; i += blockDim.x) dst[i] = src[i];
 }
 
+__global__ void embedding_bf16_f32_kernel(const bf16* __restrict__ table, const int32_t* __restrict__ ids, int64_t d, int64_t vocab,
+                                          float* __restrict__ out) {
+  int64_t t = blockIdx.x;
+  int64_t id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const uint2* src = (const uint2*)(table + id * d);
+  float4* dst = (float4*)(out + t * d);
+  for (int64_t i = threadIdx.x; i < d / 4; i += blockDim.x) {
+    uint2 u = src[i];
+    dst[i] = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u), __uint_as_float(u.y << 16),
+                         __uint_as_float(u.y & 0xFFFF0000u));
+  }
+}
+
 __global__ void embedding_f32_kernel(const float* __restrict__ wte, const float* __restrict__ wpe, const int32_t* __restrict__ ids,
                                      const int32_t* __restrict__ pos, const int32_t* __restrict__ lens, int64_t d, int64_t vocab, int max_pos,
                                      float* __restrict__ out) {
@@ -90,6 +104,12 @@ int sgrid(strictb200_ctx* ctx, int64_t n) {
 int k_embedding_bf16(strictb200_ctx* ctx, const bf16* table, const int32_t* ids, int64_t T, int64_t d, int64_t vocab, bf16* out) {
   if (d % 8) return sb_fail(STRICTB200_ERR_INVALID_ARG, "embedding: d must be a multiple of 8");
   embedding_bf16_kernel<<<(unsigned)T, 128, 0, ctx->stream>>>(table, ids, d, vocab, out);
+  SB_LAUNCHED(ctx);
+  return STRICTB200_OK;
+}
+int k_embedding_bf16_f32(strictb200_ctx* ctx, const bf16* table, const int32_t* ids, int64_t T, int64_t d, int64_t vocab, float* out) {
+  if (d % 8) return sb_fail(STRICTB200_ERR_INVALID_ARG, "embedding: d must be a multiple of 8");
+  embedding_bf16_f32_kernel<<<(unsigned)T, 128, 0, ctx->stream>>>(table, ids, d, vocab, out);
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }

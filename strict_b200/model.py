@@ -117,6 +117,16 @@ class KvCache:
         """n greedy steps with ids resident on the device (no host copies, asynchronous)."""
         N.check(N.lib().strictb200_decode_steps_device(self.model.h, self.h, None, n_steps))
 
+    KERNEL_CLASSES = ("embed", "gemm_qkv", "rope_kvappend", "attn_decode", "gemm_o", "rownorm", "gemm_gate_up", "swiglu",
+                      "gemm_down", "head", "allreduce")
+
+    def profile_decode(self, n_steps):
+        """Per-kernel-class device time of n plain-launch decode steps: {class: (total_ms, calls)}."""
+        ms = np.zeros(len(self.KERNEL_CLASSES), np.float32)
+        calls = np.zeros(len(self.KERNEL_CLASSES), np.uint64)
+        N.check(N.lib().strictb200_profile_decode(self.model.h, self.h, n_steps, N.ptr(ms), N.ptr(calls), len(ms)))
+        return {k: (float(ms[i]), int(calls[i])) for i, k in enumerate(self.KERNEL_CLASSES)}
+
     def decode_bytes(self):
         n = C.c_uint64()
         N.check(N.lib().strictb200_decode_bytes(self.model.h, self.h, C.byref(n)))

@@ -87,6 +87,7 @@ SIGNATURES = {
     "strictb200_decode_steps_device": [vp, vp, vp, i32],
     "strictb200_kv_device_ids": [vp, C.POINTER(vp)],
     "strictb200_decode_bytes": [vp, vp, C.POINTER(u64)],
+    "strictb200_profile_decode": [vp, vp, i32, vp, vp, i32],
     "strictb200_tp_unique_id": [vp],
     "strictb200_tp_init": [vp, i32, i32, vp],
     "strictb200_tp_info": [vp, C.POINTER(i32), C.POINTER(i32)],

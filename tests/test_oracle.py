@@ -118,19 +118,30 @@ def test_golden_vectors(oracle):
 
 
 # ------------------------------------------------------------------ primitives vs torch (calculator)
-def test_quant_rows_and_gemm(oracle, rng):
-    x = oracle.round_bf16(rng.standard_normal((5, 256)).astype(np.float32))
-    q, s = oracle.quant_rows(x)
-    assert np.allclose(s, np.abs(x).max(1) / 448, rtol=1e-6)
-    tq = (torch.tensor(x) * torch.tensor(448.0 / np.abs(x).max(1, keepdims=True).astype(np.float32))).to(torch.float8_e4m3fn)
-    assert np.array_equal(q, tq.view(torch.uint8).numpy())
-    wq, sw = oracle.gen_qlinear(2, 1, 48, 256)
-    y = oracle.gemm_fp8(q, s, wq, sw)
-    want = (oracle.e4m3_to_f32(q).astype(np.float64) @ oracle.e4m3_to_f32(wq).astype(np.float64).T) * s[:, None] * sw[None, :]
-    assert np.allclose(y, want, rtol=1e-6, atol=1e-9)
-    # a zero row quantises with scale 1 and produces zeros
-    q0, s0 = oracle.quant_rows(np.zeros((1, 64), np.float32))
-    assert s0[0] == 1.0 and not q0.any()
+def test_split_rows_and_linear(oracle, rng):
+    """The two-term E4M3 split reproduces bf16 rows exactly (above absmax/14336), its scale is
+    the smallest power of two that fits 448, and the linear layer equals the float64 product of
+    the bf16 activations with the dequantised weights."""
+    x = oracle.round_bf16((rng.standard_normal((6, 512)) * rng.uniform(0.01, 30, (6, 1))).astype(np.float32))
+    x[5] = 0
+    hi, lo, eff, s = oracle.split_rows(x)
+    amax = np.abs(x).max(1)
+    assert s[5] == 1.0 and not hi[5].any() and not lo[5].any()
+    assert np.all(np.log2(s) == np.round(np.log2(s)))
+    assert np.all(amax[:5] / s[:5] <= 448) and np.all(amax[:5] / s[:5] > 224)
+    assert np.array_equal(eff, oracle.e4m3_to_f32(hi) + oracle.e4m3_to_f32(lo) / 16)
+    big = np.abs(x) >= (amax / 14336)[:, None]
+    assert np.array_equal((eff * s[:, None])[big], x[big])
+    assert np.abs(eff * s[:, None] - x).max() <= amax.max() * 2.0 ** -22
+    # hi is the nearest E4M3 value of x/s
+    assert np.array_equal(hi, torch.tensor(x / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8).numpy())
+    wq, sw = oracle.gen_qlinear(2, 1, 48, 512)
+    y = oracle.linear_fp8w(x, wq, sw)
+    want = (x.astype(np.float64) @ oracle.e4m3_to_f32(wq).astype(np.float64).T) * sw[None, :]
+    assert np.allclose(y, want, rtol=2e-6, atol=1e-6 * np.abs(want).max())
+    packed, s2 = oracle.split_rows_device_layout(x)
+    assert packed.shape == (16, 512) and np.array_equal(s2, s)
+    assert np.array_equal(packed[:6], hi) and np.array_equal(packed[8:14], lo) and not packed[6:8].any()
 
 
 def test_norms_and_activations(oracle, rng):
@@ -216,20 +227,14 @@ def _torch_qwen_forward(oracle, m, cfg, tokens):
     def rb(x):  # round to bf16
         return x.to(torch.float32).to(torch.bfloat16).to(f64)
 
-    def qlin(x, name, N, K):
-        x32 = x.to(torch.float32)
-        amax = x32.abs().amax(-1, keepdim=True)
-        inv = torch.where(amax > 0, torch.tensor(448.0) / amax, torch.ones_like(amax))
-        s = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
-        xq = (x32 * inv).to(torch.float8_e4m3fn).to(f64)
+    def qlin(x, name, N, K):  # exact bf16 x E4M3 products, per-channel scale
         w = t(name + ".q", np.uint8).view(torch.float8_e4m3fn).to(f64).reshape(N, K)
-        acc = (xq @ w.T).to(torch.float32)
-        return ((acc * s) * t(name + ".s").reshape(1, N)).to(f64)
+        return (x @ w.T) * t(name + ".s").reshape(1, N).to(f64)
 
     def rms(x, g):
         x32 = x.to(torch.float32)
         r = 1.0 / torch.sqrt((x.to(f64) ** 2).mean(-1, keepdim=True).to(torch.float32) + cfg["eps"])
-        return ((x32 * r) * g).to(f64)
+        return rb(((x32 * r) * g).to(f64))
 
     x = t("embed").reshape(cfg["vocab"], d)[torch.tensor(tokens, dtype=torch.long)].to(f64)
     pos = torch.arange(T, dtype=f64)
@@ -255,12 +260,12 @@ def _torch_qwen_forward(oracle, m, cfg, tokens):
         s = ((q.permute(1, 0, 2) @ kk.transpose(1, 2)).to(torch.float32) * np.float32(1.0 / np.sqrt(D))).to(f64)
         s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
         att = rb((torch.softmax(s, -1) @ vv).permute(1, 0, 2).reshape(T, nq))
-        x = rb(x + rb(qlin(att, p + "wo", d, nq)))
+        x = x + qlin(att, p + "wo", d, nq).to(torch.float32).to(f64)
         a = rms(x, t(p + "norm2.g"))
         gu = rb(qlin(a, p + "wgu", 2 * I, d))
         g32, u32 = gu[:, :I].to(torch.float32), gu[:, I:].to(torch.float32)
         h = rb(((g32 / (1.0 + torch.exp(-g32))) * u32).to(f64))
-        x = rb(x + rb(qlin(h, p + "wdown", d, I)))
+        x = x + qlin(h, p + "wdown", d, I).to(torch.float32).to(f64)
     a = rms(x[-1:], t("normf.g"))
     return qlin(a, "head", cfg["vocab"], d)[0].numpy()
 
@@ -277,9 +282,9 @@ def test_qwen_forward_matches_independent_torch(oracle, rng):
     st = m.new_state(1, 16)
     logits = st.prefill(toks[None, :], np.array([12], np.int32))[0]
     want = _torch_qwen_forward(oracle, m, cfg, toks.tolist())
-    # identical up to occasional 1-ulp bf16/E4M3 rounding flips from different summation order
+    # identical up to occasional 1-ulp bf16 rounding flips from the different summation order
     assert np.abs(logits - want).max() < 2e-2
-    assert np.abs(logits - want).mean() / np.abs(want).mean() < 2e-3
+    assert np.abs(logits - want).mean() / np.abs(want).mean() < 5e-3
     st.close()
     m.close()
 
@@ -331,20 +336,3 @@ def test_decode_continues_prefill(oracle, cfg, seed):
     for s in (full, inc):
         s.close()
     m.close()
-
-
-def test_tensor_parallel_oracle_close_to_single(oracle):
-    cfg = dict(TINY_QWEN, n_kv_heads=2, n_q_heads=4)
-    toks = oracle.gen_tokens(2, 1, 2 * 8, cfg["vocab"]).reshape(2, 8)
-    outs = []
-    for tp in (1, 2):
-        m = oracle.Model(cfg, 4, tp=tp)
-        st = m.new_state(2, 8)
-        outs.append(st.prefill(toks, np.full(2, 8, np.int32)))
-        st.close()
-        m.close()
-    # per-rank activation scales change the E4M3 rounding, not the mathematics
-    # (E4M3 steps are 6-12 % of a value, so on this 256-wide toy the logits move by a few 1e-2)
-    assert np.abs(outs[0] - outs[1]).max() < 0.2
-    assert np.abs(outs[0] - outs[1]).mean() / np.abs(outs[0]).mean() < 0.1
-    assert np.corrcoef(outs[0].ravel(), outs[1].ravel())[0, 1] > 0.995
