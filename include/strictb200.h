@@ -65,6 +65,9 @@ int strictb200_timer_begin(strictb200_ctx* ctx);
 int strictb200_timer_end(strictb200_ctx* ctx, float* ms_out);
 /* Number of kernels this context launched since creation (library kernels only). */
 int strictb200_launch_count(strictb200_ctx* ctx, uint64_t* out);
+/* Waits for the stream, then returns (and clears) the error word kernels set when one of their
+ * bounded waits expired: 0 = none; non-zero also returns ERR_TIMEOUT. */
+int strictb200_device_status(strictb200_ctx* ctx, int* out);
 /* Writes `bytes` to a private buffer (> L2) so the next kernel starts with a cold L2. */
 int strictb200_flush_l2(strictb200_ctx* ctx);
 

@@ -57,6 +57,9 @@ int strictb200_create(int device, strictb200_ctx** out) {
   SB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   SB_CUDA(cudaEventCreate(&c->ev0));
   SB_CUDA(cudaEventCreate(&c->ev1));
+  SB_CUDA(cudaHostAlloc((void**)&c->h_status, sizeof(int), cudaHostAllocMapped));
+  *c->h_status = 0;
+  SB_CUDA(cudaHostGetDevicePointer((void**)&c->d_status, c->h_status, 0));
   *out = c;
   return STRICTB200_OK;
 }
@@ -68,6 +71,7 @@ int strictb200_destroy(strictb200_ctx* ctx) {
   sb_tp_destroy(ctx);
   if (ctx->ws) cudaFree(ctx->ws);
   if (ctx->flush_buf) cudaFree(ctx->flush_buf);
+  if (ctx->h_status) cudaFreeHost(ctx->h_status);
   cudaEventDestroy(ctx->ev0);
   cudaEventDestroy(ctx->ev1);
   cudaStreamDestroy(ctx->stream);
@@ -160,6 +164,15 @@ int strictb200_timer_end(strictb200_ctx* ctx, float* ms_out) {
 int strictb200_launch_count(strictb200_ctx* ctx, uint64_t* out) {
   if (!ctx || !out) return sb_fail(STRICTB200_ERR_INVALID_ARG, "null argument");
   *out = ctx->launches;
+  return STRICTB200_OK;
+}
+int strictb200_device_status(strictb200_ctx* ctx, int* out) {
+  SB_ENTER(ctx);
+  SB_REQUIRE(out, "null out pointer");
+  SB_CUDA(cudaStreamSynchronize(ctx->stream));
+  *out = *(volatile int*)ctx->h_status;
+  *ctx->h_status = 0;
+  if (*out) return sb_fail(STRICTB200_ERR_TIMEOUT, "a bounded device-side wait expired (code " + std::to_string(*out) + ")");
   return STRICTB200_OK;
 }
 int strictb200_flush_l2(strictb200_ctx* ctx) {

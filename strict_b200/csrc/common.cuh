@@ -27,6 +27,8 @@ struct strictb200_ctx {
   int tp_world = 1, tp_rank = 0;
   TpState* tp = nullptr;
   SbProfiler* prof = nullptr;
+  int* h_status = nullptr;  // pinned, device-visible error word written by kernels whose bounded waits expired
+  int* d_status = nullptr;
 };
 
 void sb_set_error(const std::string& msg);

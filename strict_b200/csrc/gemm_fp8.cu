@@ -278,11 +278,11 @@ int k_gemm_fp8(strictb200_ctx* ctx, const GemmArgs& g) {
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: operands and row strides must be 16-byte aligned");
   if (g.M > INT32_MAX || g.N > INT32_MAX || g.K > INT32_MAX) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: dimension too large");
   int kernel = g.kernel;
-  if (kernel == 0) kernel = g.M <= 32 ? 1 : 3;
+  if (kernel == 0) kernel = 3;
   if (kernel == 3) {
     int st = k_gemm_fp8_tmem(ctx, g);
     if (st != STRICTB200_ERR_UNSUPPORTED || g.kernel == 3) return st;
-    kernel = 2;  // shapes the tensor-memory kernel does not cover (K % 128 != 0)
+    kernel = g.M <= 32 ? 1 : 2;  // shapes the tensor-memory kernel does not cover (K per split % 128 != 0)
   }
   GemmDev d{(int)g.M, (int)sb_qrows(g.M), (int)g.N, (int)g.K, g.xq, g.ldx, g.sx, g.wq, g.ldw, g.sw, g.out, g.out_f32, g.part, g.splits, g.raw};
   if (kernel == 1) {

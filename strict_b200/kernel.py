@@ -37,6 +37,12 @@ class Context:
         N.check(N.lib().strictb200_launch_count(self.h, C.byref(n)))
         return n.value
 
+    def device_status(self):
+        """Synchronise and raise KernelException if a kernel's bounded wait expired."""
+        code = C.c_int()
+        N.check(N.lib().strictb200_device_status(self.h, C.byref(code)))
+        return code.value
+
     def flush_l2(self):
         N.check(N.lib().strictb200_flush_l2(self.h))
 
