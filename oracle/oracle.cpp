@@ -12,8 +12,10 @@
 // known answers of Strict.Compiler.Cuda.Tests/CSharpToCudaTranspilerTests.cs:46-57.
 //
 // Numerics contract of the FP8 (Qwen3) path, which the device kernels also follow:
-//  * the residual stream is fp32 (a linear layer's fp32 result is added to it unrounded); norm
-//    outputs, q/k/v, attention output and MLP activations are bf16 between ops;
+//  * the residual stream is fp32 (a linear layer's fp32 result is added to it unrounded); the
+//    qkv and gate/up projections hand their fp32 results to the fused consumers (QK-norm+RoPE,
+//    SwiGLU) unrounded; norm outputs, q, k, v (the cache), the attention output and the SwiGLU
+//    output are bf16;
 //  * a linear layer computes y = (sum_k x_k * w_k) * s_w with bf16 inputs x, E4M3 weights w and
 //    one fp32 scale per output channel: every product is exact, the sum is fp32 or better, the
 //    output is rounded to bf16 (logits stay fp32). So that the FP8 tensor cores can take the
@@ -389,7 +391,6 @@ void forward(Model* m, State* st, const int* tokens, const int* n_new, int B, in
     }
     if (qw) {
       qlinear(ly.wqkv, a.data(), T, qkv.data());
-      for (auto& v : qkv) v = round_bf16(v);
     } else gemm_f32(a.data(), ly.fqkv.w.data(), ly.fqkv.b.data(), T, nqkv, d, qkv.data());
     // q/k post-processing + cache append
 #pragma omp parallel for
@@ -409,7 +410,8 @@ void forward(Model* m, State* st, const int* tokens, const int* n_new, int B, in
       }
       for (int h = 0; h < Hkv; h++) {
         std::copy(row + nq + h * D, row + nq + (h + 1) * D, kv_at(st->k, m, st, l, b, h) + (int64_t)p * D);
-        std::copy(row + nq + nkv + h * D, row + nq + nkv + (h + 1) * D, kv_at(st->v, m, st, l, b, h) + (int64_t)p * D);
+        float* vdst = kv_at(st->v, m, st, l, b, h) + (int64_t)p * D;
+        for (int i = 0; i < D; i++) vdst[i] = qw ? round_bf16(row[nq + nkv + h * D + i]) : row[nq + nkv + h * D + i];
       }
     }
 #pragma omp parallel for schedule(dynamic, 4)
@@ -441,7 +443,7 @@ void forward(Model* m, State* st, const int* tokens, const int* n_new, int B, in
 #pragma omp parallel for
       for (int64_t t = 0; t < T; t++)
         for (int64_t i = 0; i < I; i++)
-          hact[t * I + i] = round_bf16(silu_mul(round_bf16(gu[t * 2 * I + i]), round_bf16(gu[t * 2 * I + I + i])));
+          hact[t * I + i] = round_bf16(silu_mul(gu[t * 2 * I + i], gu[t * 2 * I + I + i]));
       qlinear(ly.wdown, hact.data(), T, y.data());
       for (int64_t i = 0; i < T * d; i++) x[i] = x[i] + y[i];
     } else {

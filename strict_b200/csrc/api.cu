@@ -310,7 +310,7 @@ int strictb200_swiglu(strictb200_ctx* ctx, const uint16_t* gate_up, int64_t M, i
   SB_REQUIRE(M >= 0 && I > 0 && I % 8 == 0, "bad shape (I must be a multiple of 8)");
   if (!M) return STRICTB200_OK;
   SB_REQUIRE(gate_up && y, "null pointer");
-  return k_swiglu(ctx, (const bf16*)gate_up, M, I, (bf16*)y, nullptr, nullptr);
+  return k_swiglu(ctx, (const bf16*)gate_up, nullptr, M, I, (bf16*)y, nullptr, nullptr);
 }
 int strictb200_gelu_tanh(strictb200_ctx* ctx, const float* x, int64_t count, float* y) {
   SB_ENTER(ctx);

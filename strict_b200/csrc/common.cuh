@@ -112,11 +112,12 @@ int k_rownorm(strictb200_ctx*, const RowNormArgs& a, int64_t M, int64_t d);
 int k_reduce_scale(strictb200_ctx*, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N, float* out);
 int k_layernorm(strictb200_ctx*, const float* x, const float* g, const float* b, float eps, int64_t M, int64_t d, float* y);
 int k_add_f32(strictb200_ctx*, float* x, const float* y, int64_t n);
-int k_swiglu(strictb200_ctx*, const bf16* gate_up, int64_t M, int64_t I, bf16* y, uint8_t* q, float* qscale);
+int k_swiglu(strictb200_ctx*, const bf16* gate_up, const float* gate_up_f32, int64_t M, int64_t I, bf16* y, uint8_t* q, float* qscale);
 int k_gelu_tanh(strictb200_ctx*, const float* x, int64_t n, float* y);
 // rope.cu
 struct RopeArgs {
-  const bf16* qkv = nullptr;      // [T, nqkv] bf16 (used when part == nullptr)
+  const bf16* qkv = nullptr;      // [T, nqkv] bf16 (used when part and qkv_f32 are null)
+  const float* qkv_f32 = nullptr; // [T, nqkv] fp32 projection result
   const float* part = nullptr;    // [splits][T, nqkv] raw accumulators
   int splits = 1;
   const float* sx = nullptr;      // [T]

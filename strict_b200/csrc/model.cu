@@ -121,7 +121,7 @@ struct DecBuf {
   float* part;     // split-K partials, max over the layer's GEMMs
   bf16* qb;        // [B,Hq_l,D]
   bf16* att;       // [B,Hq_l*D]
-  bf16* gu;        // [B,2*I_l]
+  float* gu;       // [B,2*I_l] fp32 gate/up projection
   float* attn_ws;  // split-KV partials
   float* red;      // [B,d] fp32 all-reduce buffer (TP)
   float* logits;   // [B,V_l] (+ [world][B,V_l] gathered when TP)
@@ -168,7 +168,7 @@ void carve_decode(strictb200_kv* kv, char* base, DecBuf* out, size_t* total) {
     b.part = cv.take<float>(std::max(p1, std::max(p2, p3)));
     b.qb = cv.take<bf16>(B * nq);
     b.att = cv.take<bf16>(B * nq);
-    b.gu = cv.take<bf16>(B * 2 * m->I_l);
+    b.gu = cv.take<float>(B * 2 * m->I_l);
     b.attn_ws = cv.take<float>(sb_attn_decode_scratch((int)B, m->Hq_l, (int)D, kv->nsplit) / sizeof(float));
     b.red = cv.take<float>(B * d);
   } else {
@@ -330,8 +330,8 @@ int qwen_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
       PROF(STRICTB200_K_ROWNORM, k_rownorm(ctx, a, B, d));
     }
     // gate/up -> bf16, SwiGLU + quantise, down -> partials -> residual + next norm + quantise
-    PROF(STRICTB200_K_GEMM_GU, run_gemm(m, B, w.wgu, b.aq, b.sa, b.gu, 0, nullptr, 1, 0));
-    PROF(STRICTB200_K_SWIGLU, k_swiglu(ctx, b.gu, B, m->I_l, nullptr, b.aq, b.sa));
+    PROF(STRICTB200_K_GEMM_GU, run_gemm(m, B, w.wgu, b.aq, b.sa, b.gu, 1, nullptr, 1, 0));
+    PROF(STRICTB200_K_SWIGLU, k_swiglu(ctx, nullptr, b.gu, B, m->I_l, nullptr, b.aq, b.sa));
     int s4 = plan_splits(m, B, d, m->I_l);
     PROF(STRICTB200_K_GEMM_DOWN, run_gemm(m, B, w.wdown, b.aq, b.sa, nullptr, 0, b.part, s4, 1));
     {
@@ -458,9 +458,9 @@ int qwen_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb
   const bool tp = m->world > 1;
   ChunkBufs cb;
   cb.ctx = ctx;
-  bf16 *qkv, *qb, *att, *gu;
+  bf16 *qb, *att;
   uint8_t* aq;
-  float *x, *y, *sa;
+  float *x, *y, *sa, *qkv, *gu;
   int64_t amax = std::max<int64_t>(d, std::max<int64_t>(nq, m->I_l));
   SB_TRY(cb.get(&x, T * d));
   SB_TRY(cb.get(&qkv, T * nqkv));
@@ -482,10 +482,10 @@ int qwen_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb
     LayerW& w = m->L[l];
     bf16* kc = kv_k(kv, l) + (size_t)b0 * seq_stride;
     bf16* vc = kv_v(kv, l) + (size_t)b0 * seq_stride;
-    SB_TRY(run_gemm(m, T, w.wqkv, aq, sa, qkv, 0, nullptr, 1, 0));
+    SB_TRY(run_gemm(m, T, w.wqkv, aq, sa, qkv, 1, nullptr, 1, 0));
     {
       RopeArgs r;
-      r.qkv = qkv; r.seq = d_seq; r.pos = d_pos;
+      r.qkv_f32 = qkv; r.seq = d_seq; r.pos = d_pos;
       r.cos_t = m->rope_cos; r.sin_t = m->rope_sin; r.qgain = w.qn_g; r.kgain = w.kn_g; r.eps = c.eps;
       r.Hq = m->Hq_l; r.Hkv = m->Hkv_l; r.D = (int)D; r.maxlen = kv->maxlen; r.max_pos = c.max_pos;
       r.q_out = qb; r.kcache = kc; r.vcache = vc;
@@ -500,8 +500,8 @@ int qwen_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb
       a.x_f32 = y; a.residual_f32 = x; a.gain = w.norm2_g; a.eps = c.eps; a.q = aq; a.qscale = sa;
       SB_TRY(k_rownorm(ctx, a, T, d));
     }
-    SB_TRY(run_gemm(m, T, w.wgu, aq, sa, gu, 0, nullptr, 1, 0));
-    SB_TRY(k_swiglu(ctx, gu, T, m->I_l, nullptr, aq, sa));
+    SB_TRY(run_gemm(m, T, w.wgu, aq, sa, gu, 1, nullptr, 1, 0));
+    SB_TRY(k_swiglu(ctx, nullptr, gu, T, m->I_l, nullptr, aq, sa));
     {
       RowNormArgs a;
       SB_TRY(run_gemm(m, T, w.wdown, aq, sa, y, 1, nullptr, 1, 0));

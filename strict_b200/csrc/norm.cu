@@ -206,17 +206,21 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
 }
 
-// gate_up [M, 2I] bf16 -> h = bf16(silu(gate)*up); optional E4M3 quantisation of h per row.
-__global__ void __launch_bounds__(ROW_THREADS) swiglu_kernel(const bf16* __restrict__ gu, int64_t I, bf16* __restrict__ y,
-                                                             uint8_t* __restrict__ q, float* __restrict__ qscale) {
+__device__ __forceinline__ void load8_f32(const float* p, float* v) {
+  float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+// gate_up [M, 2I] (bf16, or the projection's fp32 result) -> h = bf16(silu(gate)*up); optional
+// two-term E4M3 split of h per row.
+__global__ void __launch_bounds__(ROW_THREADS) swiglu_kernel(const bf16* __restrict__ gu, const float* __restrict__ gu32, int64_t I,
+                                                             bf16* __restrict__ y, uint8_t* __restrict__ q, float* __restrict__ qscale) {
   __shared__ float red[32];
   int64_t row = blockIdx.x;
-  const bf16* gr = gu + row * 2 * I;
   float amax = 0.f;
   for (int64_t k = (int64_t)threadIdx.x * 8; k < I; k += ROW_THREADS * 8) {
     float g[8], u[8], h[8];
-    load8_bf16(gr + k, g);
-    load8_bf16(gr + I + k, u);
+    if (gu32) { load8_f32(gu32 + row * 2 * I + k, g); load8_f32(gu32 + row * 2 * I + I + k, u); }
+    else { load8_bf16(gu + row * 2 * I + k, g); load8_bf16(gu + row * 2 * I + I + k, u); }
 #pragma unroll
     for (int i = 0; i < 8; i++) { h[i] = round_bf16(silu_mul(g[i], u[i])); amax = fmaxf(amax, fabsf(h[i])); }
     if (y) store8_bf16(y + row * I + k, h);
@@ -228,8 +232,8 @@ __global__ void __launch_bounds__(ROW_THREADS) swiglu_kernel(const bf16* __restr
   if (threadIdx.x == 0) qscale[row] = sb_pow2(e);
   for (int64_t k = (int64_t)threadIdx.x * 8; k < I; k += ROW_THREADS * 8) {
     float g[8], u[8], h[8];
-    load8_bf16(gr + k, g);
-    load8_bf16(gr + I + k, u);
+    if (gu32) { load8_f32(gu32 + row * 2 * I + k, g); load8_f32(gu32 + row * 2 * I + I + k, u); }
+    else { load8_bf16(gu + row * 2 * I + k, g); load8_bf16(gu + row * 2 * I + I + k, u); }
 #pragma unroll
     for (int i = 0; i < 8; i++) h[i] = round_bf16(silu_mul(g[i], u[i]));
     sb_store_split8(q, I, row, k, h, inv);
@@ -282,9 +286,9 @@ int k_add_f32(strictb200_ctx* ctx, float* x, const float* y, int64_t n) {
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }
-int k_swiglu(strictb200_ctx* ctx, const bf16* gate_up, int64_t M, int64_t I, bf16* y, uint8_t* q, float* qscale) {
+int k_swiglu(strictb200_ctx* ctx, const bf16* gate_up, const float* gate_up_f32, int64_t M, int64_t I, bf16* y, uint8_t* q, float* qscale) {
   if (I % 8) return sb_fail(STRICTB200_ERR_INVALID_ARG, "swiglu: I must be a multiple of 8");
-  swiglu_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(gate_up, I, y, q, qscale);
+  swiglu_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(gate_up, gate_up_f32, I, y, q, qscale);
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }

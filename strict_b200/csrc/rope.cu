@@ -10,6 +10,7 @@ namespace {
 
 struct RopeDev {
   const bf16* qkv;
+  const float* qkv_f32;
   const float* part;
   int splits;
   const float* sx;
@@ -48,10 +49,13 @@ __global__ void __launch_bounds__(256) rope_kernel(RopeDev a, int64_t T) {
       }
       float sxr = a.sx[t];
       float4 w = *(const float4*)(a.sw + col);
-      x[0] = round_bf16(__fmul_rn(__fmul_rn(acc[0], sxr), w.x));
-      x[1] = round_bf16(__fmul_rn(__fmul_rn(acc[1], sxr), w.y));
-      x[2] = round_bf16(__fmul_rn(__fmul_rn(acc[2], sxr), w.z));
-      x[3] = round_bf16(__fmul_rn(__fmul_rn(acc[3], sxr), w.w));
+      x[0] = __fmul_rn(__fmul_rn(acc[0], sxr), w.x);
+      x[1] = __fmul_rn(__fmul_rn(acc[1], sxr), w.y);
+      x[2] = __fmul_rn(__fmul_rn(acc[2], sxr), w.z);
+      x[3] = __fmul_rn(__fmul_rn(acc[3], sxr), w.w);
+    } else if (a.qkv_f32) {
+      float4 v = *(const float4*)(a.qkv_f32 + t * nqkv + col);
+      x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
     } else {
       uint2 u = *(const uint2*)(a.qkv + t * nqkv + col);
       x[0] = __uint_as_float(u.x << 16); x[1] = __uint_as_float(u.x & 0xFFFF0000u);
@@ -98,7 +102,7 @@ __global__ void __launch_bounds__(256) rope_kernel(RopeDev a, int64_t T) {
 
 int k_rope_qknorm_kvappend(strictb200_ctx* ctx, const RopeArgs& a, int64_t T) {
   if (a.D != 128) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "rope: head_dim must be 128");
-  RopeDev v{a.qkv, a.part, a.splits, a.sx, a.sw, a.seq, a.pos, a.lens, a.cos_t, a.sin_t, a.qgain, a.kgain,
+  RopeDev v{a.qkv, a.qkv_f32, a.part, a.splits, a.sx, a.sw, a.seq, a.pos, a.lens, a.cos_t, a.sin_t, a.qgain, a.kgain,
             a.eps, a.Hq, a.Hkv, a.maxlen, a.max_pos, a.q_out, a.kcache, a.vcache};
   rope_kernel<<<(unsigned)T, 256, 0, ctx->stream>>>(v, T);
   SB_LAUNCHED(ctx);

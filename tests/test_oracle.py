@@ -251,10 +251,10 @@ def _torch_qwen_forward(oracle, m, cfg, tokens):
     for l in range(cfg["n_layers"]):
         p = f"layers.{l}."
         a = rms(x, t(p + "norm1.g"))
-        qkv = rb(qlin(a, p + "wqkv", nq + 2 * nkv, d))
+        qkv = qlin(a, p + "wqkv", nq + 2 * nkv, d).to(torch.float32).to(f64)
         q = rope(qkv[:, :nq].reshape(T, Hq, D), t(p + "qnorm.g"))
         k = rope(qkv[:, nq:nq + nkv].reshape(T, Hkv, D), t(p + "knorm.g"))
-        v = qkv[:, nq + nkv:].reshape(T, Hkv, D)
+        v = rb(qkv[:, nq + nkv:]).reshape(T, Hkv, D)
         kk = k.repeat_interleave(Hq // Hkv, 1).permute(1, 0, 2)
         vv = v.repeat_interleave(Hq // Hkv, 1).permute(1, 0, 2)
         s = ((q.permute(1, 0, 2) @ kk.transpose(1, 2)).to(torch.float32) * np.float32(1.0 / np.sqrt(D))).to(f64)
@@ -262,7 +262,7 @@ def _torch_qwen_forward(oracle, m, cfg, tokens):
         att = rb((torch.softmax(s, -1) @ vv).permute(1, 0, 2).reshape(T, nq))
         x = x + qlin(att, p + "wo", d, nq).to(torch.float32).to(f64)
         a = rms(x, t(p + "norm2.g"))
-        gu = rb(qlin(a, p + "wgu", 2 * I, d))
+        gu = qlin(a, p + "wgu", 2 * I, d)
         g32, u32 = gu[:, :I].to(torch.float32), gu[:, I:].to(torch.float32)
         h = rb(((g32 / (1.0 + torch.exp(-g32))) * u32).to(f64))
         x = x + qlin(h, p + "wdown", d, I).to(torch.float32).to(f64)
