@@ -158,7 +158,9 @@ def run_ours(args, rank, world, local_rank):
             uid.copy_(torch.from_numpy(h))
         dist.broadcast(uid, 0)
         ctx.tp_init(world, rank, N.ptr(np.ascontiguousarray(uid.cpu().numpy())))
-    cfg = sb.CONFIGS["qwen3-8b"]
+    cfg = dict(sb.CONFIGS["qwen3-8b"])
+    if args.layers:
+        cfg["n_layers"] = args.layers  # profiling aid: same kernels and shapes, fewer layers resident
     model = sb.Model(ctx, cfg).init_random(SEED)
     total_steps = 2 * (max(args.warmup, 3) + args.steps) + 16
     kv = model.new_cache(BATCH, PROMPT + total_steps + 8)
@@ -169,7 +171,11 @@ def run_ours(args, rank, world, local_rank):
     toks[:] = d_tok.to_host().reshape(BATCH, PROMPT)
     d_tok.free()
     t0 = time.perf_counter()
-    first, _ = kv.prefill(toks)
+    if args.synthetic_kv:
+        kv.fill_synthetic(SEED + 2, PROMPT)  # profiling aid: seeded N(0,1) keys/values instead of the prefill
+        first = toks[:, -1].copy()
+    else:
+        first, _ = kv.prefill(toks)
     ctx.synchronize()
     prefill_s = time.perf_counter() - t0
 
@@ -242,12 +248,13 @@ def run_ours(args, rank, world, local_rank):
                          "frac": bytes_step / (ms / args.steps * 1e-3) / 1e9 / hbm}}
     if rank != 0:
         return
-    base, _ = cpu_reference(2, 1) if world == 1 else (None, None)
+    base, _ = cpu_reference(2, 1) if world == 1 and not args.no_cpu else (None, None)
     line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 x fp8_e4m3 -> f32 (activations as two E4M3 terms on the FP8 tensor cores; bf16 KV)", "data": "synthetic",
             "config": {"workload": WORKLOAD, "batch": BATCH, "context": int(lens_now.mean()), "parallelism": f"tp{world}",
-                       "l2": "inputs larger than L2 (17.8 GB streamed per step)", "prefill_s": prefill_s, "cuda_graph": True},
+                       "l2": "inputs larger than L2 (17.8 GB streamed per step)", "prefill_s": prefill_s, "cuda_graph": True,
+                       "layers": cfg["n_layers"], "kv": "synthetic" if args.synthetic_kv else "prefill of the seeded prompts"},
             "roofline": roofline, "kernels": kernels, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks}
     if base:
         line["cpu_baseline"] = base
@@ -263,6 +270,9 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="profiling aid: run only this many of the 36 layers")
+    ap.add_argument("--synthetic-kv", action="store_true", help="profiling aid: fill the cache with seeded values instead of the prefill")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
