@@ -149,6 +149,19 @@ int strictb200_attn_prefill(strictb200_ctx* ctx, const uint16_t* d_q, const uint
 int strictb200_attn_decode(strictb200_ctx* ctx, const uint16_t* d_q, const uint16_t* d_kcache, const uint16_t* d_vcache,
                            const int32_t* d_lens, int B, int Hq, int Hkv, int D, int maxlen, float scale, uint16_t* d_out);
 
+/* Same computation as strictb200_attn_decode for hosts that must not allocate while serving:
+ * a decode loop that cannot absorb the device-wide stall cudaMalloc/cudaFree cause, or a host
+ * that gave all device memory to its own pool at start-up. This entry point has no counterpart
+ * in the reference. It calls no allocator of any kind: the split-KV partial results go to a
+ * 4 MiB array built into the library image (every GPU that loads the library holds it until
+ * exit). A call whose B * Hq * key-chunks * 130 floats exceed 4 MiB is rejected with
+ * ERR_INVALID_ARG. The first call on a device looks up the array's device address; make that
+ * first call before starting any stream capture. All calls on a device share the array and
+ * its previous contents (none of it needs clearing), so two calls whose kernels overlap on
+ * the GPU — different contexts or streams on one device — race; serialise them. */
+int strictb200_attn_decode_noalloc(strictb200_ctx* ctx, const uint16_t* d_q, const uint16_t* d_kcache, const uint16_t* d_vcache,
+                                   const int32_t* d_lens, int B, int Hq, int Hkv, int D, int maxlen, float scale, uint16_t* d_out);
+
 /* ---- embedding / sampling ---- */
 int strictb200_embedding_bf16(strictb200_ctx* ctx, const uint16_t* d_table, const int32_t* d_ids, int64_t T, int64_t d, int64_t vocab,
                               uint16_t* d_out);

@@ -11,6 +11,8 @@
 //
 // Shared-memory tiles hold rows of 128 bf16 (256 B = 16 chunks of 16 B); chunk c of row r
 // lives at chunk c ^ (r & 7), which makes every ldmatrix phase conflict-free.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -543,4 +545,59 @@ int k_attn_f32(strictb200_ctx* ctx, const float* qkv, float* kc, float* vc, cons
   attn_f32_kernel<<<grid, 128, smem, ctx->stream>>>(qkv, kc, vc, seq, pos, lens, H, Dh, maxlen, scale, out);
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
+}
+
+// ------------------------------------------------------------------ decode attention without any allocation
+// Some hosts of this library must not trigger an allocation while they serve requests: a
+// latency-critical decode loop cannot afford the device-wide synchronisation that cudaMalloc and
+// cudaFree imply (every stream of the process stalls behind them), and a host that hands out the
+// GPU's memory from its own pool at start-up leaves the driver's allocator nothing to give, so a
+// late request for scratch would simply fail. For those callers the split-KV partial results live
+// in a fixed array that is part of the library image: every GPU that loads the library carries
+// these 4 MiB from load to exit, whether or not the entry point is ever called.
+namespace {
+constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)1 << 20;  // 4 MiB of (m, l, o) partials
+constexpr int NOALLOC_MAX_DEVICES = 64;
+}  // namespace
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+namespace {
+// In host code `g_noalloc_scratch` is only a handle for the symbol, never a device address; the
+// address a kernel may use is asked for once per device (with that device current) and kept here.
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+std::mutex g_noalloc_mutex;
+
+int noalloc_scratch(strictb200_ctx* ctx, float** out) {
+  if (ctx->device < 0 || ctx->device >= NOALLOC_MAX_DEVICES) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "device index beyond the static scratch table");
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[ctx->device]) {
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);  // the caller made ctx->device current
+    if (e != cudaSuccess || !p) return sb_fail(STRICTB200_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e));
+    g_noalloc_ptr[ctx->device] = p;
+  }
+  *out = g_noalloc_ptr[ctx->device];
+  return STRICTB200_OK;
+}
+}  // namespace
+
+extern "C" int strictb200_attn_decode_noalloc(strictb200_ctx* ctx, const uint16_t* q, const uint16_t* kc, const uint16_t* vc,
+                                              const int32_t* lens, int B, int Hq, int Hkv, int Dh, int maxlen, float scale, uint16_t* out) {
+  SB_ENTER(ctx);
+  if (Dh != D) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "head_dim must be 128");
+  SB_REQUIRE(B >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= 16 && maxlen > 0, "bad shape");
+  if (!B) return STRICTB200_OK;
+  SB_REQUIRE(q && kc && vc && lens && out, "null pointer");
+  int nsplit = sb_attn_decode_splits(ctx, B, Hkv, maxlen);
+  size_t need = sb_attn_decode_scratch(B, Hq, Dh, nsplit) / sizeof(float);
+  if (need > NOALLOC_SCRATCH_FLOATS)
+    return sb_fail(STRICTB200_ERR_INVALID_ARG, "attn_decode_noalloc: batch " + std::to_string(B) + " x " + std::to_string(Hq) + " heads x " +
+                                                   std::to_string(nsplit) + " key chunks needs " + std::to_string(need * sizeof(float)) +
+                                                   " bytes of partial results; the built-in scratch holds " +
+                                                   std::to_string(NOALLOC_SCRATCH_FLOATS * sizeof(float)) + " (use strictb200_attn_decode)");
+  float* scratch;
+  SB_TRY(noalloc_scratch(ctx, &scratch));
+  // Nothing in the scratch has to start at zero: each key chunk a sequence owns is written in full
+  // by its block before the combine kernel reads it, and chunks beyond a sequence's length are never read.
+  return k_attn_decode(ctx, (const bf16*)q, (const bf16*)kc, (const bf16*)vc, lens, 0, B, Hq, Hkv, Dh, maxlen, scale, nsplit, scratch,
+                       (bf16*)out, nullptr, nullptr);
 }

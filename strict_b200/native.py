@@ -68,6 +68,7 @@ SIGNATURES = {
     "strictb200_rope_qknorm_kvappend": [vp, vp, vp, vp, i64, i32, i32, i32, vp, vp, f32, f32, i32, vp, vp, vp, i32],
     "strictb200_attn_prefill": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
     "strictb200_attn_decode": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, vp],
+    "strictb200_attn_decode_noalloc": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, vp],
     "strictb200_embedding_bf16": [vp, vp, vp, i64, i64, i64, vp],
     "strictb200_argmax": [vp, vp, i64, i64, vp],
     "strictb200_model_create": [vp, C.POINTER(ModelConfig), C.POINTER(vp)],
