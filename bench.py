@@ -128,7 +128,7 @@ def run_reference(args, rank):
 # ---------------------------------------------------------------------------------- GPU arm
 def run_ours(args, rank, world, local_rank):
     import strict_b200 as sb
-    from strict_b200 import native as N
+    from strict_b200 import native as N, tp
     dist = None
     if world > 1:
         import torch
@@ -141,23 +141,15 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
 
     def max_over_ranks(x):
-        if not dist:
-            return x
-        import torch
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return tp.max_over_ranks(dist, x, "cuda") if dist else x
 
     ctx = sb.Context(local_rank)
     if world > 1:
-        import torch
-        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
-        if rank == 0:
+        def make_id():
             h = np.zeros(128, np.uint8)
             N.check(N.lib().strictb200_tp_unique_id(N.ptr(h)))
-            uid.copy_(torch.from_numpy(h))
-        dist.broadcast(uid, 0)
-        ctx.tp_init(world, rank, N.ptr(np.ascontiguousarray(uid.cpu().numpy())))
+            return h
+        ctx.tp_init(world, rank, N.ptr(tp.share_unique_id(dist, rank, make_id, "cuda")))
     cfg = dict(sb.CONFIGS["qwen3-8b"])
     if args.layers:
         cfg["n_layers"] = args.layers  # profiling aid: same kernels and shapes, fewer layers resident
