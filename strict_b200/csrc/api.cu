@@ -378,7 +378,9 @@ int strictb200_argmax(strictb200_ctx* ctx, const float* x, int64_t M, int64_t N,
   SB_REQUIRE(M >= 0 && N > 0, "bad shape");
   if (!M) return STRICTB200_OK;
   SB_REQUIRE(x && out, "null pointer");
-  return k_argmax(ctx, x, M, N, N, out, nullptr);
+  void* ws;
+  SB_TRY(sb_ws(ctx, sb_argmax_scratch(M, N), &ws));
+  return k_argmax(ctx, x, M, N, N, out, nullptr, ws);
 }
 
 }  // extern "C"

@@ -365,45 +365,57 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
   }
 }
 
-// grid B, 256 threads: merge the chunks of every head of one token; optional two-term E4M3
-// split of the whole token row [Hq*128] (the o_proj input).
-__global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
-                                                           const int32_t* __restrict__ lens, int len_add, int Hq, int maxlen, int chunk,
-                                                           int nsplit, bf16* __restrict__ out, uint8_t* __restrict__ q_out,
-                                                           float* __restrict__ qscale) {
+// grid B, 512 threads: merge the key chunks of every head of one token. A thread owns 8
+// consecutive dims of one head (two when Hq > 32) and keeps them in registers for the optional
+// two-term E4M3 split of the whole token row [Hq*128] (the o_proj input).
+constexpr int CB_THREADS = 512, CB_ITEMS = 2;
+__global__ void __launch_bounds__(CB_THREADS) attn_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
+                                                                  const int32_t* __restrict__ lens, int len_add, int Hq, int maxlen, int chunk,
+                                                                  int nsplit, bf16* __restrict__ out, uint8_t* __restrict__ q_out,
+                                                                  float* __restrict__ qscale) {
   __shared__ float red[32];
   const int b = blockIdx.x;
   const int len = min(lens[b] + len_add, maxlen);
   const int ns = (len + chunk - 1) / chunk;
+  float v[CB_ITEMS][8];
   float amax = 0.f;
-  for (int e = threadIdx.x; e < Hq * D; e += 256) {
-    int h = e / D, d = e - h * D;
-    int64_t base = ((int64_t)b * Hq + h) * nsplit;
-    float M = -INFINITY;
-    for (int s = 0; s < ns; s++) M = fmaxf(M, ml_part[(base + s) * 2]);
-    float L = 0.f, O = 0.f;
-    for (int s = 0; s < ns; s++) {
-      float f = exp2f(ml_part[(base + s) * 2] - M);
-      L += ml_part[(base + s) * 2 + 1] * f;
-      O += o_part[(base + s) * D + d] * f;
+#pragma unroll
+  for (int it = 0; it < CB_ITEMS; it++) {
+    int e8 = threadIdx.x + it * CB_THREADS;  // index of an 8-dim group of the row
+    if (e8 < Hq * (D / 8)) {
+      int h = e8 / (D / 8), d = (e8 - h * (D / 8)) * 8;
+      int64_t base = ((int64_t)b * Hq + h) * nsplit;
+      float M = -INFINITY;
+      for (int s = 0; s < ns; s++) M = fmaxf(M, ml_part[(base + s) * 2]);
+      float L = 0.f, O[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < ns; s++) {
+        float f = exp2f(ml_part[(base + s) * 2] - M);
+        L += ml_part[(base + s) * 2 + 1] * f;
+        const float4* op = (const float4*)(o_part + (base + s) * D + d);
+        float4 o0 = op[0], o1 = op[1];
+        O[0] += o0.x * f; O[1] += o0.y * f; O[2] += o0.z * f; O[3] += o0.w * f;
+        O[4] += o1.x * f; O[5] += o1.y * f; O[6] += o1.z * f; O[7] += o1.w * f;
+      }
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        v[it][i] = ns > 0 ? round_bf16(O[i] / L) : 0.f;
+        amax = fmaxf(amax, fabsf(v[it][i]));
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++) w[i] = pack_bf16(v[it][2 * i], v[it][2 * i + 1]);
+      *(uint4*)(out + ((int64_t)b * Hq + h) * D + d) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    float v = ns > 0 ? round_bf16(O / L) : 0.f;
-    out[((int64_t)b * Hq + h) * D + d] = __float2bfloat16_rn(v);
-    amax = fmaxf(amax, fabsf(v));
   }
   if (!q_out) return;
   amax = block_max(amax, red);
   int ex = sb_scale_exponent(amax);
   float inv = sb_pow2(-ex);
   if (threadIdx.x == 0) qscale[b] = sb_pow2(ex);
-  __syncthreads();  // the row written above is re-read below by other threads of the block
-  for (int e = threadIdx.x * 8; e < Hq * D; e += 2048) {
-    uint4 u = *(const uint4*)(out + (int64_t)b * Hq * D + e);
-    uint32_t w[4] = {u.x, u.y, u.z, u.w};
-    float v[8];
 #pragma unroll
-    for (int i = 0; i < 4; i++) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
-    sb_store_split8(q_out, (int64_t)Hq * D, b, e, v, inv);
+  for (int it = 0; it < CB_ITEMS; it++) {
+    int e8 = threadIdx.x + it * CB_THREADS;
+    if (e8 < Hq * (D / 8)) sb_store_split8(q_out, (int64_t)Hq * D, b, (int64_t)e8 * 8, v[it], inv);
   }
 }
 
@@ -508,7 +520,7 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
                   int Dh, int maxlen, float scale, int nsplit, float* scratch, bf16* out, uint8_t* q_out, float* qscale_out) {
   if (Dh != D) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: head_dim must be 128");
   if (Hq / Hkv > 16) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: at most 16 query heads per KV head");
-  if ((Hq * D) % 4) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: bad head count");
+  if (Hq * (D / 8) > CB_THREADS * CB_ITEMS) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: at most 64 query heads per rank");
   int chunk = decode_chunk(ctx, B, Hkv, maxlen);
   if ((maxlen + chunk - 1) / chunk != nsplit) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: split count does not match the cache size");
   static bool attr = false;
@@ -523,7 +535,7 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
   dim3 grid(nsplit, Hkv, B);
   attn_decode_kernel<<<grid, 128, smem, ctx->stream>>>(q, kc, vc, lens, len_add, B, Hq, Hkv, maxlen, chunk, nsplit, scale * LOG2E, o_part, ml_part);
   SB_LAUNCHED(ctx);
-  attn_combine_kernel<<<B, 256, 0, ctx->stream>>>(o_part, ml_part, lens, len_add, Hq, maxlen, chunk, nsplit, out, q_out, qscale_out);
+  attn_combine_kernel<<<B, CB_THREADS, 0, ctx->stream>>>(o_part, ml_part, lens, len_add, Hq, maxlen, chunk, nsplit, out, q_out, qscale_out);
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }

@@ -172,7 +172,8 @@ int k_embedding_bf16(strictb200_ctx*, const bf16* table, const int32_t* ids, int
 int k_embedding_bf16_f32(strictb200_ctx*, const bf16* table, const int32_t* ids, int64_t T, int64_t d, int64_t vocab, float* out);
 int k_embedding_f32(strictb200_ctx*, const float* wte, const float* wpe, const int32_t* ids, const int32_t* pos, const int32_t* lens,
                     int64_t T, int64_t d, int64_t vocab, int max_pos, float* out);
-int k_argmax(strictb200_ctx*, const float* x, int64_t M, int64_t N, int64_t ldx, int32_t* out, float* val_out);
+int k_argmax(strictb200_ctx*, const float* x, int64_t M, int64_t N, int64_t ldx, int32_t* out, float* val_out, void* scratch);
+size_t sb_argmax_scratch(int64_t M, int64_t N);  // bytes of chunk winners for the two-stage pick
 int k_gather_rows(strictb200_ctx*, const void* src, const int32_t* rows, int64_t n_rows, int64_t row_bytes, void* dst);
 int k_add_i32(strictb200_ctx*, int32_t* x, const int32_t* inc, int32_t c, int64_t n);
 int k_f32_to_bf16(strictb200_ctx*, const float* x, int64_t n, bf16* y);

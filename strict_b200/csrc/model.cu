@@ -131,6 +131,7 @@ struct DecBuf {
   float* bf;       // GPT-2: second scratch
   float* best_val; // [world][B]
   int32_t* best_idx;
+  void* am_ws;     // chunk winners of the two-stage argmax
 };
 
 size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -181,6 +182,7 @@ void carve_decode(strictb200_kv* kv, char* base, DecBuf* out, size_t* total) {
   b.logits_all = cv.take<float>(m->world > 1 ? (size_t)m->world * B * m->V_l : 1);
   b.best_val = cv.take<float>((size_t)m->world * B);
   b.best_idx = cv.take<int32_t>((size_t)m->world * B);
+  b.am_ws = cv.take<uint8_t>(sb_argmax_scratch(B, m->V_l));
   *out = b;
   *total = cv.off;
 }
@@ -224,14 +226,14 @@ int head_and_pick(strictb200_model* m, int64_t M, const uint8_t* aq, const float
   strictb200_ctx* ctx = m->ctx;
   SB_TRY(run_gemm(m, M, m->head, aq, sa, b.logits, 1, nullptr, 1, 0));
   if (m->world == 1) {
-    SB_TRY(k_argmax(ctx, b.logits, M, m->V_l, m->V_l, d_next, nullptr));
+    SB_TRY(k_argmax(ctx, b.logits, M, m->V_l, m->V_l, d_next, nullptr, b.am_ws));
     if (h_logits) SB_CUDA(cudaMemcpyAsync(h_logits, b.logits, (size_t)M * m->V_l * 4, cudaMemcpyDeviceToHost, ctx->stream));
     return STRICTB200_OK;
   }
   (void)stride_B;
   float* my_val = b.best_val + (size_t)m->rank * M;
   int32_t* my_idx = b.best_idx + (size_t)m->rank * M;
-  SB_TRY(k_argmax(ctx, b.logits, M, m->V_l, m->V_l, my_idx, my_val));
+  SB_TRY(k_argmax(ctx, b.logits, M, m->V_l, m->V_l, my_idx, my_val, b.am_ws));
   SB_TRY(sb_tp_allgather(ctx, my_val, b.best_val, M * 4));
   SB_TRY(sb_tp_allgather(ctx, my_idx, b.best_idx, M * 4));
   merge_argmax_kernel<<<(unsigned)((M + 127) / 128), 128, 0, ctx->stream>>>(b.best_val, b.best_idx, m->world, (int)M, (int)m->V_l, d_next);
@@ -385,7 +387,7 @@ int gpt2_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
   SB_TRY(gpt2_layers(m, kv, B, b.xf, b.af, b.bf, nullptr, nullptr));
   SB_TRY(k_layernorm(ctx, b.xf, m->normf_g, m->normf_b, c.eps, B, d, b.af));
   SB_TRY(k_gemm_f32(ctx, B, c.vocab, d, b.af, m->wte, nullptr, b.logits, 0));
-  SB_TRY(k_argmax(ctx, b.logits, B, c.vocab, c.vocab, kv->d_next, nullptr));
+  SB_TRY(k_argmax(ctx, b.logits, B, c.vocab, c.vocab, kv->d_next, nullptr, b.am_ws));
   SB_TRY(k_add_i32(ctx, kv->d_lens, nullptr, 1, B));
   return STRICTB200_OK;
 }
@@ -526,6 +528,7 @@ int qwen_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb
   SB_TRY(cb.get(&hb.logits_all, m->world > 1 ? (size_t)m->world * nb * m->V_l : 1));
   SB_TRY(cb.get(&hb.best_val, (size_t)m->world * nb));
   SB_TRY(cb.get(&hb.best_idx, (size_t)m->world * nb));
+  SB_TRY(cb.get((uint8_t**)&hb.am_ws, sb_argmax_scratch(nb, m->V_l)));
   SB_TRY(head_and_pick(m, nb, aq, sa, hb, d_next, h_logits, nb));
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
   return STRICTB200_OK;
@@ -551,7 +554,7 @@ int gpt2_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb
   SB_TRY(k_gather_rows(ctx, xf, d_last_rows, nb, d * 4, last));
   SB_TRY(k_layernorm(ctx, last, m->normf_g, m->normf_b, c.eps, nb, d, lastn));
   SB_TRY(k_gemm_f32(ctx, nb, c.vocab, d, lastn, m->wte, nullptr, logits, 0));
-  SB_TRY(k_argmax(ctx, logits, nb, c.vocab, c.vocab, d_next, nullptr));
+  SB_TRY(k_argmax(ctx, logits, nb, c.vocab, c.vocab, d_next, nullptr, nullptr));
   if (h_logits) SB_CUDA(cudaMemcpyAsync(h_logits, logits, (size_t)nb * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
   return STRICTB200_OK;

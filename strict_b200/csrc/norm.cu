@@ -93,14 +93,15 @@ struct RowNormDev {
   float* qscale;
 };
 
-__global__ void __launch_bounds__(ROW_THREADS) rownorm_kernel(RowNormDev a, int64_t M, int64_t d) {
+__global__ void __launch_bounds__(512) rownorm_kernel(RowNormDev a, int64_t M, int64_t d) {
+  const int NT = blockDim.x;
   __shared__ float red[32];
   int64_t row = blockIdx.x;
   float v[MAX_CHUNKS][8];
   float ss = 0.f;
 #pragma unroll
   for (int c = 0; c < MAX_CHUNKS; c++) {
-    int64_t k = ((int64_t)c * ROW_THREADS + threadIdx.x) * 8;
+    int64_t k = ((int64_t)c * NT + threadIdx.x) * 8;
     if (k < d) {
       float* t = v[c];
       if (a.part) {
@@ -113,6 +114,7 @@ __global__ void __launch_bounds__(ROW_THREADS) rownorm_kernel(RowNormDev a, int6
           float acc[8];
 #pragma unroll
           for (int i = 0; i < 8; i++) acc[i] = 0.f;
+#pragma unroll 4
           for (int s = 0; s < a.splits; s++) {
             const float* p = a.part + (((int64_t)(g * a.splits + s) * M + row) * d + k);
             float4 p0 = *(const float4*)p, p1 = *(const float4*)(p + 4);
@@ -157,7 +159,7 @@ __global__ void __launch_bounds__(ROW_THREADS) rownorm_kernel(RowNormDev a, int6
   float amax = 0.f;
 #pragma unroll
   for (int c = 0; c < MAX_CHUNKS; c++) {
-    int64_t k = ((int64_t)c * ROW_THREADS + threadIdx.x) * 8;
+    int64_t k = ((int64_t)c * NT + threadIdx.x) * 8;
     if (k < d) {
       float4 g0 = *(const float4*)(a.gain + k), g1 = *(const float4*)(a.gain + k + 4);
       float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
@@ -176,7 +178,7 @@ __global__ void __launch_bounds__(ROW_THREADS) rownorm_kernel(RowNormDev a, int6
   if (threadIdx.x == 0) a.qscale[row] = sb_pow2(e);
 #pragma unroll
   for (int c = 0; c < MAX_CHUNKS; c++) {
-    int64_t k = ((int64_t)c * ROW_THREADS + threadIdx.x) * 8;
+    int64_t k = ((int64_t)c * NT + threadIdx.x) * 8;
     if (k < d) sb_store_split8(a.q, d, row, k, v[c], inv);
   }
 }
@@ -211,32 +213,60 @@ __device__ __forceinline__ void load8_f32(const float* p, float* v) {
   v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 // gate_up [M, 2I] (bf16, or the projection's fp32 result) -> h = bf16(silu(gate)*up); optional
-// two-term E4M3 split of h per row.
-__global__ void __launch_bounds__(ROW_THREADS) swiglu_kernel(const bf16* __restrict__ gu, const float* __restrict__ gu32, int64_t I,
-                                                             bf16* __restrict__ y, uint8_t* __restrict__ q, float* __restrict__ qscale) {
+// two-term E4M3 split of h per row. 512 threads; a thread owns up to 4 groups of 8 columns and
+// keeps h in registers between the absmax pass and the split (rows wider than 16384 recompute).
+constexpr int SW_THREADS = 512, SW_ITEMS = 4;
+__global__ void __launch_bounds__(SW_THREADS) swiglu_kernel(const bf16* __restrict__ gu, const float* __restrict__ gu32, int64_t I,
+                                                            bf16* __restrict__ y, uint8_t* __restrict__ q, float* __restrict__ qscale) {
   __shared__ float red[32];
   int64_t row = blockIdx.x;
+  const bool in_regs = I <= (int64_t)SW_THREADS * 8 * SW_ITEMS;
+  float hreg[SW_ITEMS][8];
   float amax = 0.f;
-  for (int64_t k = (int64_t)threadIdx.x * 8; k < I; k += ROW_THREADS * 8) {
-    float g[8], u[8], h[8];
+  auto compute = [&](int64_t k, float* h) {
+    float g[8], u[8];
     if (gu32) { load8_f32(gu32 + row * 2 * I + k, g); load8_f32(gu32 + row * 2 * I + I + k, u); }
     else { load8_bf16(gu + row * 2 * I + k, g); load8_bf16(gu + row * 2 * I + I + k, u); }
 #pragma unroll
-    for (int i = 0; i < 8; i++) { h[i] = round_bf16(silu_mul(g[i], u[i])); amax = fmaxf(amax, fabsf(h[i])); }
-    if (y) store8_bf16(y + row * I + k, h);
+    for (int i = 0; i < 8; i++) h[i] = round_bf16(silu_mul(g[i], u[i]));
+  };
+  if (in_regs) {
+#pragma unroll
+    for (int it = 0; it < SW_ITEMS; it++) {
+      int64_t k = ((int64_t)it * SW_THREADS + threadIdx.x) * 8;
+      if (k < I) {
+        compute(k, hreg[it]);
+#pragma unroll
+        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(hreg[it][i]));
+        if (y) store8_bf16(y + row * I + k, hreg[it]);
+      }
+    }
+  } else {
+    for (int64_t k = (int64_t)threadIdx.x * 8; k < I; k += SW_THREADS * 8) {
+      float h[8];
+      compute(k, h);
+#pragma unroll
+      for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(h[i]));
+      if (y) store8_bf16(y + row * I + k, h);
+    }
   }
   if (!q) return;
   amax = block_max(amax, red);
   int e = sb_scale_exponent(amax);
   float inv = sb_pow2(-e);
   if (threadIdx.x == 0) qscale[row] = sb_pow2(e);
-  for (int64_t k = (int64_t)threadIdx.x * 8; k < I; k += ROW_THREADS * 8) {
-    float g[8], u[8], h[8];
-    if (gu32) { load8_f32(gu32 + row * 2 * I + k, g); load8_f32(gu32 + row * 2 * I + I + k, u); }
-    else { load8_bf16(gu + row * 2 * I + k, g); load8_bf16(gu + row * 2 * I + I + k, u); }
+  if (in_regs) {
 #pragma unroll
-    for (int i = 0; i < 8; i++) h[i] = round_bf16(silu_mul(g[i], u[i]));
-    sb_store_split8(q, I, row, k, h, inv);
+    for (int it = 0; it < SW_ITEMS; it++) {
+      int64_t k = ((int64_t)it * SW_THREADS + threadIdx.x) * 8;
+      if (k < I) sb_store_split8(q, I, row, k, hreg[it], inv);
+    }
+  } else {
+    for (int64_t k = (int64_t)threadIdx.x * 8; k < I; k += SW_THREADS * 8) {
+      float h[8];
+      compute(k, h);
+      sb_store_split8(q, I, row, k, h, inv);
+    }
   }
 }
 
@@ -271,8 +301,12 @@ int k_quantize_weight_rows(strictb200_ctx* ctx, const bf16* x, int64_t M, int64_
 int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   if (d % 8 || d > (int64_t)ROW_THREADS * 8 * MAX_CHUNKS)
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "rownorm: d must be a multiple of 8 and at most 16384");
+  // one 8-value chunk per thread where the row allows it (more loads in flight per row)
+  int threads = (int)((d / 8 + 31) / 32 * 32);
+  threads = threads < 128 ? 128 : (threads > 512 ? 512 : threads);
+  while ((int64_t)threads * 8 * MAX_CHUNKS < d) threads += 32;
   RowNormDev v{a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale};
-  rownorm_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(v, M, d);
+  rownorm_kernel<<<(unsigned)M, threads, 0, ctx->stream>>>(v, M, d);
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }
@@ -288,7 +322,7 @@ int k_add_f32(strictb200_ctx* ctx, float* x, const float* y, int64_t n) {
 }
 int k_swiglu(strictb200_ctx* ctx, const bf16* gate_up, const float* gate_up_f32, int64_t M, int64_t I, bf16* y, uint8_t* q, float* qscale) {
   if (I % 8) return sb_fail(STRICTB200_ERR_INVALID_ARG, "swiglu: I must be a multiple of 8");
-  swiglu_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(gate_up, gate_up_f32, I, y, q, qscale);
+  swiglu_kernel<<<(unsigned)M, SW_THREADS, 0, ctx->stream>>>(gate_up, gate_up_f32, I, y, q, qscale);
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }

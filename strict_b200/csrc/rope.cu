@@ -1,6 +1,5 @@
 // Per-head RMS norm of q and k, rotary embedding, and append of k/v to the cache, fused with
-// the dequantising reduction of the qkv GEMM's split-K partials. One block per token row, one
-// warp per head: a lane owns 4 of the 128 dims, the rotary partner (i, i+64) lives in lane^16.
+// the dequantising reduction of the qkv GEMM's split-K partials. One warp per (token row, head): a lane owns 4 of the 128 dims, the rotary partner (i, i+64) lives in lane^16.
 #include <cmath>
 #include <vector>
 
@@ -33,16 +32,18 @@ __global__ void __launch_bounds__(256) rope_kernel(RopeDev a, int64_t T) {
   constexpr int D = 128;
   int64_t t = blockIdx.x;
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int h_first = blockIdx.y * nwarps + warp, h_step = gridDim.y * nwarps;
   int b = a.seq ? a.seq[t] : (int)t;
   int p = a.pos ? a.pos[t] : a.lens[b];
   if (p < 0 || p >= a.maxlen || p >= a.max_pos) return;  // host validates; never index outside the cache
   int nheads = a.Hq + 2 * a.Hkv;
   int64_t nqkv = (int64_t)nheads * D;
-  for (int h = warp; h < nheads; h += nwarps) {
+  for (int h = h_first; h < nheads; h += h_step) {
     int64_t col = (int64_t)h * D + lane * 4;
     float x[4];
     if (a.part) {
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
       for (int s = 0; s < a.splits; s++) {
         float4 v = *(const float4*)(a.part + ((int64_t)s * T + t) * nqkv + col);
         acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
@@ -104,7 +105,10 @@ int k_rope_qknorm_kvappend(strictb200_ctx* ctx, const RopeArgs& a, int64_t T) {
   if (a.D != 128) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "rope: head_dim must be 128");
   RopeDev v{a.qkv, a.qkv_f32, a.part, a.splits, a.sx, a.sw, a.seq, a.pos, a.lens, a.cos_t, a.sin_t, a.qgain, a.kgain,
             a.eps, a.Hq, a.Hkv, a.maxlen, a.max_pos, a.q_out, a.kcache, a.vcache};
-  rope_kernel<<<(unsigned)T, 256, 0, ctx->stream>>>(v, T);
+  int nheads = a.Hq + 2 * a.Hkv;
+  // few rows (decode): spread the heads of a row over several blocks, one head per warp
+  dim3 grid((unsigned)T, T <= 256 ? (unsigned)((nheads + 7) / 8) : 1u);
+  rope_kernel<<<grid, 256, 0, ctx->stream>>>(v, T);
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }

@@ -119,8 +119,75 @@ int k_embedding_f32(strictb200_ctx* ctx, const float* wte, const float* wpe, con
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }
-int k_argmax(strictb200_ctx* ctx, const float* x, int64_t M, int64_t N, int64_t ldx, int32_t* out, float* val_out) {
-  argmax_kernel<<<(unsigned)M, 1024, 0, ctx->stream>>>(x, N, ldx, out, val_out);
+// Two-stage pick for wide rows: blocks of 256 threads scan 4096-column chunks, then one block
+// per row merges the chunk winners (chunks ascend, ties keep the lower index).
+namespace {
+constexpr int AM_CHUNK = 4096;
+__global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restrict__ x, int64_t N, int64_t ldx, float* __restrict__ cval,
+                                                           int32_t* __restrict__ cidx, int nchunks) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  int64_t row = blockIdx.y;
+  int64_t c0 = (int64_t)blockIdx.x * AM_CHUNK, c1 = c0 + AM_CHUNK < N ? c0 + AM_CHUNK : N;
+  const float* xr = x + row * ldx;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int64_t i = c0 + threadIdx.x; i < c1; i += 256) {
+    float v = xr[i];
+    if (v > best) { best = v; bi = (int)i; }  // a thread's indices ascend: strict > keeps the lowest
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) { sv[w] = best; si[w] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < 8; k++)
+      if (sv[k] > best || (sv[k] == best && si[k] < bi)) { best = sv[k]; bi = si[k]; }
+    cval[row * nchunks + blockIdx.x] = best;
+    cidx[row * nchunks + blockIdx.x] = bi;
+  }
+}
+__global__ void argmax_merge_kernel(const float* __restrict__ cval, const int32_t* __restrict__ cidx, int nchunks, int32_t* __restrict__ out,
+                                    float* __restrict__ val_out) {
+  int64_t row = blockIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int k = threadIdx.x; k < nchunks; k += 32) {
+    float v = cval[row * nchunks + k];
+    int i = cidx[row * nchunks + k];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if (threadIdx.x == 0) {
+    out[row] = bi == 0x7fffffff ? 0 : bi;
+    if (val_out) val_out[row] = best;
+  }
+}
+}  // namespace
+size_t sb_argmax_scratch(int64_t M, int64_t N) { return (size_t)M * ((N + AM_CHUNK - 1) / AM_CHUNK) * 8; }
+int k_argmax(strictb200_ctx* ctx, const float* x, int64_t M, int64_t N, int64_t ldx, int32_t* out, float* val_out, void* scratch) {
+  if (!scratch || N <= 2 * AM_CHUNK) {
+    argmax_kernel<<<(unsigned)M, 1024, 0, ctx->stream>>>(x, N, ldx, out, val_out);
+    SB_LAUNCHED(ctx);
+    return STRICTB200_OK;
+  }
+  int nchunks = (int)((N + AM_CHUNK - 1) / AM_CHUNK);
+  float* cval = (float*)scratch;
+  int32_t* cidx = (int32_t*)(cval + (size_t)M * nchunks);
+  if (M > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "argmax: too many rows");
+  argmax_chunk_kernel<<<dim3(nchunks, (unsigned)M), 256, 0, ctx->stream>>>(x, N, ldx, cval, cidx, nchunks);
+  SB_LAUNCHED(ctx);
+  argmax_merge_kernel<<<(unsigned)M, 32, 0, ctx->stream>>>(cval, cidx, nchunks, out, val_out);
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }
