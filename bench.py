@@ -154,6 +154,8 @@ def run_ours(args, rank, world, local_rank):
     if args.layers:
         cfg["n_layers"] = args.layers  # profiling aid: same kernels and shapes, fewer layers resident
     model = sb.Model(ctx, cfg).init_random(SEED)
+    if args.no_graph:
+        model.set_graph(False)
     total_steps = 2 * (max(args.warmup, 3) + args.steps) + 16
     kv = model.new_cache(BATCH, PROMPT + total_steps + 8)
     # prompts: 32 x 2048 uniform ids from the seeded generator; real prefill fills the cache
@@ -245,7 +247,7 @@ def run_ours(args, rank, world, local_rank):
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 x fp8_e4m3 -> f32 (activations as two E4M3 terms on the FP8 tensor cores; bf16 KV)", "data": "synthetic",
             "config": {"workload": WORKLOAD, "batch": BATCH, "context": int(lens_now.mean()), "parallelism": f"tp{world}",
-                       "l2": "inputs larger than L2 (17.8 GB streamed per step)", "prefill_s": prefill_s, "cuda_graph": True,
+                       "l2": "inputs larger than L2 (17.8 GB streamed per step)", "prefill_s": prefill_s, "cuda_graph": not args.no_graph,
                        "layers": cfg["n_layers"], "kv": "synthetic" if args.synthetic_kv else "prefill of the seeded prompts"},
             "roofline": roofline, "kernels": kernels, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks}
     if base:
@@ -265,6 +267,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: run only this many of the 36 layers")
     ap.add_argument("--synthetic-kv", action="store_true", help="profiling aid: fill the cache with seeded values instead of the prefill")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-graph", action="store_true", help="plain launches instead of CUDA-graph replay of the decode step")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

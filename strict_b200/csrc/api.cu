@@ -1,4 +1,5 @@
 // Context, memory and op-level C entry points of libstrictb200.so.
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -54,6 +55,7 @@ int strictb200_create(int device, strictb200_ctx** out) {
   strictb200_ctx* c = new strictb200_ctx;
   c->device = device;
   c->sm_count = prop.multiProcessorCount;
+  if (const char* e = getenv("STRICTB200_PDL")) c->pdl = atoi(e) != 0;
   SB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   SB_CUDA(cudaEventCreate(&c->ev0));
   SB_CUDA(cudaEventCreate(&c->ev1));

@@ -218,6 +218,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
                                                           int chunk, int nsplit, float scale_log2, float* __restrict__ o_part,
                                                           float* __restrict__ ml_part) {
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_trigger();
+  pdl_wait();
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int len = min(lens[b] + len_add, maxlen);
   const int k_begin = split * chunk;
@@ -374,6 +376,8 @@ __global__ void __launch_bounds__(CB_THREADS) attn_combine_kernel(const float* _
                                                                   int nsplit, bf16* __restrict__ out, uint8_t* __restrict__ q_out,
                                                                   float* __restrict__ qscale) {
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x;
   const int len = min(lens[b] + len_add, maxlen);
   const int ns = (len + chunk - 1) / chunk;
@@ -533,10 +537,10 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
   float* ml_part = scratch + (size_t)B * Hq * nsplit * D;
   if (Hkv > 65535 || B > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: too many heads or sequences");
   dim3 grid(nsplit, Hkv, B);
-  attn_decode_kernel<<<grid, 128, smem, ctx->stream>>>(q, kc, vc, lens, len_add, B, Hq, Hkv, maxlen, chunk, nsplit, scale * LOG2E, o_part, ml_part);
-  SB_LAUNCHED(ctx);
-  attn_combine_kernel<<<B, CB_THREADS, 0, ctx->stream>>>(o_part, ml_part, lens, len_add, Hq, maxlen, chunk, nsplit, out, q_out, qscale_out);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, attn_decode_kernel, grid, dim3(128), smem, q, kc, vc, lens, len_add, B, Hq, Hkv, maxlen, chunk, nsplit, scale * LOG2E, o_part, ml_part));
+  ctx->launches++;
+  SB_CUDA(sb_launch(ctx, attn_combine_kernel, dim3(B), dim3(CB_THREADS), 0, o_part, ml_part, lens, len_add, Hq, maxlen, chunk, nsplit, out, q_out, qscale_out));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 

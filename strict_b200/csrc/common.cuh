@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <utility>
 
 #include "../../include/strictb200.h"
 
@@ -29,6 +30,7 @@ struct strictb200_ctx {
   SbProfiler* prof = nullptr;
   int* h_status = nullptr;  // pinned, device-visible error word written by kernels whose bounded waits expired
   int* d_status = nullptr;
+  int pdl = 1;  // launch the decode-path kernels with programmatic dependent launch
 };
 
 void sb_set_error(const std::string& msg);
@@ -185,6 +187,28 @@ void sb_tp_destroy(strictb200_ctx*);
 
 // ------------------------------------------------------------------ device helpers
 #ifdef __CUDACC__
+// Programmatic dependent launch. A kernel launched through sb_launch may begin while its
+// predecessor in the stream is still running: pdl_trigger() lets the successor start launching,
+// pdl_wait() blocks until the predecessor has completed and its writes are visible. Every such
+// kernel calls pdl_wait() before it reads or writes anything another kernel touches (so the
+// ordering stays transitive along the stream); only reads of constants (weights) may precede it.
+// Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline cudaError_t sb_launch(strictb200_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

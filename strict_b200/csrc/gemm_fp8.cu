@@ -18,6 +18,8 @@
 // The k index inside a 64-byte unit is permuted identically for both operands (lane t of a
 // quad holds bytes [16t,16t+16) of the unit and feeds them to two consecutive MMAs), which is
 // legal because a dot product does not depend on the order of its terms.
+#include <cstdlib>
+
 #include "common.cuh"
 
 int k_gemm_fp8_tmem(strictb200_ctx* ctx, const GemmArgs& a);  // gemm_tmem.cu
@@ -266,7 +268,9 @@ int sb_gemm_pick_splits(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K) {
   if (M > 32) return 1;
   int64_t tiles = (N + SK_ROWS - 1) / SK_ROWS;
   int s = 1;
-  while (tiles * s < (int64_t)ctx->sm_count * 3 / 2 && s < 16 && K % (2 * s * 64) == 0 && K / (2 * s) >= 512) s *= 2;
+  static int target = getenv("STRICTB200_SPLIT_TARGET") ? atoi(getenv("STRICTB200_SPLIT_TARGET")) : 0;
+  int64_t want = target ? target : (int64_t)ctx->sm_count * 3 / 2;
+  while (tiles * s < want && s < 16 && K % (2 * s * 64) == 0 && K / (2 * s) >= 512) s *= 2;
   return s;
 }
 

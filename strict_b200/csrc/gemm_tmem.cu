@@ -18,6 +18,8 @@
 // returns, so a lost signal cannot hang the GPU.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -101,6 +103,7 @@ struct TmemArgs {
   int splits;
   int raw;
   int* status;  // host-visible error word
+  int prefetch;  // issue the first ring of weight loads before the dependency wait
 };
 
 template <int BT, int STAGES>
@@ -135,11 +138,24 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
 
+  pdl_trigger();
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < nkb; kb++) {
+      // The weights are constants: their loads for the first ring of stages are issued before the
+      // dependency wait, so they stream from HBM while the preceding kernel is still running.
+      const int npre = nkb < STAGES ? nkb : STAGES;
+      if (!a.prefetch) pdl_wait();
+      for (int kb = 0; kb < npre; kb++) {
+        uint32_t full = smem_u32(&bar_full[kb]);
+        mbar_expect_tx(full, STAGE_BYTES);
+        tma_load_2d(smem_u32(smem + (size_t)kb * STAGE_BYTES), &map_w, k_begin + kb * BK, n0, full);
+      }
+      pdl_wait();
+      for (int kb = 0; kb < npre; kb++)
+        tma_load_2d(smem_u32(smem + (size_t)kb * STAGE_BYTES) + BN * BK, &map_x, k_begin + kb * BK, t0, smem_u32(&bar_full[kb]));
+      for (int kb = npre; kb < nkb; kb++) {
         int s = kb % STAGES;
-        if (kb >= STAGES && !mbar_wait(smem_u32(&bar_empty[s]), ((kb / STAGES) & 1) ^ 1)) { set_status(a.status, 1); abort_flag = 1; break; }
+        if (!mbar_wait(smem_u32(&bar_empty[s]), ((kb / STAGES) & 1) ^ 1)) { set_status(a.status, 1); abort_flag = 1; break; }
         if (*(volatile int*)&abort_flag) break;
         uint32_t full = smem_u32(&bar_full[s]);
         uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -172,6 +188,7 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
     // epilogue: warp w may touch TMEM lanes [32*(w%4), +32)
     const int lg = warp & 3;
     const int n = n0 + lg * 32 + lane;
+    pdl_wait();  // the scales and the output buffers belong to the dependency chain
     bool ok = mbar_wait(smem_u32(&bar_acc), 0);
     if (!ok) { if (lane == 0) set_status(a.status, 3); }
     ok = ok && !*(volatile int*)&abort_flag;
@@ -250,8 +267,8 @@ int launch(strictb200_ctx* ctx, const GemmArgs& g, const TmemArgs& ta) {
   SB_TRY(make_map(&mx, g.xq, ta.Mq, g.K, g.ldx, BT));
   dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((ta.Mq + BT - 1) / BT), (unsigned)g.splits);
   if (grid.y > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: M too large for one launch");
-  gemm_tmem_kernel<BT, STAGES><<<grid, 192, smem, ctx->stream>>>(mw, mx, ta);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, gemm_tmem_kernel<BT, STAGES>, grid, dim3(192), smem, mw, mx, ta));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 
@@ -264,7 +281,7 @@ int k_gemm_fp8_tmem(strictb200_ctx* ctx, const GemmArgs& g) {
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: operands and row strides must be 16-byte aligned");
   if ((g.splits > 1 || g.raw) && !g.part) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: split-K needs a partial buffer");
   SB_TRY(get_encode());
-  TmemArgs ta{(int)g.M, (int)sb_qrows(g.M), (int)g.N, (int)g.K, g.sx, g.sw, g.out, g.out_f32, g.part, g.splits, g.raw, ctx->d_status};
+  TmemArgs ta{(int)g.M, (int)sb_qrows(g.M), (int)g.N, (int)g.K, g.sx, g.sw, g.out, g.out_f32, g.part, g.splits, g.raw, ctx->d_status, getenv("STRICTB200_PREFETCH") ? atoi(getenv("STRICTB200_PREFETCH")) : 1};
   // BT = operand rows per block: the whole (split) batch for decode, 256 for prefill
   if (ta.Mq <= 32) return launch<32, 5>(ctx, g, ta);
   if (ta.Mq <= 64) return launch<64, 4>(ctx, g, ta);

@@ -190,6 +190,8 @@ void carve_decode(strictb200_kv* kv, char* base, DecBuf* out, size_t* total) {
 // Pick the global argmax from per-rank (value, index) pairs; rank r's indices are offset by r*V_l.
 __global__ void merge_argmax_kernel(const float* __restrict__ vals, const int32_t* __restrict__ idx, int world, int B, int V_l,
                                     int32_t* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   float best = -INFINITY;

@@ -95,6 +95,8 @@ struct RowNormDev {
 
 __global__ void __launch_bounds__(512) rownorm_kernel(RowNormDev a, int64_t M, int64_t d) {
   const int NT = blockDim.x;
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   int64_t row = blockIdx.x;
   float v[MAX_CHUNKS][8];
@@ -219,6 +221,8 @@ constexpr int SW_THREADS = 512, SW_ITEMS = 4;
 __global__ void __launch_bounds__(SW_THREADS) swiglu_kernel(const bf16* __restrict__ gu, const float* __restrict__ gu32, int64_t I,
                                                             bf16* __restrict__ y, uint8_t* __restrict__ q, float* __restrict__ qscale) {
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
   int64_t row = blockIdx.x;
   const bool in_regs = I <= (int64_t)SW_THREADS * 8 * SW_ITEMS;
   float hreg[SW_ITEMS][8];
@@ -306,8 +310,8 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   threads = threads < 128 ? 128 : (threads > 512 ? 512 : threads);
   while ((int64_t)threads * 8 * MAX_CHUNKS < d) threads += 32;
   RowNormDev v{a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale};
-  rownorm_kernel<<<(unsigned)M, threads, 0, ctx->stream>>>(v, M, d);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, rownorm_kernel, dim3((unsigned)M), dim3(threads), 0, v, M, d));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 int k_layernorm(strictb200_ctx* ctx, const float* x, const float* g, const float* b, float eps, int64_t M, int64_t d, float* y) {
@@ -322,8 +326,8 @@ int k_add_f32(strictb200_ctx* ctx, float* x, const float* y, int64_t n) {
 }
 int k_swiglu(strictb200_ctx* ctx, const bf16* gate_up, const float* gate_up_f32, int64_t M, int64_t I, bf16* y, uint8_t* q, float* qscale) {
   if (I % 8) return sb_fail(STRICTB200_ERR_INVALID_ARG, "swiglu: I must be a multiple of 8");
-  swiglu_kernel<<<(unsigned)M, SW_THREADS, 0, ctx->stream>>>(gate_up, gate_up_f32, I, y, q, qscale);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, swiglu_kernel, dim3((unsigned)M), dim3(SW_THREADS), 0, gate_up, gate_up_f32, I, y, q, qscale));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 int k_gelu_tanh(strictb200_ctx* ctx, const float* x, int64_t n, float* y) {
@@ -336,6 +340,8 @@ int k_gelu_tanh(strictb200_ctx* ctx, const float* x, int64_t n, float* y) {
 namespace {
 __global__ void reduce_scale_kernel(const float* __restrict__ part, int splits, const float* __restrict__ sx, const float* __restrict__ sw,
                                     int64_t M, int64_t N, float* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   int64_t total = M * N / 4, stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     int64_t m = (i * 4) / N, n = (i * 4) - m * N;
@@ -355,7 +361,7 @@ __global__ void reduce_scale_kernel(const float* __restrict__ part, int splits, 
 }  // namespace
 int k_reduce_scale(strictb200_ctx* ctx, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N, float* out) {
   if (N % 4) return sb_fail(STRICTB200_ERR_INVALID_ARG, "reduce_scale: N must be a multiple of 4");
-  reduce_scale_kernel<<<stream_grid(ctx, M * N / 4, 256), 256, 0, ctx->stream>>>(part, splits, sx, sw, M, N, out);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, reduce_scale_kernel, dim3(stream_grid(ctx, M * N / 4, 256)), dim3(256), 0, part, splits, sx, sw, M, N, out));
+  ctx->launches++;
   return STRICTB200_OK;
 }

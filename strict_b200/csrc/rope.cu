@@ -30,6 +30,8 @@ struct RopeDev {
 
 __global__ void __launch_bounds__(256) rope_kernel(RopeDev a, int64_t T) {
   constexpr int D = 128;
+  pdl_trigger();
+  pdl_wait();
   int64_t t = blockIdx.x;
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int h_first = blockIdx.y * nwarps + warp, h_step = gridDim.y * nwarps;
@@ -108,8 +110,8 @@ int k_rope_qknorm_kvappend(strictb200_ctx* ctx, const RopeArgs& a, int64_t T) {
   int nheads = a.Hq + 2 * a.Hkv;
   // few rows (decode): spread the heads of a row over several blocks, one head per warp
   dim3 grid((unsigned)T, T <= 256 ? (unsigned)((nheads + 7) / 8) : 1u);
-  rope_kernel<<<grid, 256, 0, ctx->stream>>>(v, T);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, rope_kernel, grid, dim3(256), 0, v, T));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 

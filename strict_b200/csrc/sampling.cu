@@ -15,6 +15,8 @@ __global__ void embedding_bf16_kernel(const bf16* __restrict__ table, const int3
 
 __global__ void embedding_bf16_f32_kernel(const bf16* __restrict__ table, const int32_t* __restrict__ ids, int64_t d, int64_t vocab,
                                           float* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   int64_t t = blockIdx.x;
   int64_t id = ids[t];
   if (id < 0 || id >= vocab) id = 0;
@@ -84,6 +86,8 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ src, const int32_t*
   for (int64_t i = threadIdx.x; i < row_vec; i += blockDim.x) dst[r * row_vec + i] = src[s * row_vec + i];
 }
 __global__ void add_i32_kernel(int32_t* x, const int32_t* inc, int32_t c, int64_t n) {
+  pdl_trigger();
+  pdl_wait();
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) x[i] += inc ? inc[i] : c;
 }
@@ -109,8 +113,8 @@ int k_embedding_bf16(strictb200_ctx* ctx, const bf16* table, const int32_t* ids,
 }
 int k_embedding_bf16_f32(strictb200_ctx* ctx, const bf16* table, const int32_t* ids, int64_t T, int64_t d, int64_t vocab, float* out) {
   if (d % 8) return sb_fail(STRICTB200_ERR_INVALID_ARG, "embedding: d must be a multiple of 8");
-  embedding_bf16_f32_kernel<<<(unsigned)T, 128, 0, ctx->stream>>>(table, ids, d, vocab, out);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, embedding_bf16_f32_kernel, dim3((unsigned)T), dim3(128), 0, table, ids, d, vocab, out));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 int k_embedding_f32(strictb200_ctx* ctx, const float* wte, const float* wpe, const int32_t* ids, const int32_t* pos, const int32_t* lens,
@@ -127,6 +131,8 @@ __global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restri
                                                            int32_t* __restrict__ cidx, int nchunks) {
   __shared__ float sv[8];
   __shared__ int si[8];
+  pdl_trigger();
+  pdl_wait();
   int64_t row = blockIdx.y;
   int64_t c0 = (int64_t)blockIdx.x * AM_CHUNK, c1 = c0 + AM_CHUNK < N ? c0 + AM_CHUNK : N;
   const float* xr = x + row * ldx;
@@ -154,6 +160,8 @@ __global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restri
 }
 __global__ void argmax_merge_kernel(const float* __restrict__ cval, const int32_t* __restrict__ cidx, int nchunks, int32_t* __restrict__ out,
                                     float* __restrict__ val_out) {
+  pdl_trigger();
+  pdl_wait();
   int64_t row = blockIdx.x;
   float best = -INFINITY;
   int bi = 0x7fffffff;
@@ -185,10 +193,10 @@ int k_argmax(strictb200_ctx* ctx, const float* x, int64_t M, int64_t N, int64_t 
   float* cval = (float*)scratch;
   int32_t* cidx = (int32_t*)(cval + (size_t)M * nchunks);
   if (M > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "argmax: too many rows");
-  argmax_chunk_kernel<<<dim3(nchunks, (unsigned)M), 256, 0, ctx->stream>>>(x, N, ldx, cval, cidx, nchunks);
-  SB_LAUNCHED(ctx);
-  argmax_merge_kernel<<<(unsigned)M, 32, 0, ctx->stream>>>(cval, cidx, nchunks, out, val_out);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, argmax_chunk_kernel, dim3(nchunks, (unsigned)M), dim3(256), 0, x, N, ldx, cval, cidx, nchunks));
+  ctx->launches++;
+  SB_CUDA(sb_launch(ctx, argmax_merge_kernel, dim3((unsigned)M), dim3(32), 0, (const float*)cval, (const int32_t*)cidx, nchunks, out, val_out));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 int k_gather_rows(strictb200_ctx* ctx, const void* src, const int32_t* rows, int64_t n_rows, int64_t row_bytes, void* dst) {
@@ -198,8 +206,8 @@ int k_gather_rows(strictb200_ctx* ctx, const void* src, const int32_t* rows, int
   return STRICTB200_OK;
 }
 int k_add_i32(strictb200_ctx* ctx, int32_t* x, const int32_t* inc, int32_t c, int64_t n) {
-  add_i32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(x, inc, c, n);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, add_i32_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, x, inc, c, n));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 int k_f32_to_bf16(strictb200_ctx* ctx, const float* x, int64_t n, bf16* y) {
