@@ -73,6 +73,7 @@ int strictb200_destroy(strictb200_ctx* ctx) {
   sb_tp_destroy(ctx);
   if (ctx->ws) cudaFree(ctx->ws);
   if (ctx->flush_buf) cudaFree(ctx->flush_buf);
+  if (ctx->gemm_ws) cudaFree(ctx->gemm_ws);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   cudaEventDestroy(ctx->ev0);
   cudaEventDestroy(ctx->ev1);

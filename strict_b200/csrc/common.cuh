@@ -30,6 +30,8 @@ struct strictb200_ctx {
   SbProfiler* prof = nullptr;
   int* h_status = nullptr;  // pinned, device-visible error word written by kernels whose bounded waits expired
   int* d_status = nullptr;
+  void* gemm_ws = nullptr;  // stream-K tile counters + partial tiles of the tensor-memory GEMM
+  size_t gemm_count_bytes = 0, gemm_part_bytes = 0;
   int pdl = 1;  // launch the decode-path kernels with programmatic dependent launch
 };
 

@@ -6,13 +6,27 @@
 // same kernel therefore serves decode (BT = 32/64: a pure HBM stream of weights through TMA,
 // no thread ever touches a weight byte) and prefill (BT = 256: tensor-bound tiles).
 //
-// One block = one 128 x BT output tile over one K range (grid.z = K splits):
+// Persistent schedule: the grid is one block per SM. All (output tile, 128-byte K block) pairs
+// form one linear list, tile-major, and block c owns a contiguous range of it. By default the
+// ranges are cut at tile boundaries (block c owns tiles [c*tiles/G, (c+1)*tiles/G)), so every
+// tile goes straight from its accumulator to the epilogue while the MMA warp already fills the
+// second accumulator with the next tile. With stream_k set the ranges are [c*total/G,
+// (c+1)*total/G) instead and a tile cut by a boundary is finished by whichever of its
+// contributors arrives last: each stores its fp32 partial tile to a workspace slot and bumps the
+// tile's counter, and the one that sees the final count adds the slots in contributor order (the
+// sum order never depends on timing) and runs the epilogue; nobody waits for another block. That
+// mode balances bytes per SM exactly but measured slower here (the fix-up is exposed at the end
+// of every block), so it is kept for shapes with fewer tiles than SMs only.
+//
+// Roles inside a block (192 threads):
 //   warp 0      TMA producer: cp.async.bulk.tensor 2D loads of the 128x128 B weight tile and the
-//               BT x128 B activation tile into a ring of SWIZZLE_128B stages, mbarrier tx counts
-//   warp 1      TMEM allocation; one lane issues tcgen05.mma (4 per stage, K = 32 each) and
-//               tcgen05.commit to free the stage / publish the accumulator
+//               BT x128 B activation tile into a ring of SWIZZLE_128B stages, mbarrier tx counts.
+//               The first ring of WEIGHT loads is issued before the programmatic-dependency wait.
+//   warp 1      TMEM allocation (two accumulators); one lane issues tcgen05.mma (4 per stage,
+//               K = 32 each) and tcgen05.commit to free the stage / publish an accumulator
 //   warps 2..5  epilogue: tcgen05.ld of the accumulator (lane = channel, column = operand row),
-//               acc_hi + acc_lo/16, scales, bf16/fp32 stores coalesced along the channel
+//               acc_hi + acc_lo/16, scales, bf16/fp32 stores coalesced along the channel; runs
+//               while the MMA warp already fills the other accumulator
 // No TMA multicast and no clusters are used. Every mbarrier wait is bounded: on expiry the block
 // records an error word in host-visible memory, stops issuing work, still frees its TMEM and
 // returns, so a lost signal cannot hang the GPU.
@@ -24,7 +38,7 @@
 
 namespace {
 
-constexpr int BN = 128;       // output channels per block (UMMA_M)
+constexpr int BN = 128;       // output channels per tile (UMMA_M)
 constexpr int BK = 128;       // bytes of K per stage = one 128-byte swizzle atom
 constexpr int UMMA_K = 32;    // bytes (= E4M3 elements) of K per tcgen05.mma
 constexpr uint32_t WAIT_LIMIT = 1u << 22;  // try_wait attempts before giving up (each blocks up to ~1 us)
@@ -36,6 +50,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait for the phase with the given parity. Returns false when the limit expired.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
@@ -84,6 +101,21 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
       : "r"(taddr));
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }  // the 4 epilogue warps
+// Barrier over the 4 epilogue warps that also ORs a predicate: every thread learns whether any
+// of them wants to give up, so all 128 leave the segment loop together and none is left waiting.
+__device__ __forceinline__ bool epi_any(bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, 128, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (one swizzle atom
 // wide), stored densely with the 128-byte swizzle TMA applies: groups of 8 rows are 1024 bytes
@@ -99,12 +131,18 @@ struct TmemArgs {
   const float* sw;
   void* out;
   int out_f32;
-  float* part;
-  int splits;
-  int raw;
-  int* status;  // host-visible error word
-  int prefetch;  // issue the first ring of weight loads before the dependency wait
+  int* status;      // host-visible error word
+  int prefetch;     // issue the first ring of weight loads before the dependency wait
+  int stream_k;     // 1: cut the linear (tile, K block) list evenly; 0: cut it at tile boundaries
+  int tiles_n;      // output tiles along the channels; tile = tt * tiles_n + tn
+  int64_t total;    // tiles * (K / 128)
+  float* ws_part;   // [2 * gridDim.x][BT/2 tokens][128 channels] partial tiles
+  int* ws_count;    // [tiles] contributors that have stored their partial; zero between launches
 };
+
+// Block that owns global K-block index g when `total` indices are cut into G ranges
+// [floor(c*total/G), floor((c+1)*total/G)).
+__device__ __forceinline__ int owner_of(int64_t g, int64_t total, int G) { return (int)(((g + 1) * G + total - 1) / total) - 1; }
 
 template <int BT, int STAGES>
 __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -113,18 +151,23 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
   // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024 the swizzle needs
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int STAGE_BYTES = BN * BK + BT * BK;
-  constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
-  __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_acc;
+  constexpr int ACC_COLS = BT < 32 ? 32 : BT;
+  constexpr int TMEM_COLS = 2 * ACC_COLS;  // two accumulators; 64..512, a power of two
+  __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_acc_full[2], bar_acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
-  __shared__ int abort_flag;
+  __shared__ int abort_flag, last_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, t0 = blockIdx.y * BT;
-  const int Ks = a.K / a.splits, k_begin = blockIdx.z * Ks, nkb = Ks / BK;
+  const int nkb = a.K / BK;
+  const int G = gridDim.x, c = blockIdx.x;
+  const int64_t ntiles = a.total / nkb;
+  const int64_t my_begin = a.stream_k ? (int64_t)c * a.total / G : ((int64_t)c * ntiles / G) * nkb;
+  const int64_t my_end = a.stream_k ? (int64_t)(c + 1) * a.total / G : ((int64_t)(c + 1) * ntiles / G) * nkb;
+  const int n_my = (int)(my_end - my_begin);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
-    mbar_init(smem_u32(&bar_acc), 1);
+    for (int s = 0; s < 2; s++) { mbar_init(smem_u32(&bar_acc_full[s]), 1); mbar_init(smem_u32(&bar_acc_empty[s]), 128); }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -141,81 +184,153 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
   pdl_trigger();
   if (warp == 0) {
     if (lane == 0) {
+      auto coords = [&](int it, int* kx, int* wy, int* xy) {
+        int64_t g = my_begin + it;
+        int tile = (int)(g / nkb), kb = (int)(g - (int64_t)tile * nkb);
+        *kx = kb * BK;
+        *wy = (tile % a.tiles_n) * BN;
+        *xy = (tile / a.tiles_n) * BT;
+      };
       // The weights are constants: their loads for the first ring of stages are issued before the
       // dependency wait, so they stream from HBM while the preceding kernel is still running.
-      const int npre = nkb < STAGES ? nkb : STAGES;
+      const int npre = n_my < STAGES ? n_my : STAGES;
       if (!a.prefetch) pdl_wait();
-      for (int kb = 0; kb < npre; kb++) {
-        uint32_t full = smem_u32(&bar_full[kb]);
+      for (int it = 0; it < npre; it++) {
+        int kx, wy, xy;
+        coords(it, &kx, &wy, &xy);
+        uint32_t full = smem_u32(&bar_full[it]);
         mbar_expect_tx(full, STAGE_BYTES);
-        tma_load_2d(smem_u32(smem + (size_t)kb * STAGE_BYTES), &map_w, k_begin + kb * BK, n0, full);
+        tma_load_2d(smem_u32(smem + (size_t)it * STAGE_BYTES), &map_w, kx, wy, full);
       }
       pdl_wait();
-      for (int kb = 0; kb < npre; kb++)
-        tma_load_2d(smem_u32(smem + (size_t)kb * STAGE_BYTES) + BN * BK, &map_x, k_begin + kb * BK, t0, smem_u32(&bar_full[kb]));
-      for (int kb = npre; kb < nkb; kb++) {
-        int s = kb % STAGES;
-        if (!mbar_wait(smem_u32(&bar_empty[s]), ((kb / STAGES) & 1) ^ 1)) { set_status(a.status, 1); abort_flag = 1; break; }
+      for (int it = 0; it < npre; it++) {
+        int kx, wy, xy;
+        coords(it, &kx, &wy, &xy);
+        tma_load_2d(smem_u32(smem + (size_t)it * STAGE_BYTES) + BN * BK, &map_x, kx, xy, smem_u32(&bar_full[it]));
+      }
+      for (int it = npre; it < n_my; it++) {
+        int s = it % STAGES;
+        if (!mbar_wait(smem_u32(&bar_empty[s]), ((it / STAGES) & 1) ^ 1)) { set_status(a.status, 1); abort_flag = 1; break; }
         if (*(volatile int*)&abort_flag) break;
+        int kx, wy, xy;
+        coords(it, &kx, &wy, &xy);
         uint32_t full = smem_u32(&bar_full[s]);
         uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
         mbar_expect_tx(full, STAGE_BYTES);
-        tma_load_2d(dst, &map_w, k_begin + kb * BK, n0, full);
-        tma_load_2d(dst + BN * BK, &map_x, k_begin + kb * BK, t0, full);
+        tma_load_2d(dst, &map_w, kx, wy, full);
+        tma_load_2d(dst + BN * BK, &map_x, kx, xy, full);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // instruction descriptor: D = F32 (bits 4-5 = 1), A = B = E4M3 (0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
       constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BT >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
-      bool ok = true;
-      for (int kb = 0; kb < nkb && ok; kb++) {
-        int s = kb % STAGES;
-        if (!mbar_wait(smem_u32(&bar_full[s]), (kb / STAGES) & 1)) { set_status(a.status, 2); abort_flag = 1; ok = false; break; }
+      int seg = -1;  // segment = run of K blocks of one tile inside this block's range
+      for (int it = 0; it < n_my; it++) {
+        const int kb = (int)((my_begin + it) % nkb);
+        const bool seg_first = it == 0 || kb == 0;
+        const bool seg_last = it == n_my - 1 || kb == nkb - 1;
+        if (seg_first) {
+          seg++;
+          // the epilogue must have drained this accumulator (it was used two segments ago)
+          if (seg >= 2 && !mbar_wait(smem_u32(&bar_acc_empty[seg & 1]), ((seg >> 1) & 1) ^ 1)) { set_status(a.status, 4); abort_flag = 1; break; }
+          tc_fence_after();
+        }
+        const int s = it % STAGES;
+        if (!mbar_wait(smem_u32(&bar_full[s]), (it / STAGES) & 1)) { set_status(a.status, 2); abort_flag = 1; break; }
         tc_fence_after();
-        uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
-        uint64_t da = smem_desc(sa), db = smem_desc(sa + BN * BK);
+        const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+        const uint64_t da = smem_desc(sa), db = smem_desc(sa + BN * BK);
+        const uint32_t acc = tmem + (uint32_t)((seg & 1) * ACC_COLS);
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; k++) {
           // +32 bytes of K inside the swizzle atom = +2 in the (address >> 4) field
-          tc_mma_f8(tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc, (kb | k) ? 1u : 0u);
+          tc_mma_f8(acc, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc, (!seg_first || k) ? 1u : 0u);
         }
         tc_commit(smem_u32(&bar_empty[s]));  // stage is free once these MMAs have read it
+        if (seg_last) tc_commit(smem_u32(&bar_acc_full[seg & 1]));  // accumulator complete
       }
-      tc_commit(smem_u32(&bar_acc));  // accumulator complete (arrives after all prior MMAs)
     }
   } else {
     // epilogue: warp w may touch TMEM lanes [32*(w%4), +32)
     const int lg = warp & 3;
-    const int n = n0 + lg * 32 + lane;
-    pdl_wait();  // the scales and the output buffers belong to the dependency chain
-    bool ok = mbar_wait(smem_u32(&bar_acc), 0);
-    if (!ok) { if (lane == 0) set_status(a.status, 3); }
-    ok = ok && !*(volatile int*)&abort_flag;
-    tc_fence_after();
-    if (ok) {
-      const bool raw = a.raw || a.splits > 1;
-      const float swn = (!raw && n < a.N) ? a.sw[n] : 0.f;
+    const int ch = lg * 32 + lane;  // channel within the tile
+    pdl_wait();  // the scales, the workspace and the output buffers belong to the dependency chain
+    int seg = -1;
+    int it = 0;
+    while (it < n_my) {
+      const int64_t g0 = my_begin + it;
+      const int tile = (int)(g0 / nkb), kb0 = (int)(g0 - (int64_t)tile * nkb);
+      const int len = min(nkb - kb0, n_my - it);
+      seg++;
+      it += len;
+      bool bad = !mbar_wait(smem_u32(&bar_acc_full[seg & 1]), (seg >> 1) & 1);
+      if (bad && lane == 0) set_status(a.status, 3);
+      if (epi_any(bad || *(volatile int*)&abort_flag)) break;
+      tc_fence_after();
+      const uint32_t acc = tmem + (uint32_t)((seg & 1) * ACC_COLS) + ((uint32_t)(lg * 32) << 16);
+      const int n = (tile % a.tiles_n) * BN + ch;
+      const int t0 = (tile / a.tiles_n) * BT;
+      const bool whole = len == nkb;
+      const float swn = n < a.N ? a.sw[n] : 0.f;
+      auto finish = [&](int tok, float v) {
+        if (tok < a.M && n < a.N) {
+          float y = __fmul_rn(__fmul_rn(v, a.sx[tok]), swn);
+          if (a.out_f32) ((float*)a.out)[(int64_t)tok * a.N + n] = y;
+          else ((bf16*)a.out)[(int64_t)tok * a.N + n] = __float2bfloat16_rn(y);
+        }
+      };
+      // a block has at most two cut tiles: its first segment (slot 2c) and its last one (slot 2c+1)
+      float* my_part = a.ws_part + (size_t)(2 * c + (seg == 0 ? 0 : 1)) * (BT / 2) * BN;
 #pragma unroll 1
       for (int grp = 0; grp < BT / 16; grp++) {
         uint32_t r[16];
-        tc_ld16(tmem + ((uint32_t)(lg * 32) << 16) + (uint32_t)(grp * 16), r);
+        tc_ld16(acc + (uint32_t)(grp * 16), r);
         tc_wait_ld();
-        const int tok0 = ((t0 + grp * 16) >> 1);  // operand rows 16g.. hold tokens 8g..
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-          int tok = tok0 + j;
-          if (tok < a.M && n < a.N) {
-            float v = __fadd_rn(__uint_as_float(r[j]), __fmul_rn(0.0625f, __uint_as_float(r[8 + j])));
-            if (raw) {
-              a.part[((int64_t)blockIdx.z * a.M + tok) * a.N + n] = v;
-            } else {
-              float y = __fmul_rn(__fmul_rn(v, a.sx[tok]), swn);
-              if (a.out_f32) ((float*)a.out)[(int64_t)tok * a.N + n] = y;
-              else ((bf16*)a.out)[(int64_t)tok * a.N + n] = __float2bfloat16_rn(y);
+          float v = __fadd_rn(__uint_as_float(r[j]), __fmul_rn(0.0625f, __uint_as_float(r[8 + j])));
+          if (whole) finish(((t0 + grp * 16) >> 1) + j, v);  // operand rows 16g.. hold tokens 8g..
+          else my_part[(size_t)(grp * 8 + j) * BN + ch] = v;
+        }
+      }
+      // the accumulator is drained: hand it back to the MMA warp
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bar_acc_empty[seg & 1]));
+      if (!whole) {
+        // the last contributor of the tile adds the partial tiles in contributor order and finishes it
+        const int64_t tg0 = (int64_t)tile * nkb;
+        const int c_first = owner_of(tg0, a.total, G), c_last = owner_of(tg0 + nkb - 1, a.total, G);
+        __threadfence();
+        epi_bar();
+        if (warp == 2 && lane == 0) {
+          int old = atomicAdd(&a.ws_count[tile], 1);
+          int last = old == c_last - c_first;
+          if (last) a.ws_count[tile] = 0;  // ready for the next launch
+          last_flag = last;
+        }
+        epi_bar();
+        if (last_flag) {
+          __threadfence();
+          // 32 tokens at a time: all loads of one contributor are independent and in flight together
+          constexpr int TCH = BT / 2 < 32 ? BT / 2 : 32;
+#pragma unroll 1
+          for (int tk0 = 0; tk0 < BT / 2; tk0 += TCH) {
+            float v[TCH];
+#pragma unroll
+            for (int u = 0; u < TCH; u++) v[u] = 0.f;
+            for (int cc = c_first; cc <= c_last; cc++) {
+              // contributor cc starts inside this tile -> its first segment (slot 2cc), else its last one
+              const int64_t cb = (int64_t)cc * a.total / G;
+              const float* p = a.ws_part + (size_t)(2 * cc + (cb >= tg0 ? 0 : 1)) * (BT / 2) * BN + (size_t)tk0 * BN + ch;
+#pragma unroll
+              for (int u = 0; u < TCH; u++) v[u] += __ldcg(p + (size_t)u * BN);
             }
+#pragma unroll
+            for (int u = 0; u < TCH; u++) finish((t0 >> 1) + tk0 + u, v[u]);
           }
         }
+        epi_bar();  // last_flag is reused by the next segment
       }
     }
   }
@@ -253,8 +368,28 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_
   return STRICTB200_OK;
 }
 
+// Stream-K workspace of a context: tile counters (zero between launches) then partial tiles.
+int gemm_workspace(strictb200_ctx* ctx, size_t count_bytes, size_t part_bytes, int** count, float** part) {
+  count_bytes = (count_bytes + 255) & ~(size_t)255;
+  if (count_bytes > ctx->gemm_count_bytes || part_bytes > ctx->gemm_part_bytes) {
+    SB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->gemm_ws) SB_CUDA(cudaFree(ctx->gemm_ws));
+    ctx->gemm_ws = nullptr;
+    size_t cb = count_bytes > ctx->gemm_count_bytes ? count_bytes * 2 : ctx->gemm_count_bytes;
+    size_t pb = part_bytes > ctx->gemm_part_bytes ? part_bytes : ctx->gemm_part_bytes;
+    ctx->gemm_count_bytes = ctx->gemm_part_bytes = 0;
+    SB_CUDA(cudaMalloc(&ctx->gemm_ws, cb + pb));
+    SB_CUDA(cudaMemsetAsync(ctx->gemm_ws, 0, cb, ctx->stream));
+    ctx->gemm_count_bytes = cb;
+    ctx->gemm_part_bytes = pb;
+  }
+  *count = (int*)ctx->gemm_ws;
+  *part = (float*)((char*)ctx->gemm_ws + ctx->gemm_count_bytes);
+  return STRICTB200_OK;
+}
+
 template <int BT, int STAGES>
-int launch(strictb200_ctx* ctx, const GemmArgs& g, const TmemArgs& ta) {
+int launch(strictb200_ctx* ctx, const GemmArgs& g, TmemArgs ta) {
   constexpr int STAGE_BYTES = BN * BK + BT * BK;
   size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;  // + slack for the 1024-byte round-up
   static bool attr = false;
@@ -265,26 +400,33 @@ int launch(strictb200_ctx* ctx, const GemmArgs& g, const TmemArgs& ta) {
   CUtensorMap mw, mx;
   SB_TRY(make_map(&mw, g.wq, g.N, g.K, g.ldw, BN));
   SB_TRY(make_map(&mx, g.xq, ta.Mq, g.K, g.ldx, BT));
-  dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((ta.Mq + BT - 1) / BT), (unsigned)g.splits);
-  if (grid.y > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: M too large for one launch");
-  SB_CUDA(sb_launch(ctx, gemm_tmem_kernel<BT, STAGES>, grid, dim3(192), smem, mw, mx, ta));
+  const int64_t tiles_n = (g.N + BN - 1) / BN, tiles_t = (ta.Mq + BT - 1) / BT, tiles = tiles_n * tiles_t;
+  if (tiles > INT32_MAX / 2) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: too many output tiles");
+  ta.tiles_n = (int)tiles_n;
+  ta.total = tiles * (g.K / BK);
+  ta.stream_k = tiles < ctx->sm_count;
+  int64_t cap = ta.stream_k ? ta.total : tiles;
+  int64_t grid = ctx->sm_count < cap ? ctx->sm_count : cap;  // one persistent block per SM
+  SB_TRY(gemm_workspace(ctx, (size_t)tiles * sizeof(int), (size_t)2 * grid * (BT / 2) * BN * sizeof(float), &ta.ws_count, &ta.ws_part));
+  SB_CUDA(sb_launch(ctx, gemm_tmem_kernel<BT, STAGES>, dim3((unsigned)grid), dim3(192), smem, mw, mx, ta));
   ctx->launches++;
   return STRICTB200_OK;
 }
 
 }  // namespace
 
+int k_gemm_fp8_tmem_split(strictb200_ctx* ctx, const GemmArgs& g);  // gemm_tmem_split.cu
+
 int k_gemm_fp8_tmem(strictb200_ctx* ctx, const GemmArgs& g) {
-  if (g.K % BK || g.splits < 1 || g.K % (g.splits * BK))
-    return sb_fail(STRICTB200_ERR_UNSUPPORTED, "tensor-memory GEMM needs K (per split) to be a multiple of 128");
+  if (g.K % BK) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "tensor-memory GEMM needs K to be a multiple of 128");
+  if (sb_qrows(g.M) <= 256) return k_gemm_fp8_tmem_split(ctx, g);  // one tile of tokens: one tile per block + K splits
+  if (g.splits != 1 || g.raw) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "the persistent tensor-memory GEMM produces complete outputs");
   if (((uintptr_t)g.xq | (uintptr_t)g.wq | (uintptr_t)g.ldx | (uintptr_t)g.ldw) & 15)
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: operands and row strides must be 16-byte aligned");
-  if ((g.splits > 1 || g.raw) && !g.part) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: split-K needs a partial buffer");
   SB_TRY(get_encode());
-  TmemArgs ta{(int)g.M, (int)sb_qrows(g.M), (int)g.N, (int)g.K, g.sx, g.sw, g.out, g.out_f32, g.part, g.splits, g.raw, ctx->d_status, getenv("STRICTB200_PREFETCH") ? atoi(getenv("STRICTB200_PREFETCH")) : 1};
-  // BT = operand rows per block: the whole (split) batch for decode, 256 for prefill
-  if (ta.Mq <= 32) return launch<32, 5>(ctx, g, ta);
-  if (ta.Mq <= 64) return launch<64, 4>(ctx, g, ta);
-  if (ta.Mq <= 128) return launch<128, 4>(ctx, g, ta);
-  return launch<256, 4>(ctx, g, ta);
+  static const int prefetch = getenv("STRICTB200_PREFETCH") ? atoi(getenv("STRICTB200_PREFETCH")) : 1;
+  TmemArgs ta{};
+  ta.M = (int)g.M; ta.Mq = (int)sb_qrows(g.M); ta.N = (int)g.N; ta.K = (int)g.K;
+  ta.sx = g.sx; ta.sw = g.sw; ta.out = g.out; ta.out_f32 = g.out_f32; ta.status = ctx->d_status; ta.prefetch = prefetch;
+  return launch<256, 4>(ctx, g, ta);  // 128 x 256 tiles, 4 stages x 48 KB, two 256-column accumulators
 }
