@@ -150,6 +150,9 @@ def run_ours(args, rank, world, local_rank):
             N.check(N.lib().strictb200_tp_unique_id(N.ptr(h)))
             return h
         ctx.tp_init(world, rank, N.ptr(tp.share_unique_id(dist, rank, make_id, "cuda")))
+        if os.environ.get("STRICTB200_FUSED_AR", "1") != "0":
+            # decode all-reduces: one-shot over peer memory, fused into the consuming row kernel
+            ctx.tp_open_peer_buffers(lambda mine: tp.all_gather_bytes(dist, mine, "cuda"))
     cfg = dict(sb.CONFIGS["qwen3-8b"])
     if args.layers:
         cfg["n_layers"] = args.layers  # profiling aid: same kernels and shapes, fewer layers resident
@@ -241,7 +244,12 @@ def run_ours(args, rank, world, local_rank):
                 "step": {"algorithmic_bytes": bytes_step, "achieved": bytes_step / (ms / args.steps * 1e-3) / 1e9,
                          "frac": bytes_step / (ms / args.steps * 1e-3) / 1e9 / hbm}}
     if rank != 0:
+        barrier()
+        kv.dispose(), model.dispose(), ctx.dispose()
+        dist.destroy_process_group()
         return
+    if dist:
+        barrier()
     base, _ = cpu_reference(2, 1) if world == 1 and not args.no_cpu else (None, None)
     line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -256,6 +264,8 @@ def run_ours(args, rank, world, local_rank):
     kv.dispose()
     model.dispose()
     ctx.dispose()
+    if dist:
+        dist.destroy_process_group()
 
 
 def main():

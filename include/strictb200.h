@@ -245,6 +245,16 @@ int strictb200_tp_unique_id(void* h_id128);
 /* Must be called before model_create on that context. world in {1,2,4,8}. */
 int strictb200_tp_init(strictb200_ctx* ctx, int world, int rank, const void* h_id128);
 int strictb200_tp_info(strictb200_ctx* ctx, int* world, int* rank);
+/* Optional one-shot all-reduce over peer memory for the decode step (messages of a few hundred KB,
+ * where NCCL's launch latency dominates): after tp_init every rank asks for the 64-byte CUDA IPC
+ * handle of its exchange buffer, the host gathers the handles of all ranks (rank order, world x 64
+ * bytes) and hands them to every rank. From then on the decode step publishes each rank's fp32
+ * partial projection in its buffer and the following row kernel sums the ranks' buffers with plain
+ * peer loads over NVLink (bounded wait on epoch flags; ERR_TIMEOUT through device_status if a rank
+ * never shows up). All ranks must be processes on one NVLink-connected box. Without these two
+ * calls the decode step uses NCCL. */
+int strictb200_tp_comm_handle(strictb200_ctx* ctx, void* h_handle64);
+int strictb200_tp_comm_open(strictb200_ctx* ctx, const void* h_handles);
 /* fp32 sum all-reduce in place on the context's stream (the collective the model uses). */
 int strictb200_tp_allreduce_f32(strictb200_ctx* ctx, float* d_buf, int64_t count);
 

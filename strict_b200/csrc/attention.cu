@@ -11,6 +11,7 @@
 //
 // Shared-memory tiles hold rows of 128 bf16 (256 B = 16 chunks of 16 B); chunk c of row r
 // lives at chunk c ^ (r & 7), which makes every ldmatrix phase conflict-free.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -19,6 +20,7 @@ namespace {
 
 constexpr int D = 128;
 constexpr int KT = 64;  // keys per tile
+constexpr int DEC_STAGES = 2;  // K/V tile ring of the decode kernel; 3 stages (2 blocks/SM) measured 4 % slower than 2 (3 blocks/SM)
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -227,14 +229,21 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
   const int k_end = min(len, k_begin + chunk);
   const int G = Hq / Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
-  const uint32_t sK = smem_u32(smem), sV = sK + 2 * KT * 256;
+  const uint32_t sK = smem_u32(smem), sV = sK + DEC_STAGES * KT * 256;
   const bf16* kbase = kc + ((int64_t)b * Hkv + hk) * maxlen * D;
   const bf16* vbase = vc + ((int64_t)b * Hkv + hk) * maxlen * D;
   const int ntiles = (k_end - k_begin + KT - 1) / KT;
 
-  load_tile(sK, kbase + (int64_t)k_begin * D, KT, min(KT, k_end - k_begin), 128);
-  load_tile(sV, vbase + (int64_t)k_begin * D, KT, min(KT, k_end - k_begin), 128);
-  cp_async_commit();
+  // prologue: the first DEC_STAGES-1 tiles are in flight before any is consumed (one group per tile)
+#pragma unroll
+  for (int t = 0; t < DEC_STAGES - 1; t++) {
+    if (t < ntiles) {
+      int k0 = k_begin + t * KT;
+      load_tile(sK + t * KT * 256, kbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
+      load_tile(sV + t * KT * 256, vbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
+    }
+    cp_async_commit();
+  }
 
   // Q fragments straight from global: rows = the G query heads of this KV head (zero beyond)
   uint32_t qf[8][4];
@@ -258,17 +267,18 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
   const int mi = lane >> 3, r8 = lane & 7;
 
   for (int t = 0; t < ntiles; t++) {
-    if (t + 1 < ntiles) {
-      int k0 = k_begin + (t + 1) * KT;
-      load_tile(sK + ((t + 1) & 1) * KT * 256, kbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
-      load_tile(sV + ((t + 1) & 1) * KT * 256, vbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
+    {
+      const int tn = t + DEC_STAGES - 1;  // refill the stage consumed in the previous iteration
+      if (tn < ntiles) {
+        int k0 = k_begin + tn * KT;
+        load_tile(sK + (tn % DEC_STAGES) * KT * 256, kbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
+        load_tile(sV + (tn % DEC_STAGES) * KT * 256, vbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
+      }
       cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+      cp_async_wait<DEC_STAGES - 1>();  // all but the newest DEC_STAGES-1 groups: tile t has landed
     }
     __syncthreads();
-    const uint32_t tK = sK + (t & 1) * KT * 256, tV = sV + (t & 1) * KT * 256;
+    const uint32_t tK = sK + (t % DEC_STAGES) * KT * 256, tV = sV + (t % DEC_STAGES) * KT * 256;
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
     for (int ks = 0; ks < 8; ks++) {
@@ -508,7 +518,8 @@ int k_attn_prefill(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf1
 // Keys per block: sized so that a full cache yields about six blocks per SM.
 static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
   int64_t total = (int64_t)maxlen * B * Hkv;
-  int64_t c = total / ((int64_t)ctx->sm_count * 6);
+  static const int per_sm = getenv("STRICTB200_ATTN_BLOCKS_PER_SM") ? atoi(getenv("STRICTB200_ATTN_BLOCKS_PER_SM")) : 6;
+  int64_t c = total / ((int64_t)ctx->sm_count * per_sm);
   c = (c + KT - 1) / KT * KT;
   if (c < 256) c = 256;
   if (c > maxlen) c = (maxlen + KT - 1) / KT * KT;
@@ -528,7 +539,7 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
   int chunk = decode_chunk(ctx, B, Hkv, maxlen);
   if ((maxlen + chunk - 1) / chunk != nsplit) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: split count does not match the cache size");
   static bool attr = false;
-  size_t smem = 4 * KT * 256;  // 64 KB; also covers the 34 KB merge area
+  size_t smem = 2 * DEC_STAGES * KT * 256;  // K and V rings; also covers the 34 KB merge area
   if (!attr) {
     SB_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr = true;

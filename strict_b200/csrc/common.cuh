@@ -12,6 +12,20 @@
 #include "../../include/strictb200.h"
 
 struct TpState;     // tp.cpp
+
+// One-shot all-reduce over peer memory (tp.cpp): every rank owns a buffer that all ranks of the
+// box map (CUDA IPC); a rank publishes its fp32 partial result in its own buffer and raises an
+// epoch flag in every peer's buffer, the consumer kernel waits (bounded) for all flags and adds the
+// ranks' data in rank order with plain peer loads. Passed to kernels by value.
+struct TpCommDev {
+  float* data[8];   // rank r's data area, two epoch parities of max_elems floats each
+  int* flags[8];    // rank r's flag area: flags[parity * 8 + source rank] = last epoch published
+  int* epoch;       // this rank's epoch counter (device memory, advanced by the publish kernel)
+  unsigned* done;   // this rank's block counter of the publish kernel
+  int* status;      // host-visible error word
+  int world, rank;
+  long long max_elems;
+};
 struct SbProfiler;  // model.cu
 
 struct strictb200_ctx {
@@ -104,6 +118,7 @@ struct RowNormArgs {
   int groups = 1, splits = 1;
   const float* sx = nullptr;         // [groups][M]
   const float* sw = nullptr;         // [d]
+  const TpCommDev* comm = nullptr;   // input = sum over ranks of the published partial results (fused all-reduce)
   float* residual_f32 = nullptr;     // [M,d] fp32 residual stream, in/out, may be null
   bf16* residual = nullptr;          // [M,d] bf16 residual, in/out, may be null
   const float* gain = nullptr;       // [d]; null: only the residual update is done
@@ -183,6 +198,9 @@ int k_add_i32(strictb200_ctx*, int32_t* x, const int32_t* inc, int32_t c, int64_
 int k_f32_to_bf16(strictb200_ctx*, const float* x, int64_t n, bf16* y);
 int k_bf16_to_f32(strictb200_ctx*, const bf16* x, int64_t n, float* y);
 // tp.cpp
+const TpCommDev* sb_tp_comm(strictb200_ctx*);  // null unless the peer buffers were opened
+// out[m,n] = (sum_s part[s][m,n]) * sx[m] * sw[n] written to this rank's peer buffer, then published
+int k_tp_publish(strictb200_ctx*, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N);
 int sb_tp_allreduce_f32(strictb200_ctx*, float* buf, int64_t count);
 int sb_tp_allgather(strictb200_ctx*, const void* send, void* recv, int64_t bytes_per_rank);
 void sb_tp_destroy(strictb200_ctx*);

@@ -323,7 +323,11 @@ int qwen_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
     PROF(STRICTB200_K_GEMM_O, run_gemm(m, B, w.wo, b.aq, b.sa, nullptr, 0, b.part, s2, 1));
     {
       RowNormArgs a;
-      if (tp) {
+      if (tp && sb_tp_comm(ctx)) {
+        // one-shot all-reduce over peer memory, fused into the row kernel that consumes it
+        PROF(STRICTB200_K_ALLREDUCE, k_tp_publish(ctx, b.part, s2, b.sa, w.wo.s, B, d));
+        a.comm = sb_tp_comm(ctx);
+      } else if (tp) {
         PROF(STRICTB200_K_ROWNORM, k_reduce_scale(ctx, b.part, s2, b.sa, w.wo.s, B, d, b.red));
         PROF(STRICTB200_K_ALLREDUCE, sb_tp_allreduce_f32(ctx, b.red, B * d));
         a.x_f32 = b.red;
@@ -340,7 +344,10 @@ int qwen_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
     PROF(STRICTB200_K_GEMM_DOWN, run_gemm(m, B, w.wdown, b.aq, b.sa, nullptr, 0, b.part, s4, 1));
     {
       RowNormArgs a;
-      if (tp) {
+      if (tp && sb_tp_comm(ctx)) {
+        PROF(STRICTB200_K_ALLREDUCE, k_tp_publish(ctx, b.part, s4, b.sa, w.wdown.s, B, d));
+        a.comm = sb_tp_comm(ctx);
+      } else if (tp) {
         PROF(STRICTB200_K_ROWNORM, k_reduce_scale(ctx, b.part, s4, b.sa, w.wdown.s, B, d, b.red));
         PROF(STRICTB200_K_ALLREDUCE, sb_tp_allreduce_f32(ctx, b.red, B * d));
         a.x_f32 = b.red;

@@ -17,6 +17,13 @@ __device__ __forceinline__ void load8_bf16(const bf16* p, float* v) {
     v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
   }
 }
+// Peer (or own) buffer read of the fused all-reduce: volatile, so a slot that is rewritten two
+// epochs later is never served from a stale cache line.
+__device__ __forceinline__ float4 ld_peer4(const float* p) {
+  float4 v;
+  asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ void store8_bf16(bf16* p, const float* v) {
   uint32_t w[4];
 #pragma unroll
@@ -78,6 +85,8 @@ __global__ void __launch_bounds__(ROW_THREADS) quantize_weight_rows_kernel(const
 }
 
 struct RowNormDev {
+  TpCommDev comm;
+  int use_comm;
   const float* x_f32;
   const bf16* x_in;
   const float* part;
@@ -97,6 +106,21 @@ __global__ void __launch_bounds__(512) rownorm_kernel(RowNormDev a, int64_t M, i
   const int NT = blockDim.x;
   pdl_trigger();
   pdl_wait();
+  int comm_e = 0;
+  if (a.use_comm) {
+    // Fused all-reduce: wait (bounded) until every rank has published this epoch, then the input
+    // row is the sum, in rank order, of the ranks' partial results read over NVLink.
+    comm_e = *(volatile int*)a.comm.epoch;
+    if ((int)threadIdx.x < a.comm.world) {
+      volatile int* f = a.comm.flags[a.comm.rank] + (comm_e & 1) * 8 + threadIdx.x;
+      uint32_t spins = 0;
+      while (*f - comm_e < 0) {
+        if (++spins > (1u << 24)) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
+        __nanosleep(64);
+      }
+    }
+    __syncthreads();
+  }
   __shared__ float red[32];
   int64_t row = blockIdx.x;
   float v[MAX_CHUNKS][8];
@@ -129,6 +153,15 @@ __global__ void __launch_bounds__(512) rownorm_kernel(RowNormDev a, int64_t M, i
         }
 #pragma unroll
         for (int i = 0; i < 8; i++) t[i] = tot[i];
+      } else if (a.use_comm) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) t[i] = 0.f;
+        for (int r = 0; r < a.comm.world; r++) {
+          const float* p = a.comm.data[r] + (size_t)(comm_e & 1) * a.comm.max_elems + row * d + k;
+          float4 p0 = ld_peer4(p), p1 = ld_peer4(p + 4);
+          t[0] += p0.x; t[1] += p0.y; t[2] += p0.z; t[3] += p0.w;
+          t[4] += p1.x; t[5] += p1.y; t[6] += p1.z; t[7] += p1.w;
+        }
       } else if (a.x_f32) {
         float4 p0 = *(const float4*)(a.x_f32 + row * d + k), p1 = *(const float4*)(a.x_f32 + row * d + k + 4);
         t[0] = p0.x; t[1] = p0.y; t[2] = p0.z; t[3] = p0.w;
@@ -309,7 +342,7 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   int threads = (int)((d / 8 + 31) / 32 * 32);
   threads = threads < 128 ? 128 : (threads > 512 ? 512 : threads);
   while ((int64_t)threads * 8 * MAX_CHUNKS < d) threads += 32;
-  RowNormDev v{a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale};
+  RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale};
   SB_CUDA(sb_launch(ctx, rownorm_kernel, dim3((unsigned)M), dim3(threads), 0, v, M, d));
   ctx->launches++;
   return STRICTB200_OK;

@@ -46,9 +46,59 @@ int nccl_fail(const char* what, int rc) {
 }
 }  // namespace
 
+constexpr long long COMM_MAX_ELEMS = 1 << 20;  // floats per epoch parity (4 MiB): 64 tokens x 16384 channels
+constexpr size_t COMM_FLAG_BYTES = 256;        // 2 parities x 8 source ranks, padded
+constexpr size_t COMM_BYTES = COMM_FLAG_BYTES + 2 * COMM_MAX_ELEMS * sizeof(float);
+
 struct TpState {
   nccl_comm comm = nullptr;
+  // peer-memory all-reduce
+  void* comm_buf = nullptr;       // this rank's buffer: [flags | data parity 0 | data parity 1]
+  void* peer_buf[8] = {nullptr};  // every rank's buffer as mapped into this process
+  int* local = nullptr;           // [epoch, done]
+  bool opened = false;
+  TpCommDev dev{};
 };
+
+// Publish kernel: scaled split-K sum of this rank's partial projection -> own peer buffer, then the
+// last block to finish raises the epoch flag in every rank's buffer.
+__global__ void tp_publish_kernel(const float* __restrict__ part, int splits, const float* __restrict__ sx, const float* __restrict__ sw,
+                                  int64_t M, int64_t N, TpCommDev c) {
+  pdl_trigger();
+  pdl_wait();
+  const int e = *(volatile int*)c.epoch + 1;  // stable during the kernel: only its last block advances it
+  float* out = c.data[c.rank] + (size_t)(e & 1) * c.max_elems;
+  int64_t total = M * N / 4, stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    int64_t m = (i * 4) / N, n = (i * 4) - m * N;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; s++) {
+      float4 p = *(const float4*)(part + ((int64_t)s * M + m) * N + n);
+      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    float a = sx[m];
+    float4 w = *(const float4*)(sw + n);
+    float4 r;
+    r.x = __fmul_rn(__fmul_rn(acc.x, a), w.x); r.y = __fmul_rn(__fmul_rn(acc.y, a), w.y);
+    r.z = __fmul_rn(__fmul_rn(acc.z, a), w.z); r.w = __fmul_rn(__fmul_rn(acc.w, a), w.w);
+    *(float4*)(out + m * N + n) = r;
+  }
+  // Device-scope fence per thread; the block that takes the last ticket has observed every other
+  // block's writes through the counter and makes all of them visible system-wide with one fence
+  // before it raises the flags in the peers' buffers.
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned ticket = atomicAdd(c.done, 1u);
+    if (ticket == gridDim.x - 1) {
+      *c.done = 0;
+      *(volatile int*)c.epoch = e;
+      __threadfence_system();
+      for (int r = 0; r < c.world; r++) *(volatile int*)(c.flags[r] + (e & 1) * 8 + c.rank) = e;
+      __threadfence_system();
+    }
+  }
+}
 
 int sb_tp_allreduce_f32(strictb200_ctx* ctx, float* buf, int64_t count) {
   if (ctx->tp_world == 1) return STRICTB200_OK;
@@ -65,8 +115,24 @@ int sb_tp_allgather(strictb200_ctx* ctx, const void* send, void* recv, int64_t b
   if (rc) return nccl_fail("ncclAllGather", rc);
   return STRICTB200_OK;
 }
+const TpCommDev* sb_tp_comm(strictb200_ctx* ctx) { return ctx->tp && ctx->tp->opened ? &ctx->tp->dev : nullptr; }
+
+int k_tp_publish(strictb200_ctx* ctx, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N) {
+  if (!ctx->tp || !ctx->tp->opened) return sb_fail(STRICTB200_ERR_INVALID_ARG, "peer buffers are not open");
+  if (N % 4 || M * N > COMM_MAX_ELEMS) return sb_fail(STRICTB200_ERR_INVALID_ARG, "tp_publish: result does not fit the peer buffer");
+  int64_t blocks = (M * N / 4 + 255) / 256;
+  int grid = (int)(blocks < 1 ? 1 : (blocks > ctx->sm_count ? ctx->sm_count : blocks));
+  SB_CUDA(sb_launch(ctx, tp_publish_kernel, dim3(grid), dim3(256), 0, part, splits, sx, sw, M, N, ctx->tp->dev));
+  ctx->launches++;
+  return STRICTB200_OK;
+}
+
 void sb_tp_destroy(strictb200_ctx* ctx) {
   if (ctx->tp) {
+    for (int r = 0; r < 8; r++)
+      if (ctx->tp->peer_buf[r] && ctx->tp->peer_buf[r] != ctx->tp->comm_buf) cudaIpcCloseMemHandle(ctx->tp->peer_buf[r]);
+    if (ctx->tp->comm_buf) cudaFree(ctx->tp->comm_buf);
+    if (ctx->tp->local) cudaFree(ctx->tp->local);
     if (ctx->tp->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->tp->comm);
     delete ctx->tp;
     ctx->tp = nullptr;
@@ -102,6 +168,49 @@ int strictb200_tp_init(strictb200_ctx* ctx, int world, int rank, const void* h_i
   ctx->tp = tp;
   ctx->tp_world = world;
   ctx->tp_rank = rank;
+  return STRICTB200_OK;
+}
+int strictb200_tp_comm_handle(strictb200_ctx* ctx, void* h_handle64) {
+  SB_ENTER(ctx);
+  SB_REQUIRE(h_handle64, "null handle buffer");
+  SB_REQUIRE(ctx->tp && ctx->tp_world > 1, "tensor parallelism is not initialised on this context");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  TpState* tp = ctx->tp;
+  if (!tp->comm_buf) {
+    SB_CUDA(cudaMalloc(&tp->comm_buf, COMM_BYTES));
+    SB_CUDA(cudaMemset(tp->comm_buf, 0, COMM_BYTES));
+    SB_CUDA(cudaMalloc((void**)&tp->local, 256));
+    SB_CUDA(cudaMemset(tp->local, 0, 256));
+  }
+  cudaIpcMemHandle_t h;
+  SB_CUDA(cudaIpcGetMemHandle(&h, tp->comm_buf));
+  memcpy(h_handle64, &h, 64);
+  return STRICTB200_OK;
+}
+int strictb200_tp_comm_open(strictb200_ctx* ctx, const void* h_handles) {
+  SB_ENTER(ctx);
+  SB_REQUIRE(h_handles, "null handle buffer");
+  SB_REQUIRE(ctx->tp && ctx->tp->comm_buf, "call strictb200_tp_comm_handle first");
+  TpState* tp = ctx->tp;
+  SB_REQUIRE(!tp->opened, "peer buffers already open");
+  for (int r = 0; r < ctx->tp_world; r++) {
+    if (r == ctx->tp_rank) { tp->peer_buf[r] = tp->comm_buf; continue; }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, (const char*)h_handles + 64 * r, 64);
+    SB_CUDA(cudaIpcOpenMemHandle(&tp->peer_buf[r], h, cudaIpcMemLazyEnablePeerAccess));
+  }
+  TpCommDev& d = tp->dev;
+  for (int r = 0; r < ctx->tp_world; r++) {
+    d.flags[r] = (int*)tp->peer_buf[r];
+    d.data[r] = (float*)((char*)tp->peer_buf[r] + COMM_FLAG_BYTES);
+  }
+  d.epoch = tp->local;
+  d.done = (unsigned*)(tp->local + 1);
+  d.status = ctx->d_status;
+  d.world = ctx->tp_world;
+  d.rank = ctx->tp_rank;
+  d.max_elems = COMM_MAX_ELEMS;
+  tp->opened = true;
   return STRICTB200_OK;
 }
 int strictb200_tp_info(strictb200_ctx* ctx, int* world, int* rank) {

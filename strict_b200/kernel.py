@@ -49,6 +49,14 @@ class Context:
     def tp_init(self, world, rank, unique_id):
         N.check(N.lib().strictb200_tp_init(self.h, world, rank, unique_id))
 
+    def tp_open_peer_buffers(self, all_gather):
+        """Enable the fused peer-memory all-reduce: all_gather(uint8[64]) -> uint8[world, 64] must
+        return every rank's array in rank order (any host transport)."""
+        mine = np.zeros(64, np.uint8)
+        N.check(N.lib().strictb200_tp_comm_handle(self.h, N.ptr(mine)))
+        handles = np.ascontiguousarray(all_gather(mine), dtype=np.uint8)
+        N.check(N.lib().strictb200_tp_comm_open(self.h, N.ptr(handles)))
+
     def dispose(self):
         if self.h:
             N.lib().strictb200_destroy(self.h)

@@ -93,6 +93,8 @@ SIGNATURES = {
     "strictb200_tp_unique_id": [vp],
     "strictb200_tp_init": [vp, i32, i32, vp],
     "strictb200_tp_info": [vp, C.POINTER(i32), C.POINTER(i32)],
+    "strictb200_tp_comm_handle": [vp, vp],
+    "strictb200_tp_comm_open": [vp, vp],
     "strictb200_tp_allreduce_f32": [vp, vp, i64],
 }
 

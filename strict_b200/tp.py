@@ -44,3 +44,12 @@ def max_over_ranks(dist, value, device="cpu"):
     t = torch.tensor([float(value)], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+def all_gather_bytes(dist, mine, device="cpu"):
+    """Gather a small uint8 array from every rank, rank order -> uint8[world, len]."""
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(mine, dtype=np.uint8)).to(device)
+    out = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, t)
+    return np.stack([o.cpu().numpy() for o in out])

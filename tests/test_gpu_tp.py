@@ -21,7 +21,7 @@ def _gpu_count():
         return 0
 
 
-def _worker(rank, world, port, path, out):
+def _worker(rank, world, port, path, out, fused):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
     import strict_b200 as sb
@@ -35,6 +35,8 @@ def _worker(rank, world, port, path, out):
             N.check(N.lib().strictb200_tp_unique_id(N.ptr(h)))
             return h
         ctx.tp_init(world, rank, N.ptr(tp.share_unique_id(dist, rank, make_id)))
+        if fused:
+            ctx.tp_open_peer_buffers(lambda mine: tp.all_gather_bytes(dist, mine))
         m = sb.Model(ctx, CFG).init_random(11)
         from oracle import oracle as O
         toks = O.gen_tokens(12, 1, 3 * 20, CFG["vocab"]).reshape(3, 20)
@@ -42,6 +44,7 @@ def _worker(rank, world, port, path, out):
         kv = m.new_cache(3, 64)
         nxt, logits = kv.prefill(toks, lens, want_logits=True)
         ids = kv.generate(nxt, 16)
+        assert ctx.device_status() == 0
         if rank == 0:
             np.savez(path, nxt=nxt, logits=logits, ids=ids, toks=toks, lens=lens)
         dist.barrier()
@@ -52,14 +55,15 @@ def _worker(rank, world, port, path, out):
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
-def test_tp2_matches_oracle(oracle, tmp_path):
+@pytest.mark.parametrize("fused", [False, True], ids=["nccl", "peer-memory"])
+def test_tp2_matches_oracle(oracle, tmp_path, fused):
     import torch.multiprocessing as mp
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     out = mp.Manager().dict()
     path = str(tmp_path / "tp2.npz")
-    mp.spawn(_worker, args=(2, port, path, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, path, out, fused), nprocs=2, join=True)
     assert dict(out) == {0: True, 1: True}
     r = np.load(path)
     om = oracle.Model(CFG, 11)

@@ -57,9 +57,11 @@ def _worker(rank, world, port, out):
             res[name] = (mine, want)
         uid = tp.share_unique_id(dist, rank, lambda: np.arange(128, dtype=np.uint8) ^ 0x5A)
         mx = tp.max_over_ranks(dist, 1.5 + rank)
+        gathered = tp.all_gather_bytes(dist, np.full(64, rank, np.uint8))
         ok = all(np.allclose(g, w, rtol=1e-5, atol=1e-6 * np.abs(w).max()) for g, w in res.values())
         ok = ok and np.array_equal(res["wqkv"][0], res["wqkv"][1])  # column shards are exact
         ok = ok and np.array_equal(uid, np.arange(128, dtype=np.uint8) ^ 0x5A) and mx == 1.5 + world - 1
+        ok = ok and gathered.shape == (world, 64) and all((gathered[r] == r).all() for r in range(world))
         out[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
