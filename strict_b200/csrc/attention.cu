@@ -28,6 +28,10 @@ __device__ __forceinline__ void cp_async16(uint32_t s, const void* g, bool valid
   int sz = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(g), "r"(sz));
 }
+__device__ __forceinline__ void cp_async16_hint(uint32_t s, const void* g, bool valid, uint64_t policy) {
+  int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;\n" ::"r"(s), "l"(g), "r"(sz), "l"(policy));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
@@ -64,6 +68,16 @@ __device__ __forceinline__ void load_tile(uint32_t tile, const bf16* src, int ro
     int r = c >> 4, cc = c & 15;
     bool v = r < valid_rows;
     cp_async16(tile + tile_off(r, cc), src + (int64_t)(v ? r : 0) * D + cc * 8, v);
+  }
+}
+
+// Same, with an L2 eviction policy on the global reads (the decode kernel reads every key and
+// value exactly once).
+__device__ __forceinline__ void load_tile_hint(uint32_t tile, const bf16* src, int rows, int valid_rows, int nthreads, uint64_t policy) {
+  for (int c = threadIdx.x; c < rows * 16; c += nthreads) {
+    int r = c >> 4, cc = c & 15;
+    bool v = r < valid_rows;
+    cp_async16_hint(tile + tile_off(r, cc), src + (int64_t)(v ? r : 0) * D + cc * 8, v, policy);
   }
 }
 
@@ -234,13 +248,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
   const bf16* vbase = vc + ((int64_t)b * Hkv + hk) * maxlen * D;
   const int ntiles = (k_end - k_begin + KT - 1) / KT;
 
+  const uint64_t kv_policy = l2_evict_first_policy();
   // prologue: the first DEC_STAGES-1 tiles are in flight before any is consumed (one group per tile)
 #pragma unroll
   for (int t = 0; t < DEC_STAGES - 1; t++) {
     if (t < ntiles) {
       int k0 = k_begin + t * KT;
-      load_tile(sK + t * KT * 256, kbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
-      load_tile(sV + t * KT * 256, vbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
+      load_tile_hint(sK + t * KT * 256, kbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128, kv_policy);
+      load_tile_hint(sV + t * KT * 256, vbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128, kv_policy);
     }
     cp_async_commit();
   }
@@ -271,8 +286,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
       const int tn = t + DEC_STAGES - 1;  // refill the stage consumed in the previous iteration
       if (tn < ntiles) {
         int k0 = k_begin + tn * KT;
-        load_tile(sK + (tn % DEC_STAGES) * KT * 256, kbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
-        load_tile(sV + (tn % DEC_STAGES) * KT * 256, vbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128);
+        load_tile_hint(sK + (tn % DEC_STAGES) * KT * 256, kbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128, kv_policy);
+        load_tile_hint(sV + (tn % DEC_STAGES) * KT * 256, vbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128, kv_policy);
       }
       cp_async_commit();
       cp_async_wait<DEC_STAGES - 1>();  // all but the newest DEC_STAGES-1 groups: tile t has landed
@@ -433,6 +448,63 @@ __global__ void __launch_bounds__(CB_THREADS) attn_combine_kernel(const float* _
   }
 }
 
+// The decode-step shape of the merge: one thread per 8-dim group of the token's attention row
+// (blockDim.x == Hq * 16 <= 512), at most 8 key chunks. Every partial is loaded in one batch
+// together with the sequence length (slots of chunks beyond the length hold stale data and are
+// masked out of the arithmetic, which is that of the kernel above).
+__global__ void __launch_bounds__(512) attn_combine_decode_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
+                                                                  const int32_t* __restrict__ lens, int len_add, int Hq, int maxlen, int chunk,
+                                                                  int nsplit, bf16* __restrict__ out, uint8_t* __restrict__ q_out,
+                                                                  float* __restrict__ qscale) {
+  __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.x;
+  const int e8 = threadIdx.x, h = e8 >> 4, d = (e8 & 15) * 8;
+  const int64_t base = ((int64_t)b * Hq + h) * nsplit;
+  const int len_raw = lens[b];
+  float2 ml[8];
+  float4 o[8][2];
+#pragma unroll
+  for (int s = 0; s < 8; s++)
+    if (s < nsplit) {
+      ml[s] = *(const float2*)(ml_part + (base + s) * 2);
+      const float4* op = (const float4*)(o_part + (base + s) * D + d);
+      o[s][0] = op[0];
+      o[s][1] = op[1];
+    }
+  const int len = min(len_raw + len_add, maxlen);
+  const int ns = (len + chunk - 1) / chunk;
+  float M = -INFINITY;
+#pragma unroll
+  for (int s = 0; s < 8; s++)
+    if (s < ns) M = fmaxf(M, ml[s].x);
+  float L = 0.f, O[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int s = 0; s < 8; s++)
+    if (s < ns) {
+      float f = exp2f(ml[s].x - M);
+      L += ml[s].y * f;
+      O[0] += o[s][0].x * f; O[1] += o[s][0].y * f; O[2] += o[s][0].z * f; O[3] += o[s][0].w * f;
+      O[4] += o[s][1].x * f; O[5] += o[s][1].y * f; O[6] += o[s][1].z * f; O[7] += o[s][1].w * f;
+    }
+  float v[8], amax = 0.f;
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    v[i] = ns > 0 ? round_bf16(O[i] / L) : 0.f;
+    amax = fmaxf(amax, fabsf(v[i]));
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+  *(uint4*)(out + ((int64_t)b * Hq + h) * D + d) = make_uint4(w[0], w[1], w[2], w[3]);
+  if (!q_out) return;
+  amax = block_max(amax, red);
+  int ex = sb_scale_exponent(amax);
+  if (threadIdx.x == 0) qscale[b] = sb_pow2(ex);
+  sb_store_split8(q_out, (int64_t)Hq * D, b, (int64_t)e8 * 8, v, sb_pow2(-ex));
+}
+
 // ------------------------------------------------------------------ fp32 attention (GPT-2 path)
 __global__ void kv_append_f32_kernel(const float* __restrict__ qkv, float* __restrict__ kc, float* __restrict__ vc,
                                      const int32_t* __restrict__ seq, const int32_t* __restrict__ pos, const int32_t* __restrict__ lens, int H,
@@ -550,6 +622,12 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
   dim3 grid(nsplit, Hkv, B);
   SB_CUDA(sb_launch(ctx, attn_decode_kernel, grid, dim3(128), smem, q, kc, vc, lens, len_add, B, Hq, Hkv, maxlen, chunk, nsplit, scale * LOG2E, o_part, ml_part));
   ctx->launches++;
+  if (nsplit <= 8 && Hq * 16 <= 512 && (Hq * 16) % 32 == 0) {
+    SB_CUDA(sb_launch(ctx, attn_combine_decode_kernel, dim3(B), dim3((unsigned)(Hq * 16)), 0, (const float*)o_part, (const float*)ml_part, lens, len_add, Hq,
+                      maxlen, chunk, nsplit, out, q_out, qscale_out));
+    ctx->launches++;
+    return STRICTB200_OK;
+  }
   SB_CUDA(sb_launch(ctx, attn_combine_kernel, dim3(B), dim3(CB_THREADS), 0, o_part, ml_part, lens, len_add, Hq, maxlen, chunk, nsplit, out, q_out, qscale_out));
   ctx->launches++;
   return STRICTB200_OK;

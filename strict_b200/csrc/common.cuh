@@ -215,6 +215,14 @@ void sb_tp_destroy(strictb200_ctx*);
 // Without the launch attribute both are no-ops.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// L2 eviction policy for data that is read exactly once per step (weights, the KV cache): such
+// lines are the first to be replaced, so the 126 MB L2 keeps the small tensors the kernels hand
+// to each other, the scale/gain vectors and the kernels' own instructions resident.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
 template <typename... KArgs, typename... Args>
 inline cudaError_t sb_launch(strictb200_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
@@ -228,6 +236,37 @@ inline cudaError_t sb_launch(strictb200_ctx* ctx, void (*kernel)(KArgs...), dim3
   cfg.attrs = attr;
   cfg.numAttrs = ctx->pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+// Same, as thread-block clusters of `cluster` blocks (the grid must be a multiple of it).
+template <typename... KArgs, typename... Args>
+inline cudaError_t sb_launch_cluster(strictb200_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, dim3 cluster, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster.x;
+  attr[0].val.clusterDim.y = cluster.y;
+  attr[0].val.clusterDim.z = cluster.z;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+// Cluster barrier (all threads of all blocks of the cluster) and a read of another block's
+// shared memory through the cluster's distributed shared memory window.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* own_smem, uint32_t cta_rank) {
+  uint32_t local = (uint32_t)__cvta_generic_to_shared(own_smem), remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
 }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

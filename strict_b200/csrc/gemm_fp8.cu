@@ -265,18 +265,22 @@ int launch_skinny(strictb200_ctx* ctx, const GemmDev& d) {
 
 // Number of K splits for a skinny GEMM so that the grid covers the SMs about twice.
 int sb_gemm_pick_splits(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K) {
-  if (M > 32) return 1;
-  int64_t tiles = (N + SK_ROWS - 1) / SK_ROWS;
-  int s = 1;
+  if (M > 32 || K % 128) return 1;
+  const int64_t tiles = (N + SK_ROWS - 1) / SK_ROWS, nkb = K / 128;
+  // About 1.6 blocks per SM (two blocks of this kernel fit an SM, so all of them are resident
+  // at once and share its bandwidth) measured best on the decode shapes; more than 8 partial
+  // results are not taken by the kernels that sum them.
   static int target = getenv("STRICTB200_SPLIT_TARGET") ? atoi(getenv("STRICTB200_SPLIT_TARGET")) : 0;
-  int64_t want = target ? target : (int64_t)ctx->sm_count * 3 / 2;
-  while (tiles * s < want && s < 16 && K % (2 * s * 64) == 0 && K / (2 * s) >= 512) s *= 2;
-  return s;
+  const int64_t want = target ? target : (int64_t)ctx->sm_count * 13 / 8;
+  int64_t s = (want + tiles - 1) / tiles;
+  while (s > 1 && tiles * s > 2 * (int64_t)ctx->sm_count) s--;
+  if (s > nkb / 2) s = nkb / 2;  // at least two k-blocks per split
+  return (int)(s < 1 ? 1 : (s > 8 ? 8 : s));
 }
 
 int k_gemm_fp8(strictb200_ctx* ctx, const GemmArgs& g) {
   if (g.K % 64 || g.N % 16) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: K must be a multiple of 64 and N of 16");
-  if (g.splits < 1 || g.K % (g.splits * 64)) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: K/splits must be a multiple of 64");
+  if (g.splits < 1) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: splits must be positive");
   if ((g.splits > 1 || g.raw) && !g.part) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: split-K needs a partial buffer");
   if (((uintptr_t)g.xq | (uintptr_t)g.wq | (uintptr_t)g.ldx | (uintptr_t)g.ldw) & 15)
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: operands and row strides must be 16-byte aligned");
@@ -286,8 +290,9 @@ int k_gemm_fp8(strictb200_ctx* ctx, const GemmArgs& g) {
   if (kernel == 3) {
     int st = k_gemm_fp8_tmem(ctx, g);
     if (st != STRICTB200_ERR_UNSUPPORTED || g.kernel == 3) return st;
-    kernel = g.M <= 32 ? 1 : 2;  // shapes the tensor-memory kernel does not cover (K per split % 128 != 0)
+    kernel = g.M <= 32 ? 1 : 2;  // shapes the tensor-memory kernel does not cover (K % 128 != 0)
   }
+  if (g.K % (g.splits * 64)) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: K/splits must be a multiple of 64 for this kernel");
   GemmDev d{(int)g.M, (int)sb_qrows(g.M), (int)g.N, (int)g.K, g.xq, g.ldx, g.sx, g.wq, g.ldw, g.sw, g.out, g.out_f32, g.part, g.splits, g.raw};
   if (kernel == 1) {
     if (g.M > 32) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: the skinny kernel takes at most 32 rows");

@@ -45,6 +45,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
   return false;
 }
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
+               "l"(map), "r"(x), "r"(y), "r"(bar), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
                "l"(map), "r"(x), "r"(y), "r"(bar)
@@ -113,7 +118,10 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, t0 = blockIdx.y * BT;
-  const int Ks = a.K / a.splits, k_begin = blockIdx.z * Ks, nkb = Ks / BK;
+  // split z owns the k-blocks [z * nkb_all / splits, (z + 1) * nkb_all / splits): sizes differ by at most one
+  const int nkb_all = a.K / BK;
+  const int kb_first = (int)((int64_t)blockIdx.z * nkb_all / a.splits), kb_last = (int)((int64_t)(blockIdx.z + 1) * nkb_all / a.splits);
+  const int k_begin = kb_first * BK, nkb = kb_last - kb_first;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
@@ -137,11 +145,12 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
       // The weights are constants: their loads for the first ring of stages are issued before the
       // dependency wait, so they stream from HBM while the preceding kernel is still running.
       const int npre = nkb < STAGES ? nkb : STAGES;
+      const uint64_t w_policy = l2_evict_first_policy();  // every weight byte is read once per launch
       if (!a.prefetch) pdl_wait();
       for (int kb = 0; kb < npre; kb++) {
         uint32_t full = smem_u32(&bar_full[kb]);
         mbar_expect_tx(full, STAGE_BYTES);
-        tma_load_2d(smem_u32(smem + (size_t)kb * STAGE_BYTES), &map_w, k_begin + kb * BK, n0, full);
+        tma_load_2d_hint(smem_u32(smem + (size_t)kb * STAGE_BYTES), &map_w, k_begin + kb * BK, n0, full, w_policy);
       }
       pdl_wait();
       for (int kb = 0; kb < npre; kb++)
@@ -153,7 +162,7 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
         uint32_t full = smem_u32(&bar_full[s]);
         uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
         mbar_expect_tx(full, STAGE_BYTES);
-        tma_load_2d(dst, &map_w, k_begin + kb * BK, n0, full);
+        tma_load_2d_hint(dst, &map_w, k_begin + kb * BK, n0, full, w_policy);
         tma_load_2d(dst + BN * BK, &map_x, k_begin + kb * BK, t0, full);
       }
     }
@@ -268,16 +277,21 @@ int launch(strictb200_ctx* ctx, const GemmArgs& g, const TmemArgs& ta) {
 }  // namespace
 
 int k_gemm_fp8_tmem_split(strictb200_ctx* ctx, const GemmArgs& g) {
-  if (g.K % BK || g.splits < 1 || g.K % (g.splits * BK))
-    return sb_fail(STRICTB200_ERR_UNSUPPORTED, "tensor-memory GEMM needs K (per split) to be a multiple of 128");
+  if (g.K % BK || g.splits < 1 || g.splits > g.K / BK)
+    return sb_fail(STRICTB200_ERR_UNSUPPORTED, "tensor-memory GEMM needs K to be a multiple of 128 and at most K/128 splits");
   if (((uintptr_t)g.xq | (uintptr_t)g.wq | (uintptr_t)g.ldx | (uintptr_t)g.ldw) & 15)
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: operands and row strides must be 16-byte aligned");
   if ((g.splits > 1 || g.raw) && !g.part) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: split-K needs a partial buffer");
   SB_TRY(get_encode());
   TmemArgs ta{(int)g.M, (int)sb_qrows(g.M), (int)g.N, (int)g.K, g.sx, g.sw, g.out, g.out_f32, g.part, g.splits, g.raw, ctx->d_status, getenv("STRICTB200_PREFETCH") ? atoi(getenv("STRICTB200_PREFETCH")) : 1};
   // BT = operand rows per block = the whole (split) batch
-  if (ta.Mq <= 32) return launch<32, 5>(ctx, g, ta);
-  if (ta.Mq <= 64) return launch<64, 4>(ctx, g, ta);
+  // A grid of at most one block per SM gets a ring that fills the SM's shared memory (the whole
+  // ring of weight tiles is in flight before the dependency wait); larger grids keep two blocks
+  // per SM resident.
+  const int64_t blocks = ((g.N + BN - 1) / BN) * g.splits;
+  static const int deep = getenv("STRICTB200_DEEP_RING") ? atoi(getenv("STRICTB200_DEEP_RING")) : 1;
+  if (ta.Mq <= 32) return deep && blocks <= ctx->sm_count ? launch<32, 10>(ctx, g, ta) : launch<32, 5>(ctx, g, ta);
+  if (ta.Mq <= 64) return deep && blocks <= ctx->sm_count ? launch<64, 9>(ctx, g, ta) : launch<64, 4>(ctx, g, ta);
   if (ta.Mq <= 128) return launch<128, 4>(ctx, g, ta);
   if (ta.Mq <= 256) return launch<256, 4>(ctx, g, ta);
   return sb_fail(STRICTB200_ERR_UNSUPPORTED, "the split tensor-memory GEMM takes at most 128 tokens");

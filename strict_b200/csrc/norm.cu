@@ -17,6 +17,11 @@ __device__ __forceinline__ void load8_bf16(const bf16* p, float* v) {
     v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
   }
 }
+__device__ __forceinline__ void load8_f32(const float* p, float* v) {
+  float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
 // Peer (or own) buffer read of the fused all-reduce: volatile, so a slot that is rewritten two
 // epochs later is never served from a stale cache line.
 __device__ __forceinline__ float4 ld_peer4(const float* p) {
@@ -218,6 +223,104 @@ __global__ void __launch_bounds__(512) rownorm_kernel(RowNormDev a, int64_t M, i
   }
 }
 
+// The same operation for the shapes of a decode step: the row is exactly blockDim.x * 8 wide
+// (d <= 4096), the input is one group of at most 8 split-K partials (MODE 0) or the published
+// partial results of at most 8 ranks (MODE 1), and the gain is present. Straight-line code of
+// a few KB: the constants (weight scales, gain) are fetched before the dependency wait, every
+// load of the row is issued in one batch after it, and the arithmetic is that of the kernel
+// above, operation for operation.
+template <int MODE>
+__global__ void __launch_bounds__(512) rownorm_decode_kernel(RowNormDev a, int64_t M, int64_t d) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x, k = (int64_t)threadIdx.x * 8;
+  pdl_trigger();
+  float sw[8], g[8];
+  if (MODE == 0) load8_f32(a.sw + k, sw);
+  load8_f32(a.gain + k, g);
+  pdl_wait();
+  float t[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) t[i] = 0.f;
+  float r8[8];
+  if (MODE == 0) {
+    float4 p[8][2];
+#pragma unroll
+    for (int s = 0; s < 8; s++)
+      if (s < a.splits) {
+        const float* q = a.part + (((int64_t)s * M + row) * d + k);
+        p[s][0] = *(const float4*)q;
+        p[s][1] = *(const float4*)(q + 4);
+      }
+    float sxr = a.sx[row];
+    if (a.residual_f32) load8_f32(a.residual_f32 + row * d + k, r8);
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = 0.f;
+#pragma unroll
+    for (int s = 0; s < 8; s++)
+      if (s < a.splits) {
+        acc[0] += p[s][0].x; acc[1] += p[s][0].y; acc[2] += p[s][0].z; acc[3] += p[s][0].w;
+        acc[4] += p[s][1].x; acc[5] += p[s][1].y; acc[6] += p[s][1].z; acc[7] += p[s][1].w;
+      }
+#pragma unroll
+    for (int i = 0; i < 8; i++) t[i] += __fmul_rn(__fmul_rn(acc[i], sxr), sw[i]);
+  } else {
+    // Fused all-reduce: wait (bounded) until every rank has published this epoch, then the input
+    // row is the sum, in rank order, of the ranks' partial results read over NVLink.
+    const int comm_e = *(volatile int*)a.comm.epoch;
+    if ((int)threadIdx.x < a.comm.world) {
+      volatile int* f = a.comm.flags[a.comm.rank] + (comm_e & 1) * 8 + threadIdx.x;
+      uint32_t spins = 0;
+      while (*f - comm_e < 0) {
+        if (++spins > (1u << 24)) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
+        __nanosleep(64);
+      }
+    }
+    __syncthreads();
+    float4 p[8][2];
+#pragma unroll
+    for (int r = 0; r < 8; r++)
+      if (r < a.comm.world) {
+        const float* q = a.comm.data[r] + (size_t)(comm_e & 1) * a.comm.max_elems + row * d + k;
+        p[r][0] = ld_peer4(q);
+        p[r][1] = ld_peer4(q + 4);
+      }
+    if (a.residual_f32) load8_f32(a.residual_f32 + row * d + k, r8);
+#pragma unroll
+    for (int r = 0; r < 8; r++)
+      if (r < a.comm.world) {
+        t[0] += p[r][0].x; t[1] += p[r][0].y; t[2] += p[r][0].z; t[3] += p[r][0].w;
+        t[4] += p[r][1].x; t[5] += p[r][1].y; t[6] += p[r][1].z; t[7] += p[r][1].w;
+      }
+  }
+  if (a.residual_f32) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) t[i] = __fadd_rn(r8[i], t[i]);
+    float* rp = a.residual_f32 + row * d + k;
+    *(float4*)rp = make_float4(t[0], t[1], t[2], t[3]);
+    *(float4*)(rp + 4) = make_float4(t[4], t[5], t[6], t[7]);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) ss += t[i] * t[i];
+  ss = block_sum(ss, red);
+  float ms = __fdiv_rn(ss, (float)d);
+  float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, a.eps)));
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    t[i] = round_bf16(__fmul_rn(__fmul_rn(t[i], r), g[i]));
+    amax = fmaxf(amax, fabsf(t[i]));
+  }
+  if (a.y) store8_bf16(a.y + row * d + k, t);
+  if (!a.q) return;
+  amax = block_max(amax, red);
+  int e = sb_scale_exponent(amax);
+  if (threadIdx.x == 0) a.qscale[row] = sb_pow2(e);
+  sb_store_split8(a.q, d, row, k, t, sb_pow2(-e));
+}
+
+
 __global__ void __launch_bounds__(ROW_THREADS) layernorm_kernel(const float* __restrict__ x, const float* __restrict__ g,
                                                                 const float* __restrict__ b, float eps, int64_t d, float* __restrict__ y) {
   __shared__ float red[32];
@@ -243,10 +346,6 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
 }
 
-__device__ __forceinline__ void load8_f32(const float* p, float* v) {
-  float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
 // gate_up [M, 2I] (bf16, or the projection's fp32 result) -> h = bf16(silu(gate)*up); optional
 // two-term E4M3 split of h per row. 512 threads; a thread owns up to 4 groups of 8 columns and
 // keeps h in registers between the absmax pass and the split (rows wider than 16384 recompute).
@@ -307,6 +406,38 @@ __global__ void __launch_bounds__(SW_THREADS) swiglu_kernel(const bf16* __restri
   }
 }
 
+// The decode-step shape of the above: a row of I columns is shared by a cluster of gridDim.y
+// blocks, one 8-column group per thread (I == gridDim.y * blockDim.x * 8), fp32 input, split
+// output. The blocks of a row exchange their absolute maxima through distributed shared memory.
+__global__ void __launch_bounds__(512) swiglu_decode_kernel(const float* __restrict__ gu32, int64_t I, bf16* __restrict__ y,
+                                                            uint8_t* __restrict__ q, float* __restrict__ qscale) {
+  __shared__ float red[32];
+  __shared__ float block_amax;
+  pdl_trigger();
+  pdl_wait();
+  const int64_t row = blockIdx.x, k = ((int64_t)blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  float g[8], u[8], h[8];
+  load8_f32(gu32 + row * 2 * I + k, g);
+  load8_f32(gu32 + row * 2 * I + I + k, u);
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    h[i] = round_bf16(silu_mul(g[i], u[i]));
+    amax = fmaxf(amax, fabsf(h[i]));
+  }
+  if (y) store8_bf16(y + row * I + k, h);
+  amax = block_max(amax, red);
+  if (gridDim.y > 1) {
+    if (threadIdx.x == 0) block_amax = amax;
+    cluster_sync_all();
+    for (uint32_t r = 0; r < gridDim.y; r++) amax = fmaxf(amax, ld_cluster_f32(&block_amax, r));
+  }
+  int e = sb_scale_exponent(amax);
+  if (blockIdx.y == 0 && threadIdx.x == 0) qscale[row] = sb_pow2(e);
+  sb_store_split8(q, I, row, k, h, sb_pow2(-e));
+  if (gridDim.y > 1) cluster_sync_all();  // no block leaves while its shared memory may still be read
+}
+
 __global__ void gelu_tanh_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ y) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -343,6 +474,18 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   threads = threads < 128 ? 128 : (threads > 512 ? 512 : threads);
   while ((int64_t)threads * 8 * MAX_CHUNKS < d) threads += 32;
   RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale};
+  // decode-step shapes: one 8-value chunk per thread, at most 8 partials, no bf16 residual
+  const bool narrow = d % 256 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
+  if (narrow && a.comm && a.comm->world <= 8) {
+    SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<1>, dim3((unsigned)M), dim3((unsigned)(d / 8)), 0, v, M, d));
+    ctx->launches++;
+    return STRICTB200_OK;
+  }
+  if (narrow && !a.comm && a.part && a.groups == 1 && a.splits <= 8) {
+    SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<0>, dim3((unsigned)M), dim3((unsigned)(d / 8)), 0, v, M, d));
+    ctx->launches++;
+    return STRICTB200_OK;
+  }
   SB_CUDA(sb_launch(ctx, rownorm_kernel, dim3((unsigned)M), dim3(threads), 0, v, M, d));
   ctx->launches++;
   return STRICTB200_OK;
@@ -359,6 +502,16 @@ int k_add_f32(strictb200_ctx* ctx, float* x, const float* y, int64_t n) {
 }
 int k_swiglu(strictb200_ctx* ctx, const bf16* gate_up, const float* gate_up_f32, int64_t M, int64_t I, bf16* y, uint8_t* q, float* qscale) {
   if (I % 8) return sb_fail(STRICTB200_ERR_INVALID_ARG, "swiglu: I must be a multiple of 8");
+  if (gate_up_f32 && q && I % 256 == 0 && M <= 1024) {
+    // decode shapes: one 8-column group per thread, a cluster of up to 8 blocks per row
+    for (int c = 1; c <= 8; c++) {
+      if (I % (8 * c) || (I / (8 * c)) % 32 || I / (8 * c) > 512) continue;
+      SB_CUDA(sb_launch_cluster(ctx, swiglu_decode_kernel, dim3((unsigned)M, (unsigned)c), dim3((unsigned)(I / (8 * c))), 0, dim3(1, (unsigned)c, 1),
+                                gate_up_f32, I, y, q, qscale));
+      ctx->launches++;
+      return STRICTB200_OK;
+    }
+  }
   SB_CUDA(sb_launch(ctx, swiglu_kernel, dim3((unsigned)M), dim3(SW_THREADS), 0, gate_up, gate_up_f32, I, y, q, qscale));
   ctx->launches++;
   return STRICTB200_OK;

@@ -101,6 +101,71 @@ __global__ void __launch_bounds__(256) rope_kernel(RopeDev a, int64_t T) {
   }
 }
 
+// The decode-step shape of the above: token t is sequence t at position lens[t], the input is
+// at most 8 split-K partials, one head per warp. The constants (weight scales, gains) are
+// fetched before the dependency wait and every load of the head is issued in one batch after
+// it; the arithmetic is that of the kernel above, operation for operation.
+__global__ void __launch_bounds__(256) rope_decode_kernel(RopeDev a, int64_t T) {
+  constexpr int D = 128;
+  pdl_trigger();
+  const int64_t t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y * 8 + warp, nheads = a.Hq + 2 * a.Hkv;
+  if (h >= nheads) return;
+  const int64_t nqkv = (int64_t)nheads * D, col = (int64_t)h * D + lane * 4;
+  const bool is_v = h >= a.Hq + a.Hkv;
+  const float4 w = *(const float4*)(a.sw + col);
+  float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!is_v) gv = *(const float4*)((h < a.Hq ? a.qgain : a.kgain) + lane * 4);
+  pdl_wait();
+  const int p = a.lens[t];
+  float4 v[8];
+#pragma unroll
+  for (int s = 0; s < 8; s++)
+    if (s < a.splits) v[s] = *(const float4*)(a.part + ((int64_t)s * T + t) * nqkv + col);
+  const float sxr = a.sx[t];
+  if (p < 0 || p >= a.maxlen || p >= a.max_pos) return;  // host validates; never index outside the cache
+  float4 c = make_float4(0.f, 0.f, 0.f, 0.f), sn4 = c;
+  if (!is_v) {
+    const int i0 = (lane & 15) * 4;
+    c = *(const float4*)(a.cos_t + (int64_t)p * (D / 2) + i0);
+    sn4 = *(const float4*)(a.sin_t + (int64_t)p * (D / 2) + i0);
+  }
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int s = 0; s < 8; s++)
+    if (s < a.splits) { acc[0] += v[s].x; acc[1] += v[s].y; acc[2] += v[s].z; acc[3] += v[s].w; }
+  float x[4] = {__fmul_rn(__fmul_rn(acc[0], sxr), w.x), __fmul_rn(__fmul_rn(acc[1], sxr), w.y), __fmul_rn(__fmul_rn(acc[2], sxr), w.z),
+                __fmul_rn(__fmul_rn(acc[3], sxr), w.w)};
+  float o[4];
+  if (!is_v) {
+    float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+    float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)D), a.eps)));
+    float n[4] = {__fmul_rn(__fmul_rn(x[0], r), gv.x), __fmul_rn(__fmul_rn(x[1], r), gv.y), __fmul_rn(__fmul_rn(x[2], r), gv.z),
+                  __fmul_rn(__fmul_rn(x[3], r), gv.w)};
+    float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {sn4.x, sn4.y, sn4.z, sn4.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float other = __shfl_xor_sync(0xffffffffu, n[j], 16);
+      o[j] = lane < 16 ? __fsub_rn(__fmul_rn(n[j], cs[j]), __fmul_rn(other, sn[j]))
+                       : __fadd_rn(__fmul_rn(n[j], cs[j]), __fmul_rn(other, sn[j]));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; j++) o[j] = x[j];
+  }
+  uint2 wv;
+  wv.x = f32_to_bf16_bits(o[0]) | (f32_to_bf16_bits(o[1]) << 16);
+  wv.y = f32_to_bf16_bits(o[2]) | (f32_to_bf16_bits(o[3]) << 16);
+  if (h < a.Hq) {
+    *(uint2*)(a.q_out + (t * a.Hq + h) * D + lane * 4) = wv;
+  } else {
+    const int hk = is_v ? h - a.Hq - a.Hkv : h - a.Hq;
+    bf16* cache = is_v ? a.vcache : a.kcache;
+    *(uint2*)(cache + ((t * a.Hkv + hk) * a.maxlen + p) * D + lane * 4) = wv;
+  }
+}
+
 }  // namespace
 
 int k_rope_qknorm_kvappend(strictb200_ctx* ctx, const RopeArgs& a, int64_t T) {
@@ -110,6 +175,11 @@ int k_rope_qknorm_kvappend(strictb200_ctx* ctx, const RopeArgs& a, int64_t T) {
   int nheads = a.Hq + 2 * a.Hkv;
   // few rows (decode): spread the heads of a row over several blocks, one head per warp
   dim3 grid((unsigned)T, T <= 256 ? (unsigned)((nheads + 7) / 8) : 1u);
+  if (T <= 256 && a.part && a.splits <= 8 && !a.seq && !a.pos) {
+    SB_CUDA(sb_launch(ctx, rope_decode_kernel, grid, dim3(256), 0, v, T));
+    ctx->launches++;
+    return STRICTB200_OK;
+  }
   SB_CUDA(sb_launch(ctx, rope_kernel, grid, dim3(256), 0, v, T));
   ctx->launches++;
   return STRICTB200_OK;
