@@ -448,30 +448,29 @@ __global__ void __launch_bounds__(CB_THREADS) attn_combine_kernel(const float* _
   }
 }
 
-// The decode-step shape of the merge: one thread per 8-dim group of the token's attention row
-// (blockDim.x == Hq * 16 <= 512), at most 8 key chunks. Every partial is loaded in one batch
-// together with the sequence length (slots of chunks beyond the length hold stale data and are
-// masked out of the arithmetic, which is that of the kernel above).
-__global__ void __launch_bounds__(512) attn_combine_decode_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
-                                                                  const int32_t* __restrict__ lens, int len_add, int Hq, int maxlen, int chunk,
-                                                                  int nsplit, bf16* __restrict__ out, uint8_t* __restrict__ q_out,
-                                                                  float* __restrict__ qscale) {
+// The decode-step shape of the merge: one thread per 4-dim group of the token's attention row
+// (blockDim.x == Hq * 32 <= 1024), at most 8 key chunks, so a thread has at most 16 small loads
+// in flight. Every partial is loaded in one batch together with the sequence length (slots of
+// chunks beyond the length hold stale data and are masked out of the arithmetic, which is that
+// of the kernel above).
+__global__ void __launch_bounds__(1024) attn_combine_decode_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
+                                                                   const int32_t* __restrict__ lens, int len_add, int Hq, int maxlen, int chunk,
+                                                                   int nsplit, bf16* __restrict__ out, uint8_t* __restrict__ q_out,
+                                                                   float* __restrict__ qscale) {
   __shared__ float red[32];
   pdl_trigger();
   pdl_wait();
   const int b = blockIdx.x;
-  const int e8 = threadIdx.x, h = e8 >> 4, d = (e8 & 15) * 8;
+  const int e4 = threadIdx.x, h = e4 >> 5, d = (e4 & 31) * 4;
   const int64_t base = ((int64_t)b * Hq + h) * nsplit;
   const int len_raw = lens[b];
   float2 ml[8];
-  float4 o[8][2];
+  float4 o[8];
 #pragma unroll
   for (int s = 0; s < 8; s++)
     if (s < nsplit) {
       ml[s] = *(const float2*)(ml_part + (base + s) * 2);
-      const float4* op = (const float4*)(o_part + (base + s) * D + d);
-      o[s][0] = op[0];
-      o[s][1] = op[1];
+      o[s] = *(const float4*)(o_part + (base + s) * D + d);
     }
   const int len = min(len_raw + len_add, maxlen);
   const int ns = (len + chunk - 1) / chunk;
@@ -479,30 +478,26 @@ __global__ void __launch_bounds__(512) attn_combine_decode_kernel(const float* _
 #pragma unroll
   for (int s = 0; s < 8; s++)
     if (s < ns) M = fmaxf(M, ml[s].x);
-  float L = 0.f, O[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float L = 0.f, O[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int s = 0; s < 8; s++)
     if (s < ns) {
       float f = exp2f(ml[s].x - M);
       L += ml[s].y * f;
-      O[0] += o[s][0].x * f; O[1] += o[s][0].y * f; O[2] += o[s][0].z * f; O[3] += o[s][0].w * f;
-      O[4] += o[s][1].x * f; O[5] += o[s][1].y * f; O[6] += o[s][1].z * f; O[7] += o[s][1].w * f;
+      O[0] += o[s].x * f; O[1] += o[s].y * f; O[2] += o[s].z * f; O[3] += o[s].w * f;
     }
-  float v[8], amax = 0.f;
-  uint32_t w[4];
+  float v[4], amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
+  for (int i = 0; i < 4; i++) {
     v[i] = ns > 0 ? round_bf16(O[i] / L) : 0.f;
     amax = fmaxf(amax, fabsf(v[i]));
   }
-#pragma unroll
-  for (int i = 0; i < 4; i++) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
-  *(uint4*)(out + ((int64_t)b * Hq + h) * D + d) = make_uint4(w[0], w[1], w[2], w[3]);
+  *(uint2*)(out + ((int64_t)b * Hq + h) * D + d) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
   if (!q_out) return;
   amax = block_max(amax, red);
-  int ex = sb_scale_exponent(amax);
+  const int ex = sb_scale_exponent(amax);
   if (threadIdx.x == 0) qscale[b] = sb_pow2(ex);
-  sb_store_split8(q_out, (int64_t)Hq * D, b, (int64_t)e8 * 8, v, sb_pow2(-ex));
+  sb_store_split4(q_out, (int64_t)Hq * D, b, (int64_t)e4 * 4, v, sb_pow2(-ex));
 }
 
 // ------------------------------------------------------------------ fp32 attention (GPT-2 path)
@@ -622,8 +617,8 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
   dim3 grid(nsplit, Hkv, B);
   SB_CUDA(sb_launch(ctx, attn_decode_kernel, grid, dim3(128), smem, q, kc, vc, lens, len_add, B, Hq, Hkv, maxlen, chunk, nsplit, scale * LOG2E, o_part, ml_part));
   ctx->launches++;
-  if (nsplit <= 8 && Hq * 16 <= 512 && (Hq * 16) % 32 == 0) {
-    SB_CUDA(sb_launch(ctx, attn_combine_decode_kernel, dim3(B), dim3((unsigned)(Hq * 16)), 0, (const float*)o_part, (const float*)ml_part, lens, len_add, Hq,
+  if (nsplit <= 8 && Hq <= 32) {
+    SB_CUDA(sb_launch(ctx, attn_combine_decode_kernel, dim3(B), dim3((unsigned)(Hq * 32)), 0, (const float*)o_part, (const float*)ml_part, lens, len_add, Hq,
                       maxlen, chunk, nsplit, out, q_out, qscale_out));
     ctx->launches++;
     return STRICTB200_OK;

@@ -223,47 +223,40 @@ __global__ void __launch_bounds__(512) rownorm_kernel(RowNormDev a, int64_t M, i
   }
 }
 
-// The same operation for the shapes of a decode step: the row is exactly blockDim.x * 8 wide
+// The same operation for the shapes of a decode step: the row is exactly blockDim.x * 4 wide
 // (d <= 4096), the input is one group of at most 8 split-K partials (MODE 0) or the published
-// partial results of at most 8 ranks (MODE 1), and the gain is present. Straight-line code of
-// a few KB: the constants (weight scales, gain) are fetched before the dependency wait, every
-// load of the row is issued in one batch after it, and the arithmetic is that of the kernel
-// above, operation for operation.
+// partial results of at most 8 ranks (MODE 1), and the gain is present. A thread owns 4 columns
+// so that it never has more than about ten 128-bit loads in flight (beyond that the loads of a
+// thread are served in several rounds: 16 loads per thread measured twice the time of 8). The
+// constants (weight scales, gain) are fetched before the dependency wait, every load of the row
+// is issued in one batch after it, and the arithmetic is that of the kernel above, operation
+// for operation.
 template <int MODE>
-__global__ void __launch_bounds__(512) rownorm_decode_kernel(RowNormDev a, int64_t M, int64_t d) {
+__global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int64_t M, int64_t d) {
   __shared__ float red[32];
-  const int64_t row = blockIdx.x, k = (int64_t)threadIdx.x * 8;
+  const int64_t row = blockIdx.x, k = (int64_t)threadIdx.x * 4;
   pdl_trigger();
-  float sw[8], g[8];
-  if (MODE == 0) load8_f32(a.sw + k, sw);
-  load8_f32(a.gain + k, g);
+  float4 sw = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (MODE == 0) sw = *(const float4*)(a.sw + k);
+  const float4 g = *(const float4*)(a.gain + k);
   pdl_wait();
-  float t[8];
-#pragma unroll
-  for (int i = 0; i < 8; i++) t[i] = 0.f;
-  float r8[8];
+  float t[4] = {0.f, 0.f, 0.f, 0.f};
+  float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
   if (MODE == 0) {
-    float4 p[8][2];
+    float4 p[8];
 #pragma unroll
     for (int s = 0; s < 8; s++)
-      if (s < a.splits) {
-        const float* q = a.part + (((int64_t)s * M + row) * d + k);
-        p[s][0] = *(const float4*)q;
-        p[s][1] = *(const float4*)(q + 4);
-      }
-    float sxr = a.sx[row];
-    if (a.residual_f32) load8_f32(a.residual_f32 + row * d + k, r8);
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) acc[i] = 0.f;
+      if (s < a.splits) p[s] = *(const float4*)(a.part + (((int64_t)s * M + row) * d + k));
+    const float sxr = a.sx[row];
+    if (a.residual_f32) r4 = *(const float4*)(a.residual_f32 + row * d + k);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int s = 0; s < 8; s++)
-      if (s < a.splits) {
-        acc[0] += p[s][0].x; acc[1] += p[s][0].y; acc[2] += p[s][0].z; acc[3] += p[s][0].w;
-        acc[4] += p[s][1].x; acc[5] += p[s][1].y; acc[6] += p[s][1].z; acc[7] += p[s][1].w;
-      }
-#pragma unroll
-    for (int i = 0; i < 8; i++) t[i] += __fmul_rn(__fmul_rn(acc[i], sxr), sw[i]);
+      if (s < a.splits) { acc[0] += p[s].x; acc[1] += p[s].y; acc[2] += p[s].z; acc[3] += p[s].w; }
+    t[0] += __fmul_rn(__fmul_rn(acc[0], sxr), sw.x);
+    t[1] += __fmul_rn(__fmul_rn(acc[1], sxr), sw.y);
+    t[2] += __fmul_rn(__fmul_rn(acc[2], sxr), sw.z);
+    t[3] += __fmul_rn(__fmul_rn(acc[3], sxr), sw.w);
   } else {
     // Fused all-reduce: wait (bounded) until every rank has published this epoch, then the input
     // row is the sum, in rank order, of the ranks' partial results read over NVLink.
@@ -277,47 +270,41 @@ __global__ void __launch_bounds__(512) rownorm_decode_kernel(RowNormDev a, int64
       }
     }
     __syncthreads();
-    float4 p[8][2];
+    float4 p[8];
 #pragma unroll
     for (int r = 0; r < 8; r++)
-      if (r < a.comm.world) {
-        const float* q = a.comm.data[r] + (size_t)(comm_e & 1) * a.comm.max_elems + row * d + k;
-        p[r][0] = ld_peer4(q);
-        p[r][1] = ld_peer4(q + 4);
-      }
-    if (a.residual_f32) load8_f32(a.residual_f32 + row * d + k, r8);
+      if (r < a.comm.world) p[r] = ld_peer4(a.comm.data[r] + (size_t)(comm_e & 1) * a.comm.max_elems + row * d + k);
+    if (a.residual_f32) r4 = *(const float4*)(a.residual_f32 + row * d + k);
 #pragma unroll
     for (int r = 0; r < 8; r++)
-      if (r < a.comm.world) {
-        t[0] += p[r][0].x; t[1] += p[r][0].y; t[2] += p[r][0].z; t[3] += p[r][0].w;
-        t[4] += p[r][1].x; t[5] += p[r][1].y; t[6] += p[r][1].z; t[7] += p[r][1].w;
-      }
+      if (r < a.comm.world) { t[0] += p[r].x; t[1] += p[r].y; t[2] += p[r].z; t[3] += p[r].w; }
   }
   if (a.residual_f32) {
-#pragma unroll
-    for (int i = 0; i < 8; i++) t[i] = __fadd_rn(r8[i], t[i]);
-    float* rp = a.residual_f32 + row * d + k;
-    *(float4*)rp = make_float4(t[0], t[1], t[2], t[3]);
-    *(float4*)(rp + 4) = make_float4(t[4], t[5], t[6], t[7]);
+    t[0] = __fadd_rn(r4.x, t[0]); t[1] = __fadd_rn(r4.y, t[1]); t[2] = __fadd_rn(r4.z, t[2]); t[3] = __fadd_rn(r4.w, t[3]);
+    *(float4*)(a.residual_f32 + row * d + k) = make_float4(t[0], t[1], t[2], t[3]);
   }
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; i++) ss += t[i] * t[i];
+  float ss = t[0] * t[0] + t[1] * t[1] + t[2] * t[2] + t[3] * t[3];
   ss = block_sum(ss, red);
-  float ms = __fdiv_rn(ss, (float)d);
-  float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, a.eps)));
+  const float ms = __fdiv_rn(ss, (float)d);
+  const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, a.eps)));
+  const float gg[4] = {g.x, g.y, g.z, g.w};
   float amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
-    t[i] = round_bf16(__fmul_rn(__fmul_rn(t[i], r), g[i]));
+  for (int i = 0; i < 4; i++) {
+    t[i] = round_bf16(__fmul_rn(__fmul_rn(t[i], r), gg[i]));
     amax = fmaxf(amax, fabsf(t[i]));
   }
-  if (a.y) store8_bf16(a.y + row * d + k, t);
+  if (a.y) {
+    uint2 w;
+    w.x = f32_to_bf16_bits(t[0]) | (f32_to_bf16_bits(t[1]) << 16);
+    w.y = f32_to_bf16_bits(t[2]) | (f32_to_bf16_bits(t[3]) << 16);
+    *(uint2*)(a.y + row * d + k) = w;
+  }
   if (!a.q) return;
   amax = block_max(amax, red);
-  int e = sb_scale_exponent(amax);
+  const int e = sb_scale_exponent(amax);
   if (threadIdx.x == 0) a.qscale[row] = sb_pow2(e);
-  sb_store_split8(a.q, d, row, k, t, sb_pow2(-e));
+  sb_store_split4(a.q, d, row, k, t, sb_pow2(-e));
 }
 
 
@@ -408,11 +395,12 @@ __global__ void __launch_bounds__(SW_THREADS) swiglu_kernel(const bf16* __restri
 
 // The decode-step shape of the above: a row of I columns is shared by a cluster of gridDim.y
 // blocks, one 8-column group per thread (I == gridDim.y * blockDim.x * 8), fp32 input, split
-// output. The blocks of a row exchange their absolute maxima through distributed shared memory.
+// output. The blocks of a row push their absolute maxima to each other.
 __global__ void __launch_bounds__(512) swiglu_decode_kernel(const float* __restrict__ gu32, int64_t I, bf16* __restrict__ y,
-                                                            uint8_t* __restrict__ q, float* __restrict__ qscale) {
+                                                            uint8_t* __restrict__ q, float* __restrict__ qscale, int* __restrict__ status) {
   __shared__ float red[32];
-  __shared__ float block_amax;
+  __shared__ __align__(8) ClusterExchange xch;
+  if (gridDim.y > 1) cluster_exchange_init(&xch);
   pdl_trigger();
   pdl_wait();
   const int64_t row = blockIdx.x, k = ((int64_t)blockIdx.y * blockDim.x + threadIdx.x) * 8;
@@ -428,14 +416,12 @@ __global__ void __launch_bounds__(512) swiglu_decode_kernel(const float* __restr
   if (y) store8_bf16(y + row * I + k, h);
   amax = block_max(amax, red);
   if (gridDim.y > 1) {
-    if (threadIdx.x == 0) block_amax = amax;
-    cluster_sync_all();
-    for (uint32_t r = 0; r < gridDim.y; r++) amax = fmaxf(amax, ld_cluster_f32(&block_amax, r));
+    if (!cluster_exchange(&xch, amax, gridDim.y, blockIdx.y) && threadIdx.x == 0) { *(volatile int*)status = 6; __threadfence_system(); }
+    for (uint32_t r = 0; r < gridDim.y; r++) amax = fmaxf(amax, ((volatile float*)xch.slot)[r]);
   }
-  int e = sb_scale_exponent(amax);
+  const int e = sb_scale_exponent(amax);
   if (blockIdx.y == 0 && threadIdx.x == 0) qscale[row] = sb_pow2(e);
   sb_store_split8(q, I, row, k, h, sb_pow2(-e));
-  if (gridDim.y > 1) cluster_sync_all();  // no block leaves while its shared memory may still be read
 }
 
 __global__ void gelu_tanh_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ y) {
@@ -474,15 +460,15 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   threads = threads < 128 ? 128 : (threads > 512 ? 512 : threads);
   while ((int64_t)threads * 8 * MAX_CHUNKS < d) threads += 32;
   RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale};
-  // decode-step shapes: one 8-value chunk per thread, at most 8 partials, no bf16 residual
-  const bool narrow = d % 256 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
+  // decode-step shapes: 4 columns per thread, at most 8 partials, no bf16 residual
+  const bool narrow = d % 128 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
   if (narrow && a.comm && a.comm->world <= 8) {
-    SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<1>, dim3((unsigned)M), dim3((unsigned)(d / 8)), 0, v, M, d));
+    SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<1>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
     ctx->launches++;
     return STRICTB200_OK;
   }
   if (narrow && !a.comm && a.part && a.groups == 1 && a.splits <= 8) {
-    SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<0>, dim3((unsigned)M), dim3((unsigned)(d / 8)), 0, v, M, d));
+    SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<0>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
     ctx->launches++;
     return STRICTB200_OK;
   }
@@ -507,7 +493,7 @@ int k_swiglu(strictb200_ctx* ctx, const bf16* gate_up, const float* gate_up_f32,
     for (int c = 1; c <= 8; c++) {
       if (I % (8 * c) || (I / (8 * c)) % 32 || I / (8 * c) > 512) continue;
       SB_CUDA(sb_launch_cluster(ctx, swiglu_decode_kernel, dim3((unsigned)M, (unsigned)c), dim3((unsigned)(I / (8 * c))), 0, dim3(1, (unsigned)c, 1),
-                                gate_up_f32, I, y, q, qscale));
+                                gate_up_f32, I, y, q, qscale, ctx->d_status));
       ctx->launches++;
       return STRICTB200_OK;
     }
