@@ -582,15 +582,37 @@ int k_attn_prefill(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf1
   return STRICTB200_OK;
 }
 
-// Keys per block: sized so that a full cache yields about six blocks per SM.
+// Keys per block. All blocks of a launch take about the same time, so the grid runs in waves of
+// (blocks resident per SM) x (SM count): the chunk is the multiple of the tile size that
+// minimises waves x (tiles per chunk + per-block overhead) for a full cache, among the chunk
+// sizes that leave at most 8 chunks per sequence. STRICTB200_ATTN_BLOCKS_PER_SM restores the
+// plain "that many blocks per SM" rule.
 static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
-  int64_t total = (int64_t)maxlen * B * Hkv;
-  static const int per_sm = getenv("STRICTB200_ATTN_BLOCKS_PER_SM") ? atoi(getenv("STRICTB200_ATTN_BLOCKS_PER_SM")) : 6;
-  int64_t c = total / ((int64_t)ctx->sm_count * per_sm);
-  c = (c + KT - 1) / KT * KT;
-  if (c < 256) c = 256;
-  if (c > maxlen) c = (maxlen + KT - 1) / KT * KT;
-  return (int)c;
+  static const int per_sm = getenv("STRICTB200_ATTN_BLOCKS_PER_SM") ? atoi(getenv("STRICTB200_ATTN_BLOCKS_PER_SM")) : 0;
+  const int tiles = (maxlen + KT - 1) / KT;
+  if (per_sm > 0) {
+    int64_t c = (int64_t)maxlen * B * Hkv / ((int64_t)ctx->sm_count * per_sm);
+    c = (c + KT - 1) / KT * KT;
+    if (c < 256) c = 256;
+    if (c > maxlen) c = (int64_t)tiles * KT;
+    return (int)c;
+  }
+  static int resident = 0;
+  if (!resident) {
+    const size_t smem = 2 * DEC_STAGES * KT * 256;
+    cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, attn_decode_kernel, 128, smem) != cudaSuccess || resident < 1) resident = 1;
+  }
+  const int64_t slots = (int64_t)ctx->sm_count * resident, pairs = (int64_t)B * Hkv;
+  int best = tiles;
+  double best_cost = 1e30;
+  for (int c = (tiles + 7) / 8; c <= tiles; c++) {
+    if (c < 4 && c < tiles) continue;  // at least 256 keys per block
+    const int64_t blocks = pairs * ((tiles + c - 1) / c), waves = (blocks + slots - 1) / slots;
+    const double cost = (double)waves * ((double)c + 1.5);
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = c; }
+  }
+  return best * KT;
 }
 int sb_attn_decode_splits(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
   int c = decode_chunk(ctx, B, Hkv, maxlen);

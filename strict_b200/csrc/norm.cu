@@ -224,8 +224,8 @@ __global__ void __launch_bounds__(512) rownorm_kernel(RowNormDev a, int64_t M, i
 }
 
 // The same operation for the shapes of a decode step: the row is exactly blockDim.x * 4 wide
-// (d <= 4096), the input is one group of at most 8 split-K partials (MODE 0) or the published
-// partial results of at most 8 ranks (MODE 1), and the gain is present. A thread owns 4 columns
+// (d <= 4096), the input is one group of at most 8 split-K partials (MODE 0), the published
+// partial results of at most 8 ranks (MODE 1) or a finished fp32 row (MODE 2), and the gain is present. A thread owns 4 columns
 // so that it never has more than about ten 128-bit loads in flight (beyond that the loads of a
 // thread are served in several rounds: 16 loads per thread measured twice the time of 8). The
 // constants (weight scales, gain) are fetched before the dependency wait, every load of the row
@@ -257,6 +257,10 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
     t[1] += __fmul_rn(__fmul_rn(acc[1], sxr), sw.y);
     t[2] += __fmul_rn(__fmul_rn(acc[2], sxr), sw.z);
     t[3] += __fmul_rn(__fmul_rn(acc[3], sxr), sw.w);
+  } else if (MODE == 2) {
+    const float4 p = *(const float4*)(a.x_f32 + row * d + k);
+    if (a.residual_f32) r4 = *(const float4*)(a.residual_f32 + row * d + k);
+    t[0] = p.x; t[1] = p.y; t[2] = p.z; t[3] = p.w;
   } else {
     // Fused all-reduce: wait (bounded) until every rank has published this epoch, then the input
     // row is the sum, in rank order, of the ranks' partial results read over NVLink.
@@ -464,6 +468,11 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   const bool narrow = d % 128 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
   if (narrow && a.comm && a.comm->world <= 8) {
     SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<1>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
+    ctx->launches++;
+    return STRICTB200_OK;
+  }
+  if (narrow && !a.comm && !a.part && a.x_f32) {
+    SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<2>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
     ctx->launches++;
     return STRICTB200_OK;
   }

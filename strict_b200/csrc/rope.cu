@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(256) rope_kernel(RopeDev a, int64_t T) {
 }
 
 // The decode-step shape of the above: token t is sequence t at position lens[t], the input is
-// at most 8 split-K partials, one head per warp. The constants (weight scales, gains) are
+// at most 8 split-K partials or the finished fp32 projection, one head per warp. The constants (weight scales, gains) are
 // fetched before the dependency wait and every load of the head is issued in one batch after
 // it; the arithmetic is that of the kernel above, operation for operation.
 __global__ void __launch_bounds__(256) rope_decode_kernel(RopeDev a, int64_t T) {
@@ -114,16 +114,22 @@ __global__ void __launch_bounds__(256) rope_decode_kernel(RopeDev a, int64_t T) 
   if (h >= nheads) return;
   const int64_t nqkv = (int64_t)nheads * D, col = (int64_t)h * D + lane * 4;
   const bool is_v = h >= a.Hq + a.Hkv;
-  const float4 w = *(const float4*)(a.sw + col);
+  float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
+  if (a.part) w = *(const float4*)(a.sw + col);
   float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
   if (!is_v) gv = *(const float4*)((h < a.Hq ? a.qgain : a.kgain) + lane * 4);
   pdl_wait();
   const int p = a.lens[t];
   float4 v[8];
+  float sxr = 1.f;
+  if (a.part) {
 #pragma unroll
-  for (int s = 0; s < 8; s++)
-    if (s < a.splits) v[s] = *(const float4*)(a.part + ((int64_t)s * T + t) * nqkv + col);
-  const float sxr = a.sx[t];
+    for (int s = 0; s < 8; s++)
+      if (s < a.splits) v[s] = *(const float4*)(a.part + ((int64_t)s * T + t) * nqkv + col);
+    sxr = a.sx[t];
+  } else {
+    v[0] = *(const float4*)(a.qkv_f32 + t * nqkv + col);
+  }
   if (p < 0 || p >= a.maxlen || p >= a.max_pos) return;  // host validates; never index outside the cache
   float4 c = make_float4(0.f, 0.f, 0.f, 0.f), sn4 = c;
   if (!is_v) {
@@ -131,12 +137,17 @@ __global__ void __launch_bounds__(256) rope_decode_kernel(RopeDev a, int64_t T) 
     c = *(const float4*)(a.cos_t + (int64_t)p * (D / 2) + i0);
     sn4 = *(const float4*)(a.sin_t + (int64_t)p * (D / 2) + i0);
   }
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float x[4];
+  if (a.part) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-  for (int s = 0; s < 8; s++)
-    if (s < a.splits) { acc[0] += v[s].x; acc[1] += v[s].y; acc[2] += v[s].z; acc[3] += v[s].w; }
-  float x[4] = {__fmul_rn(__fmul_rn(acc[0], sxr), w.x), __fmul_rn(__fmul_rn(acc[1], sxr), w.y), __fmul_rn(__fmul_rn(acc[2], sxr), w.z),
-                __fmul_rn(__fmul_rn(acc[3], sxr), w.w)};
+    for (int s = 0; s < 8; s++)
+      if (s < a.splits) { acc[0] += v[s].x; acc[1] += v[s].y; acc[2] += v[s].z; acc[3] += v[s].w; }
+    x[0] = __fmul_rn(__fmul_rn(acc[0], sxr), w.x); x[1] = __fmul_rn(__fmul_rn(acc[1], sxr), w.y);
+    x[2] = __fmul_rn(__fmul_rn(acc[2], sxr), w.z); x[3] = __fmul_rn(__fmul_rn(acc[3], sxr), w.w);
+  } else {
+    x[0] = v[0].x; x[1] = v[0].y; x[2] = v[0].z; x[3] = v[0].w;
+  }
   float o[4];
   if (!is_v) {
     float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
@@ -175,7 +186,7 @@ int k_rope_qknorm_kvappend(strictb200_ctx* ctx, const RopeArgs& a, int64_t T) {
   int nheads = a.Hq + 2 * a.Hkv;
   // few rows (decode): spread the heads of a row over several blocks, one head per warp
   dim3 grid((unsigned)T, T <= 256 ? (unsigned)((nheads + 7) / 8) : 1u);
-  if (T <= 256 && a.part && a.splits <= 8 && !a.seq && !a.pos) {
+  if (T <= 256 && ((a.part && a.splits <= 8) || (!a.part && a.qkv_f32)) && !a.seq && !a.pos) {
     SB_CUDA(sb_launch(ctx, rope_decode_kernel, grid, dim3(256), 0, v, T));
     ctx->launches++;
     return STRICTB200_OK;
