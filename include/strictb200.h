@@ -71,6 +71,18 @@ int strictb200_device_status(strictb200_ctx* ctx, int* out);
 /* Writes `bytes` to a private buffer (> L2) so the next kernel starts with a cold L2. */
 int strictb200_flush_l2(strictb200_ctx* ctx);
 
+/* ---- recorded call sequences. The reference launches one kernel per `kernel.Run` call
+ * (Strict.Compiler.Cuda.Tests/CSharpToCudaTranspilerTests.cs:77,86) and has no counterpart of
+ * this: the calls made on the context between begin and end are recorded into a CUDA graph
+ * instead of being run, and graph_launch replays them `times` times on the context's stream
+ * with one submission each. While recording, make no call that synchronises, copies to or from
+ * host memory, or grows a scratch buffer: run the sequence once before recording it. */
+typedef struct strictb200_graph strictb200_graph;
+int strictb200_graph_begin(strictb200_ctx* ctx);
+int strictb200_graph_end(strictb200_ctx* ctx, strictb200_graph** out);
+int strictb200_graph_launch(strictb200_ctx* ctx, strictb200_graph* g, int times);
+int strictb200_graph_destroy(strictb200_graph* g);
+
 /* ---- element-wise surface: what the kernels emitted by InstructionsToCuda compute
  * (Strict.Compiler.Cuda/InstructionsToCuda.cs:58-73,101-109), compiled ahead of time. */
 enum strictb200_ew_op { STRICTB200_ADD = 0, STRICTB200_SUBTRACT = 1, STRICTB200_MULTIPLY = 2, STRICTB200_DIVIDE = 3 };

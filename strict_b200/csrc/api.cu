@@ -27,6 +27,20 @@ int sb_ws(strictb200_ctx* ctx, size_t bytes, void** out) {
   return STRICTB200_OK;
 }
 
+int sb_ws2(strictb200_ctx* ctx, size_t bytes, void** out) {
+  if (bytes > ctx->ws2_bytes) {
+    SB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->ws2) SB_CUDA(cudaFree(ctx->ws2));
+    ctx->ws2 = nullptr;
+    ctx->ws2_bytes = 0;
+    size_t want = bytes + (bytes >> 2) + (1 << 20);
+    SB_CUDA(cudaMalloc(&ctx->ws2, want));
+    ctx->ws2_bytes = want;
+  }
+  *out = ctx->ws2;
+  return STRICTB200_OK;
+}
+
 __global__ void flush_kernel(uint4* p, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) p[i] = make_uint4((uint32_t)i, 0u, 0u, 0u);
@@ -74,11 +88,62 @@ int strictb200_destroy(strictb200_ctx* ctx) {
   if (ctx->ws) cudaFree(ctx->ws);
   if (ctx->flush_buf) cudaFree(ctx->flush_buf);
   if (ctx->gemm_ws) cudaFree(ctx->gemm_ws);
+  if (ctx->ws2) cudaFree(ctx->ws2);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   cudaEventDestroy(ctx->ev0);
   cudaEventDestroy(ctx->ev1);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
+  return STRICTB200_OK;
+}
+
+// ---------------------------------------------------------------- recorded call sequences
+struct strictb200_graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  uint64_t launches = 0;  // kernels in the recorded sequence
+};
+int strictb200_graph_begin(strictb200_ctx* ctx) {
+  SB_ENTER(ctx);
+  SB_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+  ctx->rec_launches0 = ctx->launches;
+  return STRICTB200_OK;
+}
+int strictb200_graph_end(strictb200_ctx* ctx, strictb200_graph** out) {
+  SB_ENTER(ctx);
+  cudaGraph_t g = nullptr;
+  cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+  const uint64_t recorded = ctx->launches - ctx->rec_launches0;
+  ctx->launches = ctx->rec_launches0;  // recorded kernels have not run
+  if (e != cudaSuccess || !g) {
+    cudaGetLastError();
+    return sb_fail(STRICTB200_ERR_CUDA, std::string("recording failed (a recorded call synchronised, copied or allocated?): ") + cudaGetErrorString(e));
+  }
+  SB_REQUIRE(out, "null output pointer");
+  strictb200_graph* r = new strictb200_graph;
+  r->graph = g;
+  r->launches = recorded;
+  e = cudaGraphInstantiate(&r->exec, g, 0);
+  if (e != cudaSuccess) {
+    cudaGraphDestroy(g);
+    delete r;
+    return sb_fail(STRICTB200_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+  }
+  *out = r;
+  return STRICTB200_OK;
+}
+int strictb200_graph_launch(strictb200_ctx* ctx, strictb200_graph* g, int times) {
+  SB_ENTER(ctx);
+  SB_REQUIRE(g && g->exec && times >= 0, "bad graph or repeat count");
+  for (int i = 0; i < times; i++) SB_CUDA(cudaGraphLaunch(g->exec, ctx->stream));
+  ctx->launches += g->launches * (uint64_t)times;
+  return STRICTB200_OK;
+}
+int strictb200_graph_destroy(strictb200_graph* g) {
+  if (!g) return STRICTB200_OK;
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  if (g->graph) cudaGraphDestroy(g->graph);
+  delete g;
   return STRICTB200_OK;
 }
 
@@ -261,6 +326,16 @@ static int gemm_entry(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, cons
   g.xq = xq; g.ldx = K; g.sx = sx; g.wq = wq; g.ldw = K; g.sw = sw;
   g.out = out; g.out_f32 = out_dtype; g.kernel = kernel;
   g.splits = 1;
+  // few tokens, automatic kernel choice: the job is a stream of weights, so K is split until the
+  // grid covers the GPU and a second kernel sums the partial results
+  const int splits = (kernel == 0 || kernel == 3) && N % 4 == 0 ? sb_gemm_pick_splits(ctx, M, N, K) : 1;
+  if (splits > 1) {
+    void* ws;
+    SB_TRY(sb_ws2(ctx, (size_t)splits * M * N * sizeof(float), &ws));
+    g.out = nullptr; g.part = (float*)ws; g.splits = splits; g.raw = 1;
+    SB_TRY(k_gemm_fp8(ctx, g));
+    return k_reduce_scale(ctx, (const float*)ws, splits, sx, sw, M, N, out_dtype ? (float*)out : nullptr, out_dtype ? nullptr : (bf16*)out);
+  }
   return k_gemm_fp8(ctx, g);
 }
 int strictb200_gemm_fp8(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const uint8_t* xq, const float* sx, const uint8_t* wq,

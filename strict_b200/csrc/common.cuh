@@ -37,6 +37,9 @@ struct strictb200_ctx {
   // scratch for op-level entry points (quantised activations, split partials)
   void* ws = nullptr;
   size_t ws_bytes = 0;
+  uint64_t rec_launches0 = 0;  // launch counter when a recording began
+  void* ws2 = nullptr;  // second scratch (split-K partial results of the stand-alone GEMM entry)
+  size_t ws2_bytes = 0;
   void* flush_buf = nullptr;
   size_t flush_bytes = 0;
   int tp_world = 1, tp_rank = 0;
@@ -52,6 +55,7 @@ struct strictb200_ctx {
 void sb_set_error(const std::string& msg);
 int sb_fail(int code, const std::string& msg);
 int sb_ws(strictb200_ctx* ctx, size_t bytes, void** out);  // grow-only context scratch
+int sb_ws2(strictb200_ctx* ctx, size_t bytes, void** out);  // a second one, for calls that already hold the first
 
 #define SB_CUDA(expr)                                                                          \
   do {                                                                                         \
@@ -128,7 +132,8 @@ struct RowNormArgs {
   float* qscale = nullptr;           // [M]
 };
 int k_rownorm(strictb200_ctx*, const RowNormArgs& a, int64_t M, int64_t d);
-int k_reduce_scale(strictb200_ctx*, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N, float* out);
+int k_reduce_scale(strictb200_ctx*, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N, float* out,
+                   bf16* out_bf16 = nullptr);
 int k_layernorm(strictb200_ctx*, const float* x, const float* g, const float* b, float eps, int64_t M, int64_t d, float* y);
 int k_add_f32(strictb200_ctx*, float* x, const float* y, int64_t n);
 int k_swiglu(strictb200_ctx*, const bf16* gate_up, const float* gate_up_f32, int64_t M, int64_t I, bf16* y, uint8_t* q, float* qscale);

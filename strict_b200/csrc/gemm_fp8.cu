@@ -265,8 +265,14 @@ int launch_skinny(strictb200_ctx* ctx, const GemmDev& d) {
 
 // Number of K splits for a skinny GEMM so that the grid covers the SMs about twice.
 int sb_gemm_pick_splits(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K) {
-  if (M > 32 || K % 128) return 1;
+  if (M > 128 || K % 128) return 1;
   const int64_t tiles = (N + SK_ROWS - 1) / SK_ROWS, nkb = K / 128;
+  if (M > 32) {
+    // 33..128 tokens: one block per SM fits (its ring fills the shared memory); split K until the grid covers the GPU
+    int64_t s = ctx->sm_count / tiles;
+    if (s > nkb / 2) s = nkb / 2;
+    return (int)(s < 1 ? 1 : (s > 8 ? 8 : s));
+  }
   // About 1.6 blocks per SM (two blocks of this kernel fit an SM, so all of them are resident
   // at once and share its bandwidth) measured best on the decode shapes; more than 8 partial
   // results are not taken by the kernels that sum them.

@@ -517,10 +517,10 @@ int k_gelu_tanh(strictb200_ctx* ctx, const float* x, int64_t n, float* y) {
   return STRICTB200_OK;
 }
 
-// out[m,n] = (sum_s part[s][m,n]) * sx[m] * sw[n]  (fp32; the input of a cross-rank all-reduce)
+// out[m,n] = (sum_s part[s][m,n]) * sx[m] * sw[n], fp32 (the input of a cross-rank all-reduce) or bf16
 namespace {
 __global__ void reduce_scale_kernel(const float* __restrict__ part, int splits, const float* __restrict__ sx, const float* __restrict__ sw,
-                                    int64_t M, int64_t N, float* __restrict__ out) {
+                                    int64_t M, int64_t N, float* __restrict__ out, bf16* __restrict__ out_bf16) {
   pdl_trigger();
   pdl_wait();
   int64_t total = M * N / 4, stride = (int64_t)gridDim.x * blockDim.x;
@@ -536,13 +536,15 @@ __global__ void reduce_scale_kernel(const float* __restrict__ part, int splits, 
     float4 r;
     r.x = __fmul_rn(__fmul_rn(acc.x, a), w.x); r.y = __fmul_rn(__fmul_rn(acc.y, a), w.y);
     r.z = __fmul_rn(__fmul_rn(acc.z, a), w.z); r.w = __fmul_rn(__fmul_rn(acc.w, a), w.w);
-    *(float4*)(out + m * N + n) = r;
+    if (out) *(float4*)(out + m * N + n) = r;
+    else *(uint2*)(out_bf16 + m * N + n) = make_uint2(f32_to_bf16_bits(r.x) | (f32_to_bf16_bits(r.y) << 16), f32_to_bf16_bits(r.z) | (f32_to_bf16_bits(r.w) << 16));
   }
 }
 }  // namespace
-int k_reduce_scale(strictb200_ctx* ctx, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N, float* out) {
+int k_reduce_scale(strictb200_ctx* ctx, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N, float* out,
+                   bf16* out_bf16) {
   if (N % 4) return sb_fail(STRICTB200_ERR_INVALID_ARG, "reduce_scale: N must be a multiple of 4");
-  SB_CUDA(sb_launch(ctx, reduce_scale_kernel, dim3(stream_grid(ctx, M * N / 4, 256)), dim3(256), 0, part, splits, sx, sw, M, N, out));
+  SB_CUDA(sb_launch(ctx, reduce_scale_kernel, dim3(stream_grid(ctx, M * N / 4, 256)), dim3(256), 0, part, splits, sx, sw, M, N, out, out_bf16));
   ctx->launches++;
   return STRICTB200_OK;
 }

@@ -32,6 +32,31 @@ class Context:
         N.check(N.lib().strictb200_timer_end(self.h, C.byref(ms)))
         return ms.value
 
+    def record(self):
+        """Context manager: the calls made inside are recorded, not run; yields nothing and leaves
+        the recorded sequence in ``self.last_graph`` (replay with ``replay(graph, times)``)."""
+        ctx = self
+
+        class _Rec:
+            def __enter__(self):
+                N.check(N.lib().strictb200_graph_begin(ctx.h))
+
+            def __exit__(self, et, ev, tb):
+                g = C.c_void_p()
+                st = N.lib().strictb200_graph_end(ctx.h, C.byref(g))
+                if et is None:
+                    N.check(st)
+                    ctx.last_graph = g
+                return False
+
+        return _Rec()
+
+    def replay(self, graph, times=1):
+        N.check(N.lib().strictb200_graph_launch(self.h, graph, times))
+
+    def free_graph(self, graph):
+        N.check(N.lib().strictb200_graph_destroy(graph))
+
     def launch_count(self):
         n = C.c_uint64()
         N.check(N.lib().strictb200_launch_count(self.h, C.byref(n)))

@@ -51,6 +51,10 @@ SIGNATURES = {
     "strictb200_launch_count": [vp, C.POINTER(u64)],
     "strictb200_flush_l2": [vp],
     "strictb200_device_status": [vp, C.POINTER(i32)],
+    "strictb200_graph_begin": [vp],
+    "strictb200_graph_end": [vp, C.POINTER(vp)],
+    "strictb200_graph_launch": [vp, vp, i32],
+    "strictb200_graph_destroy": [vp],
     "strictb200_ew_binary": [vp, i32, vp, vp, vp, i64],
     "strictb200_ew_program": [vp, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64],
     "strictb200_gen_normal_f32": [vp, u64, u64, i64, i64, f32, vp],

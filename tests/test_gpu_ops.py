@@ -201,6 +201,43 @@ def test_gemm_kernels_agree_and_linearity(ctx, oracle, rng):
     assert np.allclose(outs[0].reshape(M, N_)[:, rows], want, rtol=2e-5, atol=1e-5 * scale)
 
 
+@pytest.mark.parametrize("M,N_,K", [(1, 4096, 4096), (8, 1024, 3072), (32, 4096, 4096), (32, 1008, 1536), (17, 6144, 4096), (100, 4096, 4096), (128, 1008, 1536)])
+@pytest.mark.parametrize("out_dtype", [0, 1])
+def test_gemm_auto_split_k_vs_oracle(ctx, oracle, rng, M, N_, K, out_dtype):
+    """kernel 0 with few tokens: K splits (uneven where K/128 does not divide) and a summing kernel."""
+    got, want = _gemm_case(ctx, oracle, rng, M, N_, K, kernel=0, out_dtype=out_dtype)
+    if out_dtype:
+        assert np.allclose(got, want, rtol=2e-5, atol=1e-5 * np.abs(want).max())
+    else:
+        ref = oracle.round_bf16(want)
+        assert np.abs(got - ref).max() <= np.abs(ref).max() * 2 ** -7 and (got != ref).mean() < 1e-3
+
+
+def test_recorded_sequence_replays(ctx, oracle, rng):
+    """Calls made while recording do not run; a replay runs them, `times` times, and counts its launches."""
+    n = 1 << 12
+    a = rng.standard_normal(n).astype(np.float32)
+    da, dout = DV.of(ctx, a), DV(ctx, n)
+    N.check(L().strictb200_ew_binary(ctx.h, 0, da.p, da.p, dout.p, n))  # out = 2a
+    ctx.synchronize()
+    launches0 = ctx.launch_count()
+    with ctx.record():
+        N.check(L().strictb200_ew_binary(ctx.h, 0, dout.p, da.p, dout.p, n))  # out += a
+        N.check(L().strictb200_ew_binary(ctx.h, 0, dout.p, da.p, dout.p, n))
+    graph = ctx.last_graph
+    assert ctx.launch_count() == launches0
+    assert np.array_equal(dout.to_host(), a + a)  # nothing ran yet
+    ctx.replay(graph, 3)
+    want = a + a
+    for _ in range(6):
+        want = want + a
+    assert np.array_equal(dout.to_host(), want)
+    assert ctx.launch_count() == launches0 + 6
+    ctx.free_graph(graph)
+    for v in (da, dout):
+        v.free()
+
+
 def test_gemm_fp8w_entry(ctx, oracle, rng):
     M, N_, K = 8, 512, 1024
     x = oracle.round_bf16(rng.standard_normal((M, K)).astype(np.float32))
