@@ -416,6 +416,7 @@ int launch(strictb200_ctx* ctx, const GemmArgs& g, TmemArgs ta) {
 }  // namespace
 
 int k_gemm_fp8_tmem_split(strictb200_ctx* ctx, const GemmArgs& g);  // gemm_tmem_split.cu
+int k_gemm_fp8_tmem_pair(strictb200_ctx* ctx, const GemmArgs& g);   // gemm_tmem_pair.cu
 
 int k_gemm_fp8_tmem(strictb200_ctx* ctx, const GemmArgs& g) {
   if (g.K % BK) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "tensor-memory GEMM needs K to be a multiple of 128");
@@ -423,6 +424,9 @@ int k_gemm_fp8_tmem(strictb200_ctx* ctx, const GemmArgs& g) {
   if (g.splits != 1 || g.raw) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "the persistent tensor-memory GEMM produces complete outputs");
   if (((uintptr_t)g.xq | (uintptr_t)g.wq | (uintptr_t)g.ldx | (uintptr_t)g.ldw) & 15)
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: operands and row strides must be 16-byte aligned");
+  // many tokens: two SMs per 256 x 256 tile (half the operand bytes per flop through each SM)
+  static const int pair = getenv("STRICTB200_GEMM_PAIR") ? atoi(getenv("STRICTB200_GEMM_PAIR")) : 1;
+  if (pair && g.N >= 256 && ctx->sm_count >= 2) return k_gemm_fp8_tmem_pair(ctx, g);
   SB_TRY(get_encode());
   static const int prefetch = getenv("STRICTB200_PREFETCH") ? atoi(getenv("STRICTB200_PREFETCH")) : 1;
   TmemArgs ta{};
