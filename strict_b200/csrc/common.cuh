@@ -137,6 +137,9 @@ int k_reduce_scale(strictb200_ctx*, const float* part, int splits, const float* 
 int k_layernorm(strictb200_ctx*, const float* x, const float* g, const float* b, float eps, int64_t M, int64_t d, float* y);
 int k_add_f32(strictb200_ctx*, float* x, const float* y, int64_t n);
 int k_swiglu(strictb200_ctx*, const bf16* gate_up, const float* gate_up_f32, int64_t M, int64_t I, bf16* y, uint8_t* q, float* qscale);
+// gate_up as split-K partials [splits][M][2I] + scales -> two-term split of silu(gate)*up
+int k_swiglu_part(strictb200_ctx*, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t I, uint8_t* q,
+                  float* qscale);
 int k_gelu_tanh(strictb200_ctx*, const float* x, int64_t n, float* y);
 // rope.cu
 struct RopeArgs {

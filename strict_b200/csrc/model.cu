@@ -150,6 +150,14 @@ struct Carver {
 struct GemmPlan { int splits; };
 
 int plan_splits(strictb200_model* m, int64_t M, int64_t N, int64_t K) { return sb_gemm_pick_splits(m->ctx, M, N, K); }
+// K splits of the decode gate/up projection: 1 (the GEMM writes the scaled fp32 result) unless the
+// shard is so narrow that its tiles leave most SMs idle; the SwiGLU kernel sums at most 4 partials.
+int plan_gate_up_splits(strictb200_model* m, int64_t M) {
+  const int64_t tiles = (2 * (int64_t)m->I_l + 127) / 128;
+  if (M > 32 || m->I_l % 128 || tiles >= m->ctx->sm_count) return 1;
+  int s = sb_gemm_pick_splits(m->ctx, M, 2 * (int64_t)m->I_l, m->c.d_model);
+  return s > 4 ? 4 : s;
+}
 
 void carve_decode(strictb200_kv* kv, char* base, DecBuf* out, size_t* total) {
   strictb200_model* m = kv->m;
@@ -166,7 +174,8 @@ void carve_decode(strictb200_kv* kv, char* base, DecBuf* out, size_t* total) {
     size_t p1 = (size_t)plan_splits(m, B, nqkv, d) * B * nqkv;
     size_t p2 = (size_t)plan_splits(m, B, d, nq) * B * d;
     size_t p3 = (size_t)plan_splits(m, B, d, m->I_l) * B * d;
-    b.part = cv.take<float>(std::max(p1, std::max(p2, p3)));
+    size_t p4 = (size_t)plan_gate_up_splits(m, B) * B * 2 * m->I_l;
+    b.part = cv.take<float>(std::max(std::max(p1, p2), std::max(p3, p4)));
     b.qb = cv.take<bf16>(B * nq);
     b.att = cv.take<bf16>(B * nq);
     b.gu = cv.take<float>(B * 2 * m->I_l);
@@ -338,8 +347,16 @@ int qwen_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
       PROF(STRICTB200_K_ROWNORM, k_rownorm(ctx, a, B, d));
     }
     // gate/up -> bf16, SwiGLU + quantise, down -> partials -> residual + next norm + quantise
-    PROF(STRICTB200_K_GEMM_GU, run_gemm(m, B, w.wgu, b.aq, b.sa, b.gu, 1, nullptr, 1, 0));
-    PROF(STRICTB200_K_SWIGLU, k_swiglu(ctx, nullptr, b.gu, B, m->I_l, nullptr, b.aq, b.sa));
+    const int s3 = plan_gate_up_splits(m, B);
+    if (s3 > 1) {
+      // narrow shard: K splits so that the grid covers the GPU; SwiGLU sums the partials (every
+      // block of a row has read the row's input scale before the row's new scale is written)
+      PROF(STRICTB200_K_GEMM_GU, run_gemm(m, B, w.wgu, b.aq, b.sa, nullptr, 0, b.part, s3, 1));
+      PROF(STRICTB200_K_SWIGLU, k_swiglu_part(ctx, b.part, s3, b.sa, w.wgu.s, B, m->I_l, b.aq, b.sa));
+    } else {
+      PROF(STRICTB200_K_GEMM_GU, run_gemm(m, B, w.wgu, b.aq, b.sa, b.gu, 1, nullptr, 1, 0));
+      PROF(STRICTB200_K_SWIGLU, k_swiglu(ctx, nullptr, b.gu, B, m->I_l, nullptr, b.aq, b.sa));
+    }
     int s4 = plan_splits(m, B, d, m->I_l);
     PROF(STRICTB200_K_GEMM_DOWN, run_gemm(m, B, w.wdown, b.aq, b.sa, nullptr, 0, b.part, s4, 1));
     {

@@ -428,6 +428,52 @@ __global__ void __launch_bounds__(512) swiglu_decode_kernel(const float* __restr
   sb_store_split8(q, I, row, k, h, sb_pow2(-e));
 }
 
+// The same for a gate/up projection that arrives as at most 4 raw split-K partials
+// [splits][M][2I] with the scales still to apply (the narrow shards of tensor parallelism, whose
+// GEMM needs K splits to cover the GPU): 4 columns per thread, so 2 x splits loads in flight.
+__global__ void __launch_bounds__(512) swiglu_decode_part_kernel(const float* __restrict__ part, int splits, const float* __restrict__ sx,
+                                                                 const float* __restrict__ sw, int64_t M, int64_t I, uint8_t* __restrict__ q,
+                                                                 float* __restrict__ qscale, int* __restrict__ status) {
+  __shared__ float red[32];
+  __shared__ __align__(8) ClusterExchange xch;
+  if (gridDim.y > 1) cluster_exchange_init(&xch);
+  pdl_trigger();
+  const int64_t row = blockIdx.x, k = ((int64_t)blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  const float4 wg = *(const float4*)(sw + k), wu = *(const float4*)(sw + I + k);
+  pdl_wait();
+  float4 pg[4], pu[4];
+#pragma unroll
+  for (int s = 0; s < 4; s++)
+    if (s < splits) {
+      const float* p = part + ((int64_t)s * M + row) * 2 * I + k;
+      pg[s] = *(const float4*)p;
+      pu[s] = *(const float4*)(p + I);
+    }
+  const float sxr = sx[row];
+  float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int s = 0; s < 4; s++)
+    if (s < splits) {
+      g[0] += pg[s].x; g[1] += pg[s].y; g[2] += pg[s].z; g[3] += pg[s].w;
+      u[0] += pu[s].x; u[1] += pu[s].y; u[2] += pu[s].z; u[3] += pu[s].w;
+    }
+  const float wgv[4] = {wg.x, wg.y, wg.z, wg.w}, wuv[4] = {wu.x, wu.y, wu.z, wu.w};
+  float h[4], amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    h[i] = round_bf16(silu_mul(__fmul_rn(__fmul_rn(g[i], sxr), wgv[i]), __fmul_rn(__fmul_rn(u[i], sxr), wuv[i])));
+    amax = fmaxf(amax, fabsf(h[i]));
+  }
+  amax = block_max(amax, red);
+  if (gridDim.y > 1) {
+    if (!cluster_exchange(&xch, amax, gridDim.y, blockIdx.y) && threadIdx.x == 0) { *(volatile int*)status = 6; __threadfence_system(); }
+    for (uint32_t r = 0; r < gridDim.y; r++) amax = fmaxf(amax, ((volatile float*)xch.slot)[r]);
+  }
+  const int e = sb_scale_exponent(amax);
+  if (blockIdx.y == 0 && threadIdx.x == 0) qscale[row] = sb_pow2(e);
+  sb_store_split4(q, I, row, k, h, sb_pow2(-e));
+}
+
 __global__ void gelu_tanh_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ y) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -510,6 +556,18 @@ int k_swiglu(strictb200_ctx* ctx, const bf16* gate_up, const float* gate_up_f32,
   SB_CUDA(sb_launch(ctx, swiglu_kernel, dim3((unsigned)M), dim3(SW_THREADS), 0, gate_up, gate_up_f32, I, y, q, qscale));
   ctx->launches++;
   return STRICTB200_OK;
+}
+int k_swiglu_part(strictb200_ctx* ctx, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t I, uint8_t* q,
+                  float* qscale) {
+  if (splits < 1 || splits > 4 || I % 128) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "swiglu over partials: at most 4 splits, I a multiple of 128");
+  for (int c = 1; c <= 8; c++) {
+    if (I % (4 * c) || (I / (4 * c)) % 32 || I / (4 * c) > 512) continue;
+    SB_CUDA(sb_launch_cluster(ctx, swiglu_decode_part_kernel, dim3((unsigned)M, (unsigned)c), dim3((unsigned)(I / (4 * c))), 0, dim3(1, (unsigned)c, 1), part,
+                              splits, sx, sw, M, I, q, qscale, ctx->d_status));
+    ctx->launches++;
+    return STRICTB200_OK;
+  }
+  return sb_fail(STRICTB200_ERR_UNSUPPORTED, "swiglu over partials: no block shape for this width");
 }
 int k_gelu_tanh(strictb200_ctx* ctx, const float* x, int64_t n, float* y) {
   gelu_tanh_kernel<<<stream_grid(ctx, n, 256), 256, 0, ctx->stream>>>(x, n, y);
