@@ -25,6 +25,13 @@ struct TpCommDev {
   int* status;      // host-visible error word
   int world, rank;
   long long max_elems;
+  // Row-granular variant (the row kernel itself exchanges the sums): every value is pushed into
+  // the peers' buffers as an 8-byte packet {value, epoch}, so a packet validates itself and
+  // neither fences nor separate flags are needed.
+  float* row_data[8];   // rank r's packet area: [parity][source rank][row_elems][2] words
+  int* row_epoch;       // this rank's per-row epoch counters (device memory, one writer per row)
+  long long row_elems;  // values per (parity, source rank)
+  int max_rows;
 };
 struct SbProfiler;  // model.cu
 

@@ -333,9 +333,9 @@ int qwen_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
     {
       RowNormArgs a;
       if (tp && sb_tp_comm(ctx)) {
-        // one-shot all-reduce over peer memory, fused into the row kernel that consumes it
-        PROF(STRICTB200_K_ALLREDUCE, k_tp_publish(ctx, b.part, s2, b.sa, w.wo.s, B, d));
+        // one-shot all-reduce over peer memory inside the row kernel that consumes it
         a.comm = sb_tp_comm(ctx);
+        a.part = b.part; a.splits = s2; a.sx = b.sa; a.sw = w.wo.s;
       } else if (tp) {
         PROF(STRICTB200_K_ROWNORM, k_reduce_scale(ctx, b.part, s2, b.sa, w.wo.s, B, d, b.red));
         PROF(STRICTB200_K_ALLREDUCE, sb_tp_allreduce_f32(ctx, b.red, B * d));
@@ -362,8 +362,8 @@ int qwen_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
     {
       RowNormArgs a;
       if (tp && sb_tp_comm(ctx)) {
-        PROF(STRICTB200_K_ALLREDUCE, k_tp_publish(ctx, b.part, s4, b.sa, w.wdown.s, B, d));
         a.comm = sb_tp_comm(ctx);
+        a.part = b.part; a.splits = s4; a.sx = b.sa; a.sw = w.wdown.s;
       } else if (tp) {
         PROF(STRICTB200_K_ROWNORM, k_reduce_scale(ctx, b.part, s4, b.sa, w.wdown.s, B, d, b.red));
         PROF(STRICTB200_K_ALLREDUCE, sb_tp_allreduce_f32(ctx, b.red, B * d));

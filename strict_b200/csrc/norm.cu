@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
   const int64_t row = blockIdx.x, k = (int64_t)threadIdx.x * 4;
   pdl_trigger();
   float4 sw = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (MODE == 0) sw = *(const float4*)(a.sw + k);
+  if (MODE == 0 || MODE == 3) sw = *(const float4*)(a.sw + k);
   const float4 g = *(const float4*)(a.gain + k);
   pdl_wait();
   float t[4] = {0.f, 0.f, 0.f, 0.f};
@@ -257,6 +257,56 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
     t[1] += __fmul_rn(__fmul_rn(acc[1], sxr), sw.y);
     t[2] += __fmul_rn(__fmul_rn(acc[2], sxr), sw.z);
     t[3] += __fmul_rn(__fmul_rn(acc[3], sxr), sw.w);
+  } else if (MODE == 3) {
+    // Fused all-reduce, row-granular: this block sums the rank's own split-K partials of its row
+    // and pushes every value, paired with the row's epoch, into every peer's buffer (two 16-byte
+    // stores of two {value, epoch} packets each); then it polls its own buffer until the packets
+    // of the same row have arrived from every peer and adds the ranks' values in rank order.
+    // One NVLink one-way latency, no fence, no other kernel, no grid-wide step. The waits are
+    // bounded; on expiry the error word is set and the (wrong) sum is used.
+    float4 p[8];
+#pragma unroll
+    for (int s = 0; s < 8; s++)
+      if (s < a.splits) p[s] = *(const float4*)(a.part + (((int64_t)s * M + row) * d + k));
+    const float sxr = a.sx[row];
+    const int e = *(volatile int*)(a.comm.row_epoch + row) + 1;  // this block is the row's only writer
+    if (a.residual_f32) r4 = *(const float4*)(a.residual_f32 + row * d + k);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < 8; s++)
+      if (s < a.splits) { acc[0] += p[s].x; acc[1] += p[s].y; acc[2] += p[s].z; acc[3] += p[s].w; }
+    const float own[4] = {__fmul_rn(__fmul_rn(acc[0], sxr), sw.x), __fmul_rn(__fmul_rn(acc[1], sxr), sw.y),
+                          __fmul_rn(__fmul_rn(acc[2], sxr), sw.z), __fmul_rn(__fmul_rn(acc[3], sxr), sw.w)};
+    const float ef = __int_as_float(e);
+    const size_t val = (size_t)(row * d + k) * 2;  // word offset of this thread's 4 packets inside a (parity, source) area
+    const size_t area = (size_t)a.comm.row_elems * 2;
+#pragma unroll
+    for (int r = 0; r < 8; r++)
+      if (r < a.comm.world && r != a.comm.rank) {
+        float* dst = a.comm.row_data[r] + ((size_t)(e & 1) * 8 + a.comm.rank) * area + val;
+        asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(own[0]), "f"(ef), "f"(own[1]), "f"(ef) : "memory");
+        asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 4), "f"(own[2]), "f"(ef), "f"(own[3]), "f"(ef) : "memory");
+      }
+#pragma unroll
+    for (int r = 0; r < 8; r++)
+      if (r < a.comm.world) {
+        if (r == a.comm.rank) {
+          t[0] += own[0]; t[1] += own[1]; t[2] += own[2]; t[3] += own[3];
+        } else {
+          const float* src = a.comm.row_data[a.comm.rank] + ((size_t)(e & 1) * 8 + r) * area + val;
+          float4 q0, q1;
+          uint32_t spins = 0;
+          while (true) {
+            q0 = ld_peer4(src);
+            q1 = ld_peer4(src + 4);
+            if (__float_as_int(q0.y) == e && __float_as_int(q0.w) == e && __float_as_int(q1.y) == e && __float_as_int(q1.w) == e) break;
+            if (++spins > (1u << 22)) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
+          }
+          t[0] += q0.x; t[1] += q0.z; t[2] += q1.x; t[3] += q1.z;
+        }
+      }
+    __syncthreads();  // every thread of the row has read the epoch
+    if (threadIdx.x == 0) *(volatile int*)(a.comm.row_epoch + row) = e;
   } else if (MODE == 2) {
     const float4 p = *(const float4*)(a.x_f32 + row * d + k);
     if (a.residual_f32) r4 = *(const float4*)(a.residual_f32 + row * d + k);
@@ -512,6 +562,17 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale};
   // decode-step shapes: 4 columns per thread, at most 8 partials, no bf16 residual
   const bool narrow = d % 128 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
+  if (narrow && a.comm && a.part && a.groups == 1 && a.splits <= 8 && a.comm->world <= 8 && M <= a.comm->max_rows && M * d <= a.comm->row_elems) {
+    SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<3>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
+    ctx->launches++;
+    return STRICTB200_OK;
+  }
+  if (a.comm && a.part) {
+    // shapes the row-granular exchange does not take: publish the scaled sums with a kernel of
+    // their own, then the row kernel only gathers
+    SB_TRY(k_tp_publish(ctx, a.part, a.splits, a.sx, a.sw, M, d));
+    v.part = nullptr;
+  }
   if (narrow && a.comm && a.comm->world <= 8) {
     SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<1>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
     ctx->launches++;

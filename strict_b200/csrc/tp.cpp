@@ -48,14 +48,18 @@ int nccl_fail(const char* what, int rc) {
 
 constexpr long long COMM_MAX_ELEMS = 1 << 20;  // floats per epoch parity (4 MiB): 64 tokens x 16384 channels
 constexpr size_t COMM_FLAG_BYTES = 256;        // 2 parities x 8 source ranks, padded
-constexpr size_t COMM_BYTES = COMM_FLAG_BYTES + 2 * COMM_MAX_ELEMS * sizeof(float);
+constexpr int COMM_ROWS = 64;                  // rows of the row-granular exchange
+constexpr long long COMM_ROW_ELEMS = (long long)COMM_ROWS * 4096;  // values per (parity, source rank) of the row area
+// row area: [parity][source rank][value][2] words, every value travelling with its epoch (8-byte packets)
+constexpr size_t COMM_ROW_OFFSET = COMM_FLAG_BYTES + 2 * COMM_MAX_ELEMS * sizeof(float);
+constexpr size_t COMM_BYTES = COMM_ROW_OFFSET + (size_t)2 * 8 * COMM_ROW_ELEMS * 2 * sizeof(float);
 
 struct TpState {
   nccl_comm comm = nullptr;
   // peer-memory all-reduce
-  void* comm_buf = nullptr;       // this rank's buffer: [flags | data parity 0 | data parity 1]
+  void* comm_buf = nullptr;       // this rank's buffer: [flags | data parity 0 | data parity 1 | row packets]
   void* peer_buf[8] = {nullptr};  // every rank's buffer as mapped into this process
-  int* local = nullptr;           // [epoch, done]
+  int* local = nullptr;           // [epoch, done, ... | per-row epochs at int 64]
   bool opened = false;
   TpCommDev dev{};
 };
@@ -179,8 +183,8 @@ int strictb200_tp_comm_handle(strictb200_ctx* ctx, void* h_handle64) {
   if (!tp->comm_buf) {
     SB_CUDA(cudaMalloc(&tp->comm_buf, COMM_BYTES));
     SB_CUDA(cudaMemset(tp->comm_buf, 0, COMM_BYTES));
-    SB_CUDA(cudaMalloc((void**)&tp->local, 256));
-    SB_CUDA(cudaMemset(tp->local, 0, 256));
+    SB_CUDA(cudaMalloc((void**)&tp->local, 256 + COMM_ROWS * sizeof(int)));
+    SB_CUDA(cudaMemset(tp->local, 0, 256 + COMM_ROWS * sizeof(int)));
   }
   cudaIpcMemHandle_t h;
   SB_CUDA(cudaIpcGetMemHandle(&h, tp->comm_buf));
@@ -203,7 +207,11 @@ int strictb200_tp_comm_open(strictb200_ctx* ctx, const void* h_handles) {
   for (int r = 0; r < ctx->tp_world; r++) {
     d.flags[r] = (int*)tp->peer_buf[r];
     d.data[r] = (float*)((char*)tp->peer_buf[r] + COMM_FLAG_BYTES);
+    d.row_data[r] = (float*)((char*)tp->peer_buf[r] + COMM_ROW_OFFSET);
   }
+  d.row_epoch = tp->local + 64;
+  d.row_elems = COMM_ROW_ELEMS;
+  d.max_rows = COMM_ROWS;
   d.epoch = tp->local;
   d.done = (unsigned*)(tp->local + 1);
   d.status = ctx->d_status;
