@@ -426,7 +426,7 @@ int strictb200_attn_prefill(strictb200_ctx* ctx, const uint16_t* q, const uint16
   SB_REQUIRE(B >= 0 && S >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && maxlen > 0, "bad shape");
   if (!B || !S) return STRICTB200_OK;
   SB_REQUIRE(q && kc && vc && lens && out, "null pointer");
-  return k_attn_prefill(ctx, (const bf16*)q, (const bf16*)kc, (const bf16*)vc, lens, past, nullptr, B, S, Hq, Hkv, D, maxlen, scale, (bf16*)out);
+  return k_attn_prefill(ctx, (const bf16*)q, (const bf16*)kc, (const bf16*)vc, lens, past, nullptr, B, S, (int64_t)B * S, Hq, Hkv, D, maxlen, scale, (bf16*)out);
 }
 int strictb200_attn_decode(strictb200_ctx* ctx, const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const int32_t* lens, int B,
                            int Hq, int Hkv, int D, int maxlen, float scale, uint16_t* out) {

@@ -566,9 +566,18 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(const float* __restrict__
 
 }  // namespace
 
+int k_attn_prefill_tc(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16* vc, const int32_t* lens, const int32_t* past,
+                      const int32_t* qstart, int B, int S, int64_t q_rows, int Hq, int Hkv, int maxlen, float scale, bf16* out);  // attention_tc.cu
+
 int k_attn_prefill(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16* vc, const int32_t* lens, const int32_t* past,
-                   const int32_t* qstart, int B, int S, int Hq, int Hkv, int Dh, int maxlen, float scale, bf16* out) {
+                   const int32_t* qstart, int B, int S, int64_t q_rows, int Hq, int Hkv, int Dh, int maxlen, float scale, bf16* out) {
   if (Dh != D) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: head_dim must be 128");
+  // tcgen05 kernel first; the mma.sync kernel below takes what it declines
+  static const int use_tc = getenv("STRICTB200_ATTN_TC") ? atoi(getenv("STRICTB200_ATTN_TC")) : 1;
+  if (use_tc) {
+    int st = k_attn_prefill_tc(ctx, q, kc, vc, lens, past, qstart, B, S, q_rows, Hq, Hkv, maxlen, scale, out);
+    if (st != STRICTB200_ERR_UNSUPPORTED) return st;
+  }
   static bool attr = false;
   size_t smem = 64 * 256 + 4 * KT * 256;
   if (!attr) {

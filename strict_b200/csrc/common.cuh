@@ -194,7 +194,7 @@ int k_gemm_f32(strictb200_ctx*, int64_t M, int64_t N, int64_t K, const float* x,
                int accumulate);
 // attention.cu
 int k_attn_prefill(strictb200_ctx*, const bf16* q, const bf16* kc, const bf16* vc, const int32_t* lens, const int32_t* past,
-                   const int32_t* qstart, int B, int S, int Hq, int Hkv, int D, int maxlen, float scale, bf16* out);
+                   const int32_t* qstart, int B, int S, int64_t q_rows, int Hq, int Hkv, int D, int maxlen, float scale, bf16* out);
 size_t sb_attn_decode_scratch(int B, int Hq, int D, int nsplit);
 int sb_attn_decode_splits(strictb200_ctx*, int B, int Hkv, int maxlen);
 int k_attn_decode(strictb200_ctx*, const bf16* q, const bf16* kc, const bf16* vc, const int32_t* lens, int len_add, int B, int Hq,

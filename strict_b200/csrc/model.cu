@@ -519,7 +519,7 @@ int qwen_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb
       r.q_out = qb; r.kcache = kc; r.vcache = vc;
       SB_TRY(k_rope_qknorm_kvappend(ctx, r, T));
     }
-    SB_TRY(k_attn_prefill(ctx, qb, kc, vc, d_lens_after, d_past, d_qstart, nb, max_new, m->Hq_l, m->Hkv_l, (int)D, kv->maxlen, scale, att));
+    SB_TRY(k_attn_prefill(ctx, qb, kc, vc, d_lens_after, d_past, d_qstart, nb, max_new, T, m->Hq_l, m->Hkv_l, (int)D, kv->maxlen, scale, att));
     SB_TRY(k_quantize_rows(ctx, att, T, nq, nq, aq, sa));
     {
       RowNormArgs a;
