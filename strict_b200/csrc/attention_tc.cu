@@ -7,7 +7,8 @@
 //                    fp32 accumulator in tensor memory (128 columns)
 //   softmax          every thread reads its row of S with tcgen05.ld (twice: maximum, then
 //                    exponentials), keeps running maximum and sum, and writes P as TWO bf16
-//                    terms (hi + lo, so that P.V matches an exact-softmax oracle to fp32 noise)
+//                    terms (hi + lo by truncation, so that P.V matches an exact-softmax oracle
+//                    to 2^-16)
 //                    back to tensor memory with tcgen05.st (2 x 64 columns)
 //   O_tile = P V     tcgen05.mma with A = P from tensor memory and B = the V tile in shared
 //                    memory, read MN-major (its rows are keys = the K dimension of this product);
@@ -105,6 +106,11 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]),
       "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -223,16 +229,23 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(const __grid_const
     // ---- softmax of this thread's row
     const int k0 = t * BKV;
     const int k_lim = min(len, qpos + 1) - k0;  // keys [0, k_lim) of the tile are visible to this row
+    const bool full = k0 + BKV <= min(len, pst + q0 + 1);  // every row of the block sees the whole tile (block-uniform)
     float m_tile = -INFINITY;
 #pragma unroll 1
     for (int c = 0; c < 4; c++) {
       uint32_t r[32];
       tc_ld32(tS + lane_base + (uint32_t)(c * 32), r);
       tc_wait_ld();
+      if (full) {
 #pragma unroll
-      for (int j = 0; j < 32; j++)
-        if (c * 32 + j < k_lim) m_tile = fmaxf(m_tile, __uint_as_float(r[j]) * a.scale_log2);
+        for (int j = 0; j < 32; j++) m_tile = fmaxf(m_tile, __uint_as_float(r[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+          if (c * 32 + j < k_lim) m_tile = fmaxf(m_tile, __uint_as_float(r[j]));
+      }
     }
+    m_tile *= a.scale_log2;  // the scale is positive: the maximum commutes with it
     const float m_new = fmaxf(m_run, m_tile);
     const float m_use = m_new == -INFINITY ? 0.f : m_new;
     const float corr = exp2f(m_run - m_use);
@@ -247,12 +260,19 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(const __grid_const
 #pragma unroll
       for (int j = 0; j < 16; j++) {
         const int kk = c * 32 + 2 * j;
-        float p0 = kk < k_lim ? exp2f(__uint_as_float(r[2 * j]) * a.scale_log2 - m_use) : 0.f;
-        float p1 = kk + 1 < k_lim ? exp2f(__uint_as_float(r[2 * j + 1]) * a.scale_log2 - m_use) : 0.f;
+        float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * j]), a.scale_log2, -m_use));
+        float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * j + 1]), a.scale_log2, -m_use));
+        if (!full) {
+          if (kk >= k_lim) p0 = 0.f;
+          if (kk + 1 >= k_lim) p1 = 0.f;
+        }
         row_sum += p0 + p1;
-        const float h0 = round_bf16(p0), h1 = round_bf16(p1);
-        hi[j] = f32_to_bf16_bits(h0) | (f32_to_bf16_bits(h1) << 16);
-        lo[j] = f32_to_bf16_bits(p0 - h0) | (f32_to_bf16_bits(p1 - h1) << 16);
+        // two-term split by truncation: hi = the upper 16 bits of p, lo = the upper 16 bits of the
+        // (exact) remainder; p - hi - lo < 2^-16 p, and no conversion instruction is needed
+        const uint32_t b0 = __float_as_uint(p0), b1 = __float_as_uint(p1);
+        hi[j] = __byte_perm(b0, b1, 0x7632);
+        const uint32_t l0 = __float_as_uint(p0 - __uint_as_float(b0 & 0xFFFF0000u)), l1 = __float_as_uint(p1 - __uint_as_float(b1 & 0xFFFF0000u));
+        lo[j] = __byte_perm(l0, l1, 0x7632);
       }
       tc_st16(tPhi + lane_base + (uint32_t)(c * 16), hi);
       tc_st16(tPlo + lane_base + (uint32_t)(c * 16), lo);
@@ -276,9 +296,6 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(const __grid_const
         tc_commit(smem_u32(&bar_o));
       }
     }
-    // meanwhile: scale the running output by the change of maximum
-#pragma unroll
-    for (int i = 0; i < D; i++) o[i] *= corr;
     __syncthreads();
     if (*(volatile int*)&abort_flag) { ok = false; break; }
     if (!mbar_wait(smem_u32(&bar_o), ph)) { if (threadIdx.x == 0) set_status(a.status, 10); ok = false; break; }
@@ -295,7 +312,7 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(const __grid_const
       tc_ld32(tS + lane_base + (uint32_t)(c * 32), r);
       tc_wait_ld();
 #pragma unroll
-      for (int j = 0; j < 32; j++) o[c * 32 + j] += __uint_as_float(r[j]);
+      for (int j = 0; j < 32; j++) o[c * 32 + j] = fmaf(o[c * 32 + j], corr, __uint_as_float(r[j]));  // scale by the change of maximum, add
     }
     tc_fence_before();
     __syncthreads();  // O_tile has been read by everyone: the next S may overwrite it
