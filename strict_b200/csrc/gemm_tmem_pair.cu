@@ -34,7 +34,7 @@ constexpr int BN = 128;       // channels per block (half of the pair's UMMA_M =
 constexpr int BTH = 128;      // operand rows per block (half of the pair's UMMA_N = 256)
 constexpr int BK = 128;       // bytes of K per stage = one 128-byte swizzle atom
 constexpr int UMMA_K = 32;    // bytes (= E4M3 elements) of K per tcgen05.mma
-constexpr int STAGES = 6;
+constexpr int STAGES = 7;
 constexpr int STAGE_BYTES = BN * BK + BTH * BK;  // 32 KB per block
 constexpr int ACC_COLS = 256, TMEM_COLS = 512;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;  // try_wait attempts before giving up (each blocks up to ~1 us)
