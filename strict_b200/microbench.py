@@ -1,7 +1,7 @@
 """Kernel microbenchmarks at the shapes of BASELINE.json configs[1] (GEMM/GEMV) and configs[2]
 (GQA attention), through the C ABI, timed with CUDA events on the library's stream.
 
-    python -m strict_b200.microbench [gemm] [attn] [--iters N]
+    python -m strict_b200.microbench [gemm] [attn] [--iters N] [--shape M,N,K]
 
 Every timed call reads buffers that were not touched by the previous call (weights rotate
 through enough distinct copies to exceed the 126 MB L2; the attention caches are GBs), so the
@@ -30,15 +30,15 @@ def _peaks():
     return 6650.0, 1590.0, "fallback"
 
 
-def gemm_cases(ctx, iters):
+def gemm_cases(ctx, iters, shape=None):
     hbm, bf16_tf, kind = _peaks()
-    for N_, K in ((4096, 4096), (14336, 4096)):
+    for N_, K in ((4096, 4096), (14336, 4096)) if shape is None else ((shape[1], shape[2]),):
         copies = max(2, int(np.ceil(300e6 / (N_ * K))))  # > 2x L2 of distinct weights
         wq = [DV(ctx, N_ * K, np.uint8) for _ in range(copies)]
         sw = DV(ctx, N_)
         for i, w in enumerate(wq):
             N.check(L().strictb200_gen_weight_e4m3(ctx.h, 2, 10 + i, 0, N_, K, 0, K, 0.02, w.p, sw.p))
-        for M in (1, 8, 32, 128, 2048):
+        for M in (1, 8, 32, 128, 2048) if shape is None else (shape[0],):
             x = DV(ctx, M * K, np.uint16)
             N.check(L().strictb200_gen_normal_bf16(ctx.h, 2, 99, 0, M * K, 1.0, x.p))
             y = DV(ctx, M * N_, np.uint16)
@@ -123,10 +123,11 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="*", default=["gemm", "attn"])
     ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--shape", default=None, help="M,N,K: run the GEMM case for this one shape only")
     args = ap.parse_args()
     ctx = Context(0)
     if "gemm" in args.what:
-        gemm_cases(ctx, args.iters)
+        gemm_cases(ctx, args.iters, tuple(int(v) for v in args.shape.split(",")) if args.shape else None)
     if "attn" in args.what:
         attn_cases(ctx, args.iters)
     ctx.dispose()
