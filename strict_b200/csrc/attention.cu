@@ -573,7 +573,8 @@ int k_attn_prefill(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf1
                    const int32_t* qstart, int B, int S, int64_t q_rows, int Hq, int Hkv, int Dh, int maxlen, float scale, bf16* out) {
   if (Dh != D) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: head_dim must be 128");
   // tcgen05 kernel first; the mma.sync kernel below takes what it declines
-  static const int use_tc = getenv("STRICTB200_ATTN_TC") ? atoi(getenv("STRICTB200_ATTN_TC")) : 1;
+  const char* tc_env = getenv("STRICTB200_ATTN_TC");  // read per call: the tests switch between the two kernels
+  const int use_tc = tc_env ? atoi(tc_env) : 1;
   if (use_tc) {
     int st = k_attn_prefill_tc(ctx, q, kc, vc, lens, past, qstart, B, S, q_rows, Hq, Hkv, maxlen, scale, out);
     if (st != STRICTB200_ERR_UNSUPPORTED) return st;

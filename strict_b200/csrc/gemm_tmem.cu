@@ -425,7 +425,8 @@ int k_gemm_fp8_tmem(strictb200_ctx* ctx, const GemmArgs& g) {
   if (((uintptr_t)g.xq | (uintptr_t)g.wq | (uintptr_t)g.ldx | (uintptr_t)g.ldw) & 15)
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: operands and row strides must be 16-byte aligned");
   // many tokens: two SMs per 256 x 256 tile (half the operand bytes per flop through each SM)
-  static const int pair = getenv("STRICTB200_GEMM_PAIR") ? atoi(getenv("STRICTB200_GEMM_PAIR")) : 1;
+  const char* pair_env = getenv("STRICTB200_GEMM_PAIR");  // read per call: the tests switch between the two kernels
+  const int pair = pair_env ? atoi(pair_env) : 1;
   if (pair && g.N >= 256 && ctx->sm_count >= 2) return k_gemm_fp8_tmem_pair(ctx, g);
   SB_TRY(get_encode());
   static const int prefetch = getenv("STRICTB200_PREFETCH") ? atoi(getenv("STRICTB200_PREFETCH")) : 1;

@@ -175,6 +175,14 @@ def test_gemm_tiles_vs_oracle(ctx, oracle, rng, M, N_, K, kernel):
     assert np.allclose(got, want, rtol=2e-5, atol=1e-5 * np.abs(want).max())
 
 
+@pytest.mark.parametrize("M,N_,K", [(300, 1008, 1536), (2048, 4096, 4096)])
+def test_gemm_one_sm_persistent_kernel_vs_oracle(ctx, oracle, rng, M, N_, K, monkeypatch):
+    """The one-SM persistent tcgen05 kernel (the fallback of the paired kernel) stays correct."""
+    monkeypatch.setenv("STRICTB200_GEMM_PAIR", "0")
+    got, want = _gemm_case(ctx, oracle, rng, M, N_, K, kernel=3, out_dtype=1)
+    assert np.allclose(got, want, rtol=2e-5, atol=1e-5 * np.abs(want).max())
+
+
 def test_gemm_kernels_agree_and_linearity(ctx, oracle, rng):
     """Size-independent properties at a benchmark shape: the three kernels agree, and the GEMM
     is linear in the activation scale."""
@@ -342,8 +350,11 @@ def _attn_tol(got, want):
     return err.max() <= 2e-2 and err.mean() / np.abs(want).mean() <= 5e-3
 
 
-@pytest.mark.parametrize("B,S,Hq,Hkv,lens", [(1, 1, 4, 2, [1]), (2, 65, 4, 1, [65, 3]), (2, 200, 8, 2, [200, 129]), (1, 64, 2, 2, [64])])
-def test_attn_prefill_vs_oracle(ctx, oracle, rng, B, S, Hq, Hkv, lens):
+@pytest.mark.parametrize("B,S,Hq,Hkv,lens", [(1, 1, 4, 2, [1]), (2, 65, 4, 1, [65, 3]), (2, 200, 8, 2, [200, 129]), (1, 64, 2, 2, [64]),
+                                             (2, 256, 4, 2, [256, 130]), (1, 250, 8, 8, [250])])
+@pytest.mark.parametrize("tensor_memory_kernel", ["1", "0"])
+def test_attn_prefill_vs_oracle(ctx, oracle, rng, B, S, Hq, Hkv, lens, tensor_memory_kernel, monkeypatch):
+    monkeypatch.setenv("STRICTB200_ATTN_TC", tensor_memory_kernel)  # tcgen05 kernel / mma.sync kernel
     D, maxlen = 128, 256
     q = oracle.round_bf16(rng.standard_normal((B, S, Hq, D)).astype(np.float32))
     k = oracle.round_bf16(rng.standard_normal((B, S, Hkv, D)).astype(np.float32))
