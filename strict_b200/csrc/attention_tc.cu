@@ -10,12 +10,16 @@
 //                    terms (hi + lo by truncation, so that P.V matches an exact-softmax oracle
 //                    to 2^-16)
 //                    back to tensor memory with tcgen05.st (2 x 64 columns)
-//   O_tile = P V     tcgen05.mma with A = P from tensor memory and B = the V tile in shared
-//                    memory, read MN-major (its rows are keys = the K dimension of this product);
-//                    the result reuses the columns of S
-//   O += O_tile      in registers (128 fp32 per thread), after scaling by the change of maximum
+//   O += P V        tcgen05.mma with A = P from tensor memory and B = the V tile in shared
+//                    memory, read MN-major (its rows are keys = the K dimension of this product),
+//                    accumulating into the running output, which stays in tensor memory (128
+//                    columns) for the whole block. P overwrites S in place (32 fp32 columns of a
+//                    chunk become 16 columns of P hi and 16 of P lo), so a block needs 256 columns.
+//   rescaling        the running output follows the running maximum lazily: a row is rescaled
+//                    (read-modify-write of its 128 columns) only when its maximum grew by more
+//                    than 2^8; otherwise it keeps the older reference maximum
 // The K tile of the next step is requested as soon as S is complete, the V tile as soon as
-// O_tile is complete, so the copies run under the softmax and the accumulation. Two blocks fit
+// the previous P.V is complete, so the copies run under the softmax. Two blocks fit
 // an SM (96 KB of shared memory, 256 tensor-memory columns each) and fill each other's gaps.
 // Every mbarrier wait is bounded: on expiry the block records an error word in host-visible
 // memory, stops, frees its tensor memory and returns.
@@ -107,6 +111,15 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
       "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]),
+      "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -175,7 +188,7 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(const __grid_const
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
   const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-  const uint32_t tS = tmem, tPhi = tmem + 128, tPlo = tmem + 192;  // columns: S / O_tile, P hi, P lo
+  const uint32_t tS = tmem, tO = tmem + 128;  // columns: S (then P hi/lo in place) and the running output
 
   if (threadIdx.x == 0) {
     mbar_expect_tx(smem_u32(&bar_q), TILE_BYTES);
@@ -193,18 +206,26 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(const __grid_const
   constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   constexpr uint32_t idesc_pv = idesc_s | (1u << 16);
 
-  float o[D];
-#pragma unroll
-  for (int i = 0; i < D; i++) o[i] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
   const int qpos = pst + q0 + (int)threadIdx.x;  // position of this thread's query row
   bool ok = true;
 
   for (int t = 0; t < ntiles; t++) {
     const uint32_t ph = (uint32_t)(t & 1);
-    // ---- S = Q K^T
+    // ---- S = Q K^T (after the previous P.V has finished reading P and the V tile)
     if (threadIdx.x == 0) {
-      bool good = (t > 0 || mbar_wait(smem_u32(&bar_q), 0)) && mbar_wait(smem_u32(&bar_k), ph);
+      bool good = true;
+      if (t > 0) {
+        good = mbar_wait(smem_u32(&bar_o), ph ^ 1);
+        if (good) {
+          mbar_expect_tx(smem_u32(&bar_v), TILE_BYTES);
+          tma_load_2d(sV, &map_v, 0, kv_row0 + t * BKV, smem_u32(&bar_v));
+          tma_load_2d(sV + HALF_BYTES, &map_v, 64, kv_row0 + t * BKV, smem_u32(&bar_v));
+        }
+      } else {
+        good = mbar_wait(smem_u32(&bar_q), 0);
+      }
+      good = good && mbar_wait(smem_u32(&bar_k), ph);
       if (!good) { set_status(a.status, 7); abort_flag = 1; }
       else {
         tc_fence_after();
@@ -246,10 +267,25 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(const __grid_const
       }
     }
     m_tile *= a.scale_log2;  // the scale is positive: the maximum commutes with it
-    const float m_new = fmaxf(m_run, m_tile);
-    const float m_use = m_new == -INFINITY ? 0.f : m_new;
-    const float corr = exp2f(m_run - m_use);
-    m_run = m_new;
+    // The running output lives in tensor memory, so following the maximum costs a read-modify-write
+    // of the row. It is only done when the maximum grew by more than 2^8 (the exponentials then
+    // stay below 256, harmless for the two-term bf16 P and the fp32 sums); otherwise the row keeps
+    // its older reference maximum, and the final division by the running sum is unchanged.
+    const bool grow = m_tile > m_run + 8.0f;  // also true for the first tile (m_run = -inf)
+    const float m_use = grow ? m_tile : m_run;
+    const float corr = grow ? exp2f(m_run - m_use) : 1.0f;  // 0 for the first tile
+    m_run = m_use;
+    if (t > 0 && __any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+      for (int c = 0; c < 4; c++) {
+        uint32_t r[32];
+        tc_ld32(tO + lane_base + (uint32_t)(c * 32), r);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
+        tc_st32(tO + lane_base + (uint32_t)(c * 32), r);
+      }
+    }
     float row_sum = 0.f;
 #pragma unroll 1
     for (int c = 0; c < 4; c++) {
@@ -274,61 +310,56 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(const __grid_const
         const uint32_t l0 = __float_as_uint(p0 - __uint_as_float(b0 & 0xFFFF0000u)), l1 = __float_as_uint(p1 - __uint_as_float(b1 & 0xFFFF0000u));
         lo[j] = __byte_perm(l0, l1, 0x7632);
       }
-      tc_st16(tPhi + lane_base + (uint32_t)(c * 16), hi);
-      tc_st16(tPlo + lane_base + (uint32_t)(c * 16), lo);
+      // in place: the 32 fp32 columns of this chunk become 16 columns of P hi and 16 of P lo
+      tc_st16(tS + lane_base + (uint32_t)(c * 32), hi);
+      tc_st16(tS + lane_base + (uint32_t)(c * 32 + 16), lo);
     }
     tc_wait_st();
     l_run = l_run * corr + row_sum;
     tc_fence_before();
-    __syncthreads();  // P of all rows is in tensor memory; S has been read by everyone
-    // ---- O_tile = P V (into the columns of S)
+    __syncthreads();  // P of all rows is in tensor memory (and the rescaled O, if any)
+    // ---- O += P V
     if (threadIdx.x == 0) {
       if (!mbar_wait(smem_u32(&bar_v), ph)) { set_status(a.status, 9); abort_flag = 1; }
       else {
         tc_fence_after();
 #pragma unroll
         for (int s = 0; s < 8; s++) {
-          // 16 keys = 16 rows of 128 bytes = 2048 bytes of the V tile; 16 keys = 8 packed columns of P
+          // 16 keys = 16 rows of 128 bytes = 2048 bytes of the V tile = 8 packed columns of P hi (and of P lo)
           const uint64_t dv = desc_mnmajor(sV + (uint32_t)(s * 2048));
-          tc_mma_ts(tS, tPhi + (uint32_t)(s * 8), dv, idesc_pv, s ? 1u : 0u);
-          tc_mma_ts(tS, tPlo + (uint32_t)(s * 8), dv, idesc_pv, 1u);
+          const uint32_t pcol = (uint32_t)((s >> 1) * 32 + (s & 1) * 8);
+          tc_mma_ts(tO, tS + pcol, dv, idesc_pv, (t | s) ? 1u : 0u);
+          tc_mma_ts(tO, tS + pcol + 16, dv, idesc_pv, 1u);
         }
         tc_commit(smem_u32(&bar_o));
       }
     }
-    __syncthreads();
-    if (*(volatile int*)&abort_flag) { ok = false; break; }
-    if (!mbar_wait(smem_u32(&bar_o), ph)) { if (threadIdx.x == 0) set_status(a.status, 10); ok = false; break; }
-    tc_fence_after();
-    // the V tile is free: request the next one
-    if (threadIdx.x == 0 && t + 1 < ntiles) {
-      mbar_expect_tx(smem_u32(&bar_v), TILE_BYTES);
-      tma_load_2d(sV, &map_v, 0, kv_row0 + (t + 1) * BKV, smem_u32(&bar_v));
-      tma_load_2d(sV + HALF_BYTES, &map_v, 64, kv_row0 + (t + 1) * BKV, smem_u32(&bar_v));
-    }
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-      uint32_t r[32];
-      tc_ld32(tS + lane_base + (uint32_t)(c * 32), r);
-      tc_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 32; j++) o[c * 32 + j] = fmaf(o[c * 32 + j], corr, __uint_as_float(r[j]));  // scale by the change of maximum, add
-    }
-    tc_fence_before();
-    __syncthreads();  // O_tile has been read by everyone: the next S may overwrite it
   }
 
-  if (ok && q0 + (int)threadIdx.x < n_new) {
+  __syncthreads();
+  if (*(volatile int*)&abort_flag) ok = false;
+  if (ok && !mbar_wait(smem_u32(&bar_o), (uint32_t)((ntiles - 1) & 1))) { if (threadIdx.x == 0) set_status(a.status, 10); ok = false; }
+  tc_fence_after();
+  if (ok) {
+    const bool live = q0 + (int)threadIdx.x < n_new;
     const float inv = 1.0f / l_run;
     bf16* dst = a.out + ((row0 + q0 + threadIdx.x) * a.Hq + h) * D;
+#pragma unroll 1
+    for (int c = 0; c < 4; c++) {
+      uint32_t r[32];
+      tc_ld32(tO + lane_base + (uint32_t)(c * 32), r);
+      tc_wait_ld();
+      if (live) {
 #pragma unroll
-    for (int i = 0; i < D; i += 8) {
-      uint4 w;
-      w.x = f32_to_bf16_bits(o[i] * inv) | (f32_to_bf16_bits(o[i + 1] * inv) << 16);
-      w.y = f32_to_bf16_bits(o[i + 2] * inv) | (f32_to_bf16_bits(o[i + 3] * inv) << 16);
-      w.z = f32_to_bf16_bits(o[i + 4] * inv) | (f32_to_bf16_bits(o[i + 5] * inv) << 16);
-      w.w = f32_to_bf16_bits(o[i + 6] * inv) | (f32_to_bf16_bits(o[i + 7] * inv) << 16);
-      *(uint4*)(dst + i) = w;
+        for (int i = 0; i < 32; i += 8) {
+          uint4 w;
+          w.x = f32_to_bf16_bits(__uint_as_float(r[i]) * inv) | (f32_to_bf16_bits(__uint_as_float(r[i + 1]) * inv) << 16);
+          w.y = f32_to_bf16_bits(__uint_as_float(r[i + 2]) * inv) | (f32_to_bf16_bits(__uint_as_float(r[i + 3]) * inv) << 16);
+          w.z = f32_to_bf16_bits(__uint_as_float(r[i + 4]) * inv) | (f32_to_bf16_bits(__uint_as_float(r[i + 5]) * inv) << 16);
+          w.w = f32_to_bf16_bits(__uint_as_float(r[i + 6]) * inv) | (f32_to_bf16_bits(__uint_as_float(r[i + 7]) * inv) << 16);
+          *(uint4*)(dst + c * 32 + i) = w;
+        }
+      }
     }
   }
   tc_fence_before();
