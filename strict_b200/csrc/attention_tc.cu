@@ -1,7 +1,6 @@
 // Causal GQA prefill attention on the tcgen05 tensor cores (head_dim 128, bf16).
-// One block = 128 query positions of one head, 256 threads: query row r is lane r of tensor memory
-// and is served by threads r and 128 + r, each owning 64 of the 128 columns of every step; they
-// only exchange the row maximum (through shared memory), so the softmax needs no shuffles.
+// One block = 128 query positions of one head, 128 threads: thread r owns query row r, which is
+// also lane r of tensor memory, so the softmax needs no shuffles.
 // Per 128-key tile:
 //   S = Q K^T        tcgen05.mma kind::f16, A = Q tile and B = K tile in shared memory (both
 //                    K-major, two 64-dim halves of 128-byte-swizzled rows written by TMA),
@@ -151,14 +150,13 @@ struct TcAttnArgs {
   int* status;
 };
 
-__global__ void __launch_bounds__(256) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+__global__ void __launch_bounds__(128) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                                               const __grid_constant__ CUtensorMap map_v, TcAttnArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t bar_q, bar_k, bar_v, bar_s, bar_o;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float x_max[2][BQ], x_sum[BQ];  // exchange between the two threads of a row
 
   const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * BQ;
   const int len = a.lens[b], pst = a.past ? a.past[b] : 0;
@@ -167,7 +165,6 @@ __global__ void __launch_bounds__(256) attn_prefill_tc_kernel(const __grid_const
   const int64_t row0 = a.qstart ? a.qstart[b] : (int64_t)b * a.S;
   const int hk = h / (a.Hq / a.Hkv);
   const int warp = threadIdx.x >> 5;
-  const int half = threadIdx.x >> 7, row = threadIdx.x & (BQ - 1);  // two threads per query row: each owns 64 of the 128 columns
   const int kv_end = min(len, pst + q0 + BQ);  // last key any row of this block may see, exclusive
   const int ntiles = (kv_end + BKV - 1) / BKV;
   const int kv_row0 = (b * a.Hkv + hk) * a.maxlen;
@@ -190,7 +187,7 @@ __global__ void __launch_bounds__(256) attn_prefill_tc_kernel(const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // a warp reaches the lanes of its quarter
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
   const uint32_t tS = tmem, tO = tmem + 128;  // columns: S (then P hi/lo in place) and the running output
 
   if (threadIdx.x == 0) {
@@ -210,7 +207,7 @@ __global__ void __launch_bounds__(256) attn_prefill_tc_kernel(const __grid_const
   constexpr uint32_t idesc_pv = idesc_s | (1u << 16);
 
   float m_run = -INFINITY, l_run = 0.f;
-  const int qpos = pst + q0 + row;  // position of this thread's query row
+  const int qpos = pst + q0 + (int)threadIdx.x;  // position of this thread's query row
   bool ok = true;
 
   for (int t = 0; t < ntiles; t++) {
@@ -256,7 +253,7 @@ __global__ void __launch_bounds__(256) attn_prefill_tc_kernel(const __grid_const
     const bool full = k0 + BKV <= min(len, pst + q0 + 1);  // every row of the block sees the whole tile (block-uniform)
     float m_tile = -INFINITY;
 #pragma unroll 1
-    for (int c = 2 * half; c < 2 * half + 2; c++) {
+    for (int c = 0; c < 4; c++) {
       uint32_t r[32];
       tc_ld32(tS + lane_base + (uint32_t)(c * 32), r);
       tc_wait_ld();
@@ -269,9 +266,7 @@ __global__ void __launch_bounds__(256) attn_prefill_tc_kernel(const __grid_const
           if (c * 32 + j < k_lim) m_tile = fmaxf(m_tile, __uint_as_float(r[j]));
       }
     }
-    x_max[half][row] = m_tile;
-    __syncthreads();
-    m_tile = fmaxf(x_max[0][row], x_max[1][row]) * a.scale_log2;  // the scale is positive: the maximum commutes with it
+    m_tile *= a.scale_log2;  // the scale is positive: the maximum commutes with it
     // The running output lives in tensor memory, so following the maximum costs a read-modify-write
     // of the row. It is only done when the maximum grew by more than 2^8 (the exponentials then
     // stay below 256, harmless for the two-term bf16 P and the fp32 sums); otherwise the row keeps
@@ -282,7 +277,7 @@ __global__ void __launch_bounds__(256) attn_prefill_tc_kernel(const __grid_const
     m_run = m_use;
     if (t > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-      for (int c = 2 * half; c < 2 * half + 2; c++) {
+      for (int c = 0; c < 4; c++) {
         uint32_t r[32];
         tc_ld32(tO + lane_base + (uint32_t)(c * 32), r);
         tc_wait_ld();
@@ -293,7 +288,7 @@ __global__ void __launch_bounds__(256) attn_prefill_tc_kernel(const __grid_const
     }
     float row_sum = 0.f;
 #pragma unroll 1
-    for (int c = 2 * half; c < 2 * half + 2; c++) {
+    for (int c = 0; c < 4; c++) {
       uint32_t r[32];
       tc_ld32(tS + lane_base + (uint32_t)(c * 32), r);
       tc_wait_ld();
@@ -345,16 +340,12 @@ __global__ void __launch_bounds__(256) attn_prefill_tc_kernel(const __grid_const
   if (*(volatile int*)&abort_flag) ok = false;
   if (ok && !mbar_wait(smem_u32(&bar_o), (uint32_t)((ntiles - 1) & 1))) { if (threadIdx.x == 0) set_status(a.status, 10); ok = false; }
   tc_fence_after();
-  if (half) x_sum[row] = l_run;  // the two threads of a row saw the same maxima: their sums add
-  __syncthreads();
-  if (!half) x_sum[row] += l_run;
-  __syncthreads();
   if (ok) {
-    const bool live = q0 + row < n_new;
-    const float inv = 1.0f / x_sum[row];
-    bf16* dst = a.out + ((row0 + q0 + row) * a.Hq + h) * D;
+    const bool live = q0 + (int)threadIdx.x < n_new;
+    const float inv = 1.0f / l_run;
+    bf16* dst = a.out + ((row0 + q0 + threadIdx.x) * a.Hq + h) * D;
 #pragma unroll 1
-    for (int c = 2 * half; c < 2 * half + 2; c++) {
+    for (int c = 0; c < 4; c++) {
       uint32_t r[32];
       tc_ld32(tO + lane_base + (uint32_t)(c * 32), r);
       tc_wait_ld();
@@ -426,7 +417,7 @@ int k_attn_prefill_tc(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const 
   }
   TcAttnArgs a{lens, past, qstart, S, Hq, Hkv, maxlen, scale * LOG2E, out, ctx->d_status};
   dim3 grid((unsigned)((S + BQ - 1) / BQ), (unsigned)Hq, (unsigned)B);
-  attn_prefill_tc_kernel<<<grid, 256, smem, ctx->stream>>>(mq, mk, mv, a);
+  attn_prefill_tc_kernel<<<grid, 128, smem, ctx->stream>>>(mq, mk, mv, a);
   SB_LAUNCHED(ctx);
   return STRICTB200_OK;
 }
