@@ -370,6 +370,267 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(const __grid_const
   }
 }
 
+// ------------------------------------------------------------------ two query tiles per block
+// The kernel above runs S -> softmax -> PV of a block strictly one after the other, so the tensor
+// pipe idles during the softmax and the softmax threads idle during the MMAs (two blocks per SM
+// hide part of it). Here one block owns TWO tiles of 128 query rows (A and B, 256 consecutive
+// positions of one head) that share every K/V tile, with separate roles:
+//   warps 0..7   softmax of tile A (its own 256 tensor-memory columns: S/P and O); row r = lane r is
+//                served by two threads (warps 0..3 and 4..7) that own 64 of the 128 columns each
+//                and exchange only the row maximum, so two warps per scheduler hide each
+//                other's tensor-memory and exp2 latencies
+//   warps 8..15  softmax of tile B (the other 256 columns), same split
+//   warp 16      one lane issues all MMAs in ping-pong order (PV_A(t) S_A(t+1) PV_B(t) S_B(t+1)):
+//                while the A threads run their softmax the tensor pipe works on tile B, and so on
+//   warp 17      one lane issues the TMA copies into two-stage K and V rings
+// The whole tensor memory (512 columns) and 193 KB of shared memory: one block per SM.
+constexpr int TC2_THREADS = 576;  // 16 softmax warps + MMA warp + TMA warp
+
+__global__ void __launch_bounds__(TC2_THREADS) attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                                                      const __grid_constant__ CUtensorMap map_v, TcAttnArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t bar_q, k_full[2], k_empty[2], v_full[2], v_empty[2], bar_s[2], bar_p[2], bar_o[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ float x_max[2][2][BQ], x_sum[2][BQ];  // [tile][column half][row]: exchange between the two threads of a row
+
+  const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * 2 * BQ;
+  const int len = a.lens[b], pst = a.past ? a.past[b] : 0;
+  const int n_new = len - pst;
+  if (q0 >= n_new) return;  // whole block, before anything is allocated
+  const int64_t row0 = a.qstart ? a.qstart[b] : (int64_t)b * a.S;
+  const int hk = h / (a.Hq / a.Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_row0 = (b * a.Hkv + hk) * a.maxlen;
+  // K/V tiles each query tile needs (tile B is empty when the sequence ends inside tile A)
+  int nt[2];
+  nt[0] = (min(len, pst + q0 + BQ) + BKV - 1) / BKV;
+  nt[1] = q0 + BQ < n_new ? (min(len, pst + q0 + 2 * BQ) + BKV - 1) / BKV : 0;
+  const int ntiles = max(nt[0], nt[1]);
+
+  const uint32_t sQ = smem_u32(smem), sK = sQ + 2 * TILE_BYTES, sV = sK + 2 * TILE_BYTES;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar_q), 1);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(smem_u32(&k_full[i]), 1); mbar_init(smem_u32(&k_empty[i]), 1);
+      mbar_init(smem_u32(&v_full[i]), 1); mbar_init(smem_u32(&v_empty[i]), 1);
+      mbar_init(smem_u32(&bar_s[i]), 1); mbar_init(smem_u32(&bar_p[i]), 2 * BQ); mbar_init(smem_u32(&bar_o[i]), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 16) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_slot;
+  constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+  constexpr uint32_t idesc_pv = idesc_s | (1u << 16);
+
+  if (warp == 17) {
+    // ---- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(smem_u32(&bar_q), (nt[1] ? 2 : 1) * TILE_BYTES);
+      for (int w = 0; w < (nt[1] ? 2 : 1); w++) {
+        tma_load_2d(sQ + w * TILE_BYTES, &map_q, h * D, (int)(row0 + q0 + w * BQ), smem_u32(&bar_q));
+        tma_load_2d(sQ + w * TILE_BYTES + HALF_BYTES, &map_q, h * D + 64, (int)(row0 + q0 + w * BQ), smem_u32(&bar_q));
+      }
+      for (int t = 0; t < ntiles; t++) {
+        const int st = t & 1;
+        const uint32_t ph = (uint32_t)((t >> 1) & 1);
+        if (t >= 2 && !mbar_wait(smem_u32(&k_empty[st]), ph ^ 1)) { set_status(a.status, 11); break; }
+        mbar_expect_tx(smem_u32(&k_full[st]), TILE_BYTES);
+        tma_load_2d(sK + st * TILE_BYTES, &map_k, 0, kv_row0 + t * BKV, smem_u32(&k_full[st]));
+        tma_load_2d(sK + st * TILE_BYTES + HALF_BYTES, &map_k, 64, kv_row0 + t * BKV, smem_u32(&k_full[st]));
+        if (t >= 2 && !mbar_wait(smem_u32(&v_empty[st]), ph ^ 1)) { set_status(a.status, 12); break; }
+        mbar_expect_tx(smem_u32(&v_full[st]), TILE_BYTES);
+        tma_load_2d(sV + st * TILE_BYTES, &map_v, 0, kv_row0 + t * BKV, smem_u32(&v_full[st]));
+        tma_load_2d(sV + st * TILE_BYTES + HALF_BYTES, &map_v, 64, kv_row0 + t * BKV, smem_u32(&v_full[st]));
+      }
+    }
+  } else if (warp == 16) {
+    // ---- MMA issue, ping-pong between the two query tiles: S_A(0) S_B(0), then per K/V tile
+    // PV_A(t) S_A(t+1) PV_B(t) S_B(t+1). The tensor pipe runs them in program order, so while
+    // the A threads are in the softmax of step t+1 the pipe works on tile B, and vice versa.
+    if (lane == 0) {
+      auto issue_s = [&](int w, int t) {
+        const int st = t & 1;
+        const uint32_t tS = tmem + (uint32_t)(w * 256);
+#pragma unroll
+        for (int s = 0; s < 8; s++) {
+          const uint32_t off = (uint32_t)((s >> 2) * HALF_BYTES + (s & 3) * 32);
+          tc_mma_ss(tS, desc_kmajor(sQ + w * TILE_BYTES + off), desc_kmajor(sK + st * TILE_BYTES + off), idesc_s, s ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&bar_s[w]));
+      };
+      bool good = mbar_wait(smem_u32(&bar_q), 0) && mbar_wait(smem_u32(&k_full[0]), 0);
+      if (good) {
+        tc_fence_after();
+        for (int w = 0; w < 2; w++)
+          if (nt[w] > 0) issue_s(w, 0);
+        tc_commit(smem_u32(&k_empty[0]));
+      }
+      for (int t = 0; t < ntiles && good; t++) {
+        const int st = t & 1;
+        const uint32_t rph = (uint32_t)((t >> 1) & 1), ph = (uint32_t)(t & 1);
+        good = mbar_wait(smem_u32(&v_full[st]), rph);
+        bool k_next_ready = false;
+        for (int w = 0; w < 2 && good; w++) {
+          if (t < nt[w]) {
+            good = mbar_wait(smem_u32(&bar_p[w]), ph);  // P (and the rescaled O) of this step are in tensor memory
+            if (!good) break;
+            tc_fence_after();
+            const uint32_t tS = tmem + (uint32_t)(w * 256), tO = tS + 128;
+#pragma unroll
+            for (int s = 0; s < 8; s++) {
+              const uint64_t dv = desc_mnmajor(sV + st * TILE_BYTES + (uint32_t)(s * 2048));
+              const uint32_t pcol = (uint32_t)((s >> 1) * 32 + (s & 1) * 8);
+              tc_mma_ts(tO, tS + pcol, dv, idesc_pv, (t | s) ? 1u : 0u);
+              tc_mma_ts(tO, tS + pcol + 16, dv, idesc_pv, 1u);
+            }
+            tc_commit(smem_u32(&bar_o[w]));
+          }
+          if (t + 1 < nt[w]) {
+            if (!k_next_ready) {
+              good = mbar_wait(smem_u32(&k_full[(t + 1) & 1]), (uint32_t)(((t + 1) >> 1) & 1));
+              if (!good) break;
+              tc_fence_after();
+              k_next_ready = true;
+            }
+            issue_s(w, t + 1);
+          }
+        }
+        if (!good) break;
+        tc_commit(smem_u32(&v_empty[st]));                               // both PV products have read the V tile
+        if (t + 1 < ntiles) tc_commit(smem_u32(&k_empty[(t + 1) & 1]));  // both S products of the next step have read its K tile
+      }
+      if (!good) set_status(a.status, 13);
+    }
+  } else {
+    // ---- softmax warpgroups: w = 0 (tile A) or 1 (tile B)
+    const int w = warp >> 3, half = (warp >> 2) & 1, row = (int)threadIdx.x & (BQ - 1);
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    auto wg_sync = [&]() { asm volatile("bar.sync %0, 256;" ::"r"(1 + w) : "memory"); };  // the 256 threads of this tile
+    const uint32_t tS = tmem + (uint32_t)(w * 256), tO = tS + 128;
+    const int qw = q0 + w * BQ;           // first query row of this tile
+    const int qpos = pst + qw + row;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int t = 0; t < nt[w]; t++) {
+      const uint32_t ph = (uint32_t)(t & 1);
+      if (!mbar_wait(smem_u32(&bar_s[w]), ph)) { if (row == 0) set_status(a.status, 14); ok = false; break; }
+      tc_fence_after();
+      const int k0 = t * BKV;
+      const int k_lim = min(len, qpos + 1) - k0;
+      const bool full = k0 + BKV <= min(len, pst + qw + 1);
+      float m_tile = -INFINITY;
+#pragma unroll 1
+      for (int c = 2 * half; c < 2 * half + 2; c++) {
+        uint32_t r[32];
+        tc_ld32(tS + lane_base + (uint32_t)(c * 32), r);
+        tc_wait_ld();
+        if (full) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) m_tile = fmaxf(m_tile, __uint_as_float(r[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            if (c * 32 + j < k_lim) m_tile = fmaxf(m_tile, __uint_as_float(r[j]));
+        }
+      }
+      x_max[w][half][row] = m_tile;
+      wg_sync();
+      m_tile = fmaxf(x_max[w][0][row], x_max[w][1][row]) * a.scale_log2;
+      const bool grow = m_tile > m_run + 8.0f;  // lazy rescaling, as in the kernel above
+      const float m_use = grow ? m_tile : m_run;
+      const float corr = grow ? exp2f(m_run - m_use) : 1.0f;
+      m_run = m_use;
+      if (t > 0 && __any_sync(0xffffffffu, grow)) {
+        // the previous PV of this tile must have finished writing O
+        if (!mbar_wait(smem_u32(&bar_o[w]), ph ^ 1)) { if (row == 0) set_status(a.status, 15); ok = false; break; }
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 2 * half; c < 2 * half + 2; c++) {
+          uint32_t r[32];
+          tc_ld32(tO + lane_base + (uint32_t)(c * 32), r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
+          tc_st32(tO + lane_base + (uint32_t)(c * 32), r);
+        }
+      }
+      float row_sum = 0.f;
+#pragma unroll 1
+      for (int c = 2 * half; c < 2 * half + 2; c++) {
+        uint32_t r[32];
+        tc_ld32(tS + lane_base + (uint32_t)(c * 32), r);
+        tc_wait_ld();
+        uint32_t hi[16], lo[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          const int kk = c * 32 + 2 * j;
+          float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * j]), a.scale_log2, -m_use));
+          float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * j + 1]), a.scale_log2, -m_use));
+          if (!full) {
+            if (kk >= k_lim) p0 = 0.f;
+            if (kk + 1 >= k_lim) p1 = 0.f;
+          }
+          row_sum += p0 + p1;
+          const uint32_t b0 = __float_as_uint(p0), b1 = __float_as_uint(p1);
+          hi[j] = __byte_perm(b0, b1, 0x7632);
+          const uint32_t l0 = __float_as_uint(p0 - __uint_as_float(b0 & 0xFFFF0000u)), l1 = __float_as_uint(p1 - __uint_as_float(b1 & 0xFFFF0000u));
+          lo[j] = __byte_perm(l0, l1, 0x7632);
+        }
+        tc_st16(tS + lane_base + (uint32_t)(c * 32), hi);
+        tc_st16(tS + lane_base + (uint32_t)(c * 32 + 16), lo);
+      }
+      tc_wait_st();
+      l_run = l_run * corr + row_sum;
+      tc_fence_before();
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_p[w])) : "memory");
+      wg_sync();  // x_max is rewritten in the next step
+    }
+    if (ok && nt[w] > 0) {
+      if (!mbar_wait(smem_u32(&bar_o[w]), (uint32_t)((nt[w] - 1) & 1))) { if (row == 0) set_status(a.status, 16); ok = false; }
+      tc_fence_after();
+    }
+    if (half) x_sum[w][row] = l_run;  // the two threads of a row saw the same maxima: their sums add
+    wg_sync();
+    if (!half) x_sum[w][row] += l_run;
+    wg_sync();
+    if (ok && nt[w] > 0) {
+      const bool live = qw + row < n_new;
+      const float inv = 1.0f / x_sum[w][row];
+      bf16* dst = a.out + ((row0 + qw + row) * a.Hq + h) * D;
+#pragma unroll 1
+      for (int c = 2 * half; c < 2 * half + 2; c++) {
+        uint32_t r[32];
+        tc_ld32(tO + lane_base + (uint32_t)(c * 32), r);
+        tc_wait_ld();
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 wv;
+            wv.x = f32_to_bf16_bits(__uint_as_float(r[i]) * inv) | (f32_to_bf16_bits(__uint_as_float(r[i + 1]) * inv) << 16);
+            wv.y = f32_to_bf16_bits(__uint_as_float(r[i + 2]) * inv) | (f32_to_bf16_bits(__uint_as_float(r[i + 3]) * inv) << 16);
+            wv.z = f32_to_bf16_bits(__uint_as_float(r[i + 4]) * inv) | (f32_to_bf16_bits(__uint_as_float(r[i + 5]) * inv) << 16);
+            wv.w = f32_to_bf16_bits(__uint_as_float(r[i + 6]) * inv) | (f32_to_bf16_bits(__uint_as_float(r[i + 7]) * inv) << 16);
+            *(uint4*)(dst + c * 32 + i) = wv;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 16) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeFn g_encode = nullptr;
@@ -416,6 +677,21 @@ int k_attn_prefill_tc(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const 
     attr = true;
   }
   TcAttnArgs a{lens, past, qstart, S, Hq, Hkv, maxlen, scale * LOG2E, out, ctx->d_status};
+  // two query tiles per block (ping-pong) from 256 new tokens per sequence on; STRICTB200_ATTN_TC=1 / 2 forces a kernel
+  const char* mode = getenv("STRICTB200_ATTN_TC");
+  const int forced = mode ? atoi(mode) : 0;
+  if (forced == 2 || (forced != 1 && S >= 2 * BQ)) {
+    const size_t smem2 = 6 * TILE_BYTES + 1024;
+    static bool attr2 = false;
+    if (!attr2) {
+      SB_CUDA(cudaFuncSetAttribute(attn_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+      attr2 = true;
+    }
+    dim3 grid2((unsigned)((S + 2 * BQ - 1) / (2 * BQ)), (unsigned)Hq, (unsigned)B);
+    attn_prefill_tc2_kernel<<<grid2, TC2_THREADS, smem2, ctx->stream>>>(mq, mk, mv, a);
+    SB_LAUNCHED(ctx);
+    return STRICTB200_OK;
+  }
   dim3 grid((unsigned)((S + BQ - 1) / BQ), (unsigned)Hq, (unsigned)B);
   attn_prefill_tc_kernel<<<grid, 128, smem, ctx->stream>>>(mq, mk, mv, a);
   SB_LAUNCHED(ctx);

@@ -559,7 +559,7 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   int threads = (int)((d / 8 + 31) / 32 * 32);
   threads = threads < 128 ? 128 : (threads > 512 ? 512 : threads);
   // many rows (prefill): narrower blocks, two chunks per thread and more blocks per SM keep more bytes in flight
-  if (M > 1024 && threads > 256 && !getenv("SB_ROWNORM_512")) threads = 256;
+  if (M > 1024 && threads > 256) threads = 256;
   while ((int64_t)threads * 8 * MAX_CHUNKS < d) threads += 32;
   RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale};
   // decode-step shapes: 4 columns per thread, at most 8 partials, no bf16 residual

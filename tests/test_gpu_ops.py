@@ -352,9 +352,9 @@ def _attn_tol(got, want):
 
 @pytest.mark.parametrize("B,S,Hq,Hkv,lens", [(1, 1, 4, 2, [1]), (2, 65, 4, 1, [65, 3]), (2, 200, 8, 2, [200, 129]), (1, 64, 2, 2, [64]),
                                              (2, 256, 4, 2, [256, 130]), (1, 250, 8, 8, [250])])
-@pytest.mark.parametrize("tensor_memory_kernel", ["1", "0"])
+@pytest.mark.parametrize("tensor_memory_kernel", ["1", "0", "2"])
 def test_attn_prefill_vs_oracle(ctx, oracle, rng, B, S, Hq, Hkv, lens, tensor_memory_kernel, monkeypatch):
-    monkeypatch.setenv("STRICTB200_ATTN_TC", tensor_memory_kernel)  # tcgen05 kernel / mma.sync kernel
+    monkeypatch.setenv("STRICTB200_ATTN_TC", tensor_memory_kernel)  # tcgen05 one tile per block / mma.sync / tcgen05 two tiles per block
     D, maxlen = 128, 256
     q = oracle.round_bf16(rng.standard_normal((B, S, Hq, D)).astype(np.float32))
     k = oracle.round_bf16(rng.standard_normal((B, S, Hkv, D)).astype(np.float32))
