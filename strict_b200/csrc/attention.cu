@@ -504,6 +504,8 @@ __global__ void __launch_bounds__(1024) attn_combine_decode_kernel(const float* 
 __global__ void kv_append_f32_kernel(const float* __restrict__ qkv, float* __restrict__ kc, float* __restrict__ vc,
                                      const int32_t* __restrict__ seq, const int32_t* __restrict__ pos, const int32_t* __restrict__ lens, int H,
                                      int Dh, int maxlen) {
+  pdl_trigger();
+  pdl_wait();
   int64_t t = blockIdx.x;
   int b = seq ? seq[t] : (int)t;
   int p = pos ? pos[t] : lens[b];
@@ -521,6 +523,8 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(const float* __restrict__
                                                        const int32_t* __restrict__ seq, const int32_t* __restrict__ pos,
                                                        const int32_t* __restrict__ lens, int H, int Dh, int maxlen, float scale,
                                                        float* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float sc[];  // [maxlen] scores, then [Dh] query
   __shared__ float red[32];
   int h = blockIdx.x;
@@ -670,12 +674,12 @@ int k_attn_f32(strictb200_ctx* ctx, const float* qkv, float* kc, float* vc, cons
     SB_CUDA(cudaFuncSetAttribute(attn_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_smem = smem;
   }
-  kv_append_f32_kernel<<<(unsigned)T, 256, 0, ctx->stream>>>(qkv, kc, vc, seq, pos, lens, H, Dh, maxlen);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, kv_append_f32_kernel, dim3((unsigned)T), dim3(256), 0, qkv, kc, vc, seq, pos, lens, H, Dh, maxlen));
+  ctx->launches++;
   if (T > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: too many rows for the fp32 path");
   dim3 grid(H, (unsigned)T);
-  attn_f32_kernel<<<grid, 128, smem, ctx->stream>>>(qkv, kc, vc, seq, pos, lens, H, Dh, maxlen, scale, out);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, attn_f32_kernel, grid, dim3(128), smem, (const float*)qkv, (const float*)kc, (const float*)vc, seq, pos, lens, H, Dh, maxlen, scale, out));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 

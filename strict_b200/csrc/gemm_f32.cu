@@ -6,19 +6,29 @@
 namespace {
 constexpr int F32_MT = 8;
 
+constexpr int F32_PRE = 8;  // float4 of its weight row a lane fetches before the dependency wait (covers K <= 1024)
+
 __global__ void __launch_bounds__(256) gemm_f32_kernel(int M, int N, int K, const float* __restrict__ x, const float* __restrict__ w,
                                                        const float* __restrict__ bias, float* __restrict__ y, int accumulate) {
+  pdl_trigger();
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int n = blockIdx.x * 8 + warp;
   int m0 = blockIdx.y * F32_MT;
   if (n >= N) return;
+  const float4* wr = (const float4*)(w + (int64_t)n * K);
+  const int nk4 = K / 4;
+  // the weights are constants: the head of the row streams in while the previous kernel still runs
+  float4 wpre[F32_PRE];
+#pragma unroll
+  for (int i = 0; i < F32_PRE; i++)
+    if (lane + 32 * i < nk4) wpre[i] = __ldg(wr + lane + 32 * i);
+  const float bn = bias ? bias[n] : 0.f;
+  pdl_wait();
   float acc[F32_MT];
 #pragma unroll
   for (int i = 0; i < F32_MT; i++) acc[i] = 0.f;
-  const float4* wr = (const float4*)(w + (int64_t)n * K);
   int mt = min(F32_MT, M - m0);
-  for (int k4 = lane; k4 < K / 4; k4 += 32) {
-    float4 wv = __ldg(wr + k4);
+  auto fma_row = [&](int k4, const float4& wv) {
 #pragma unroll
     for (int i = 0; i < F32_MT; i++) {
       if (i < mt) {
@@ -26,13 +36,18 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(int M, int N, int K, cons
         acc[i] += wv.x * xv.x + wv.y * xv.y + wv.z * xv.z + wv.w * xv.w;
       }
     }
-  }
+  };
+#pragma unroll
+  for (int i = 0; i < F32_PRE; i++)
+    if (lane + 32 * i < nk4) fma_row(lane + 32 * i, wpre[i]);
+#pragma unroll 4
+  for (int k4 = lane + 32 * F32_PRE; k4 < nk4; k4 += 32) fma_row(k4, __ldg(wr + k4));
 #pragma unroll
   for (int i = 0; i < F32_MT; i++) {
     float v = warp_sum(acc[i]);
     if (lane == 0 && i < mt) {
       int64_t o = (int64_t)(m0 + i) * N + n;
-      v += bias ? bias[n] : 0.f;
+      v += bn;
       y[o] = accumulate ? y[o] + v : v;
     }
   }
@@ -44,7 +59,7 @@ int k_gemm_f32(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const float
   if (K % 4) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_f32: K must be a multiple of 4");
   dim3 grid((unsigned)((N + 7) / 8), (unsigned)((M + F32_MT - 1) / F32_MT));
   if (grid.y > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_f32: M too large");
-  gemm_f32_kernel<<<grid, 256, 0, ctx->stream>>>((int)M, (int)N, (int)K, x, w, bias, y, accumulate);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, gemm_f32_kernel, grid, dim3(256), 0, (int)M, (int)N, (int)K, x, w, bias, y, accumulate));
+  ctx->launches++;
   return STRICTB200_OK;
 }

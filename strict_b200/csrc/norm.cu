@@ -259,11 +259,9 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
     t[3] += __fmul_rn(__fmul_rn(acc[3], sxr), sw.w);
   } else if (MODE == 3) {
     // Fused all-reduce, row-granular: this block sums the rank's own split-K partials of its row
-    // and pushes every value, paired with the row's epoch, into every peer's buffer (two 16-byte
-    // stores of two {value, epoch} packets each); then it polls its own buffer until the packets
-    // of the same row have arrived from every peer and adds the ranks' values in rank order.
-    // One NVLink one-way latency, no fence, no other kernel, no grid-wide step. The waits are
-    // bounded; on expiry the error word is set and the (wrong) sum is used.
+    // and exchanges them with the peers as 8-byte packets {value, epoch} pushed into their
+    // buffers (two 16-byte stores of two packets each); a receiver polls its own buffer until
+    // the packets carry the row's current epoch. No fence, no other kernel, no grid-wide step.
     float4 p[8];
 #pragma unroll
     for (int s = 0; s < 8; s++)
@@ -278,33 +276,61 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
     const float own[4] = {__fmul_rn(__fmul_rn(acc[0], sxr), sw.x), __fmul_rn(__fmul_rn(acc[1], sxr), sw.y),
                           __fmul_rn(__fmul_rn(acc[2], sxr), sw.z), __fmul_rn(__fmul_rn(acc[3], sxr), sw.w)};
     const float ef = __int_as_float(e);
-    const size_t val = (size_t)(row * d + k) * 2;  // word offset of this thread's 4 packets inside a (parity, source) area
+    const size_t val = (size_t)(row * d + k) * 2;  // word offset of this thread's 4 packets inside a packet area
     const size_t area = (size_t)a.comm.row_elems * 2;
-#pragma unroll
-    for (int r = 0; r < 8; r++)
-      if (r < a.comm.world && r != a.comm.rank) {
-        float* dst = a.comm.row_data[r] + ((size_t)(e & 1) * 8 + a.comm.rank) * area + val;
-        asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(own[0]), "f"(ef), "f"(own[1]), "f"(ef) : "memory");
-        asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 4), "f"(own[2]), "f"(ef), "f"(own[3]), "f"(ef) : "memory");
+    auto push = [&](float* dst, const float* v4) {
+      asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(v4[0]), "f"(ef), "f"(v4[1]), "f"(ef) : "memory");
+      asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 4), "f"(v4[2]), "f"(ef), "f"(v4[3]), "f"(ef) : "memory");
+    };
+    auto poll = [&](const float* src, float* v4) {  // bounded: on expiry the error word is set and the (wrong) values are used
+      float4 q0, q1;
+      uint32_t spins = 0;
+      while (true) {
+        q0 = ld_peer4(src);
+        q1 = ld_peer4(src + 4);
+        if (__float_as_int(q0.y) == e && __float_as_int(q0.w) == e && __float_as_int(q1.y) == e && __float_as_int(q1.w) == e) break;
+        if (++spins > (1u << 22)) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
+        if ((spins & 4095u) == 0 && *(volatile int*)a.comm.status) break;  // another wait already expired: do not wait it out again
       }
+      v4[0] = q0.x; v4[1] = q0.z; v4[2] = q1.x; v4[3] = q1.z;
+    };
+    float* mine = a.comm.row_data[a.comm.rank];
+    if (a.comm.world < 4) {
+      // one shot: every rank sends its whole row to every peer and sums all of them
 #pragma unroll
-    for (int r = 0; r < 8; r++)
-      if (r < a.comm.world) {
-        if (r == a.comm.rank) {
-          t[0] += own[0]; t[1] += own[1]; t[2] += own[2]; t[3] += own[3];
-        } else {
-          const float* src = a.comm.row_data[a.comm.rank] + ((size_t)(e & 1) * 8 + r) * area + val;
-          float4 q0, q1;
-          uint32_t spins = 0;
-          while (true) {
-            q0 = ld_peer4(src);
-            q1 = ld_peer4(src + 4);
-            if (__float_as_int(q0.y) == e && __float_as_int(q0.w) == e && __float_as_int(q1.y) == e && __float_as_int(q1.w) == e) break;
-            if (++spins > (1u << 22)) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
-          }
-          t[0] += q0.x; t[1] += q0.z; t[2] += q1.x; t[3] += q1.z;
+      for (int r = 0; r < 8; r++)
+        if (r < a.comm.world && r != a.comm.rank) push(a.comm.row_data[r] + ((size_t)(e & 1) * 8 + a.comm.rank) * area + val, own);
+#pragma unroll
+      for (int r = 0; r < 8; r++)
+        if (r < a.comm.world) {
+          float v[4] = {own[0], own[1], own[2], own[3]};
+          if (r != a.comm.rank) poll(mine + ((size_t)(e & 1) * 8 + r) * area + val, v);
+          t[0] += v[0]; t[1] += v[1]; t[2] += v[2]; t[3] += v[3];
         }
+    } else {
+      // two shots (the one-shot push sends world-1 copies of the row from every rank, 7 MB per
+      // rank and sum at 8 ranks): rank j owns the columns [j*d/world, (j+1)*d/world) of every
+      // row. Each thread sends its 4 partial sums to the owner of its columns; the owner's
+      // threads add the ranks' values in rank order and send the sums back to everyone.
+      const int owner = (int)(k / (d / a.comm.world));  // uniform per warp: d/world is a multiple of 128
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      if (owner != a.comm.rank) {
+        push(a.comm.row_data[owner] + ((size_t)(e & 1) * 8 + a.comm.rank) * area + val, own);
+        poll(mine + (16 + (size_t)(e & 1)) * area + val, sum);
+      } else {
+#pragma unroll
+        for (int r = 0; r < 8; r++)
+          if (r < a.comm.world) {
+            float v[4] = {own[0], own[1], own[2], own[3]};
+            if (r != a.comm.rank) poll(mine + ((size_t)(e & 1) * 8 + r) * area + val, v);
+            sum[0] += v[0]; sum[1] += v[1]; sum[2] += v[2]; sum[3] += v[3];
+          }
+#pragma unroll
+        for (int r = 0; r < 8; r++)
+          if (r < a.comm.world && r != a.comm.rank) push(a.comm.row_data[r] + (16 + (size_t)(e & 1)) * area + val, sum);
       }
+      t[0] += sum[0]; t[1] += sum[1]; t[2] += sum[2]; t[3] += sum[3];
+    }
     __syncthreads();  // every thread of the row has read the epoch
     if (threadIdx.x == 0) *(volatile int*)(a.comm.row_epoch + row) = e;
   } else if (MODE == 2) {
@@ -364,6 +390,8 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
 
 __global__ void __launch_bounds__(ROW_THREADS) layernorm_kernel(const float* __restrict__ x, const float* __restrict__ g,
                                                                 const float* __restrict__ b, float eps, int64_t d, float* __restrict__ y) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   int64_t row = blockIdx.x;
   const float* xr = x + row * d;
@@ -525,6 +553,8 @@ __global__ void __launch_bounds__(512) swiglu_decode_part_kernel(const float* __
 }
 
 __global__ void gelu_tanh_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ y) {
+  pdl_trigger();
+  pdl_wait();
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     float v = x[i];
@@ -564,7 +594,8 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale};
   // decode-step shapes: 4 columns per thread, at most 8 partials, no bf16 residual
   const bool narrow = d % 128 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
-  if (narrow && a.comm && a.part && a.groups == 1 && a.splits <= 8 && a.comm->world <= 8 && M <= a.comm->max_rows && M * d <= a.comm->row_elems) {
+  if (narrow && a.comm && a.part && a.groups == 1 && a.splits <= 8 && a.comm->world <= 8 && M <= a.comm->max_rows && M * d <= a.comm->row_elems &&
+      (a.comm->world < 4 || d % (a.comm->world * 128) == 0)) {
     SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<3>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
     ctx->launches++;
     return STRICTB200_OK;
@@ -595,8 +626,8 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   return STRICTB200_OK;
 }
 int k_layernorm(strictb200_ctx* ctx, const float* x, const float* g, const float* b, float eps, int64_t M, int64_t d, float* y) {
-  layernorm_kernel<<<(unsigned)M, ROW_THREADS, 0, ctx->stream>>>(x, g, b, eps, d, y);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, layernorm_kernel, dim3((unsigned)M), dim3(ROW_THREADS), 0, x, g, b, eps, d, y));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 int k_add_f32(strictb200_ctx* ctx, float* x, const float* y, int64_t n) {
@@ -633,8 +664,8 @@ int k_swiglu_part(strictb200_ctx* ctx, const float* part, int splits, const floa
   return sb_fail(STRICTB200_ERR_UNSUPPORTED, "swiglu over partials: no block shape for this width");
 }
 int k_gelu_tanh(strictb200_ctx* ctx, const float* x, int64_t n, float* y) {
-  gelu_tanh_kernel<<<stream_grid(ctx, n, 256), 256, 0, ctx->stream>>>(x, n, y);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, gelu_tanh_kernel, dim3(stream_grid(ctx, n, 256)), dim3(256), 0, x, n, y));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 

@@ -32,6 +32,8 @@ __global__ void embedding_bf16_f32_kernel(const bf16* __restrict__ table, const 
 __global__ void embedding_f32_kernel(const float* __restrict__ wte, const float* __restrict__ wpe, const int32_t* __restrict__ ids,
                                      const int32_t* __restrict__ pos, const int32_t* __restrict__ lens, int64_t d, int64_t vocab, int max_pos,
                                      float* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   int64_t t = blockIdx.x;
   int64_t id = ids[t];
   if (id < 0 || id >= vocab) id = 0;
@@ -119,8 +121,8 @@ int k_embedding_bf16_f32(strictb200_ctx* ctx, const bf16* table, const int32_t* 
 }
 int k_embedding_f32(strictb200_ctx* ctx, const float* wte, const float* wpe, const int32_t* ids, const int32_t* pos, const int32_t* lens,
                     int64_t T, int64_t d, int64_t vocab, int max_pos, float* out) {
-  embedding_f32_kernel<<<(unsigned)T, 256, 0, ctx->stream>>>(wte, wpe, ids, pos, lens, d, vocab, max_pos, out);
-  SB_LAUNCHED(ctx);
+  SB_CUDA(sb_launch(ctx, embedding_f32_kernel, dim3((unsigned)T), dim3(256), 0, wte, wpe, ids, pos, lens, d, vocab, max_pos, out));
+  ctx->launches++;
   return STRICTB200_OK;
 }
 // Two-stage pick for wide rows: blocks of 256 threads scan 4096-column chunks, then one block

@@ -52,7 +52,8 @@ constexpr int COMM_ROWS = 64;                  // rows of the row-granular excha
 constexpr long long COMM_ROW_ELEMS = (long long)COMM_ROWS * 4096;  // values per (parity, source rank) of the row area
 // row area: [parity][source rank][value][2] words, every value travelling with its epoch (8-byte packets)
 constexpr size_t COMM_ROW_OFFSET = COMM_FLAG_BYTES + 2 * COMM_MAX_ELEMS * sizeof(float);
-constexpr size_t COMM_BYTES = COMM_ROW_OFFSET + (size_t)2 * 8 * COMM_ROW_ELEMS * 2 * sizeof(float);
+// [2 parities][8 source ranks] areas of partial sums, then [2 parities] areas of finished sums (two-shot exchange)
+constexpr size_t COMM_BYTES = COMM_ROW_OFFSET + (size_t)(2 * 8 + 2) * COMM_ROW_ELEMS * 2 * sizeof(float);
 
 struct TpState {
   nccl_comm comm = nullptr;
