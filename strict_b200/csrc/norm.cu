@@ -105,6 +105,7 @@ struct RowNormDev {
   bf16* y;
   uint8_t* q;
   float* qscale;
+  int two_shot;  // fused all-reduce: owner-reduces-and-returns instead of everyone-sends-to-everyone
 };
 
 __global__ void __launch_bounds__(512) rownorm_kernel(RowNormDev a, int64_t M, int64_t d) {
@@ -295,7 +296,7 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
       v4[0] = q0.x; v4[1] = q0.z; v4[2] = q1.x; v4[3] = q1.z;
     };
     float* mine = a.comm.row_data[a.comm.rank];
-    if (a.comm.world < 4) {
+    if (!a.two_shot) {
       // one shot: every rank sends its whole row to every peer and sums all of them
 #pragma unroll
       for (int r = 0; r < 8; r++)
@@ -591,11 +592,16 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   // many rows (prefill): narrower blocks, two chunks per thread and more blocks per SM keep more bytes in flight
   if (M > 1024 && threads > 256) threads = 256;
   while ((int64_t)threads * 8 * MAX_CHUNKS < d) threads += 32;
-  RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale};
+  RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale, 0};
   // decode-step shapes: 4 columns per thread, at most 8 partials, no bf16 residual
   const bool narrow = d % 128 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
-  if (narrow && a.comm && a.part && a.groups == 1 && a.splits <= 8 && a.comm->world <= 8 && M <= a.comm->max_rows && M * d <= a.comm->row_elems &&
-      (a.comm->world < 4 || d % (a.comm->world * 128) == 0)) {
+  // Four or more ranks exchange in two shots (one shot sends world-1 copies of every row);
+  // STRICTB200_TP_TWO_SHOT=0/1 forces either (read per call: the tests run both on two GPUs).
+  if (a.comm) {
+    const char* ts = getenv("STRICTB200_TP_TWO_SHOT");
+    v.two_shot = (ts ? atoi(ts) != 0 : a.comm->world >= 4) && d % (a.comm->world * 128) == 0;
+  }
+  if (narrow && a.comm && a.part && a.groups == 1 && a.splits <= 8 && a.comm->world <= 8 && M <= a.comm->max_rows && M * d <= a.comm->row_elems) {
     SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<3>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
     ctx->launches++;
     return STRICTB200_OK;

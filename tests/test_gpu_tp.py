@@ -23,6 +23,8 @@ def _gpu_count():
 
 def _worker(rank, world, port, path, out, fused):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    if fused:
+        os.environ["STRICTB200_TP_TWO_SHOT"] = "1" if fused == 2 else "0"  # the two exchange patterns of the fused all-reduce
     import torch.distributed as dist
     import strict_b200 as sb
     from strict_b200 import native as N, tp
@@ -55,7 +57,7 @@ def _worker(rank, world, port, path, out, fused):
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("fused", [False, True], ids=["nccl", "peer-memory"])
+@pytest.mark.parametrize("fused", [0, 1, 2], ids=["nccl", "peer-memory-one-shot", "peer-memory-two-shot"])
 def test_tp2_matches_oracle(oracle, tmp_path, fused):
     import torch.multiprocessing as mp
     with socket.socket() as s:
