@@ -277,18 +277,22 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
     const float own[4] = {__fmul_rn(__fmul_rn(acc[0], sxr), sw.x), __fmul_rn(__fmul_rn(acc[1], sxr), sw.y),
                           __fmul_rn(__fmul_rn(acc[2], sxr), sw.z), __fmul_rn(__fmul_rn(acc[3], sxr), sw.w)};
     const float ef = __int_as_float(e);
-    const size_t val = (size_t)(row * d + k) * 2;  // word offset of this thread's 4 packets inside a packet area
+    // Word offsets of this thread's two 16-byte stores inside a packet area: the warp's 128 columns
+    // are 256 words; the lanes' first stores are contiguous, then the second ones, so that each
+    // store instruction of a warp writes four whole 128-byte lines (NVLink carries whole lines
+    // far better than half-written sectors).
+    const size_t off0 = (size_t)(row * d + (k & ~(int64_t)127)) * 2 + (size_t)(threadIdx.x & 31) * 4, off1 = off0 + 128;
     const size_t area = (size_t)a.comm.row_elems * 2;
-    auto push = [&](float* dst, const float* v4) {
-      asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(v4[0]), "f"(ef), "f"(v4[1]), "f"(ef) : "memory");
-      asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 4), "f"(v4[2]), "f"(ef), "f"(v4[3]), "f"(ef) : "memory");
+    auto push = [&](float* dst, const float* v4) {  // dst: start of a packet area
+      asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + off0), "f"(v4[0]), "f"(ef), "f"(v4[1]), "f"(ef) : "memory");
+      asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + off1), "f"(v4[2]), "f"(ef), "f"(v4[3]), "f"(ef) : "memory");
     };
     auto poll = [&](const float* src, float* v4) {  // bounded: on expiry the error word is set and the (wrong) values are used
       float4 q0, q1;
       uint32_t spins = 0;
       while (true) {
-        q0 = ld_peer4(src);
-        q1 = ld_peer4(src + 4);
+        q0 = ld_peer4(src + off0);
+        q1 = ld_peer4(src + off1);
         if (__float_as_int(q0.y) == e && __float_as_int(q0.w) == e && __float_as_int(q1.y) == e && __float_as_int(q1.w) == e) break;
         if (++spins > (1u << 22)) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
         if ((spins & 4095u) == 0 && *(volatile int*)a.comm.status) break;  // another wait already expired: do not wait it out again
@@ -300,12 +304,12 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
       // one shot: every rank sends its whole row to every peer and sums all of them
 #pragma unroll
       for (int r = 0; r < 8; r++)
-        if (r < a.comm.world && r != a.comm.rank) push(a.comm.row_data[r] + ((size_t)(e & 1) * 8 + a.comm.rank) * area + val, own);
+        if (r < a.comm.world && r != a.comm.rank) push(a.comm.row_data[r] + ((size_t)(e & 1) * 8 + a.comm.rank) * area, own);
 #pragma unroll
       for (int r = 0; r < 8; r++)
         if (r < a.comm.world) {
           float v[4] = {own[0], own[1], own[2], own[3]};
-          if (r != a.comm.rank) poll(mine + ((size_t)(e & 1) * 8 + r) * area + val, v);
+          if (r != a.comm.rank) poll(mine + ((size_t)(e & 1) * 8 + r) * area, v);
           t[0] += v[0]; t[1] += v[1]; t[2] += v[2]; t[3] += v[3];
         }
     } else {
@@ -316,19 +320,19 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
       const int owner = (int)(k / (d / a.comm.world));  // uniform per warp: d/world is a multiple of 128
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
       if (owner != a.comm.rank) {
-        push(a.comm.row_data[owner] + ((size_t)(e & 1) * 8 + a.comm.rank) * area + val, own);
-        poll(mine + (16 + (size_t)(e & 1)) * area + val, sum);
+        push(a.comm.row_data[owner] + ((size_t)(e & 1) * 8 + a.comm.rank) * area, own);
+        poll(mine + (16 + (size_t)(e & 1)) * area, sum);
       } else {
 #pragma unroll
         for (int r = 0; r < 8; r++)
           if (r < a.comm.world) {
             float v[4] = {own[0], own[1], own[2], own[3]};
-            if (r != a.comm.rank) poll(mine + ((size_t)(e & 1) * 8 + r) * area + val, v);
+            if (r != a.comm.rank) poll(mine + ((size_t)(e & 1) * 8 + r) * area, v);
             sum[0] += v[0]; sum[1] += v[1]; sum[2] += v[2]; sum[3] += v[3];
           }
 #pragma unroll
         for (int r = 0; r < 8; r++)
-          if (r < a.comm.world && r != a.comm.rank) push(a.comm.row_data[r] + (16 + (size_t)(e & 1)) * area + val, sum);
+          if (r < a.comm.world && r != a.comm.rank) push(a.comm.row_data[r] + (16 + (size_t)(e & 1)) * area, sum);
       }
       t[0] += sum[0]; t[1] += sum[1]; t[2] += sum[2]; t[3] += sum[3];
     }

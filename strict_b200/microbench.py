@@ -1,13 +1,15 @@
 """Kernel microbenchmarks at the shapes of BASELINE.json configs[1] (GEMM/GEMV) and configs[2]
 (GQA attention), through the C ABI, timed with CUDA events on the library's stream.
 
-    python -m strict_b200.microbench [gemm] [attn] [--iters N] [--shape M,N,K]
+    python -m strict_b200.microbench [gemm] [attn] [ew] [--iters N] [--shape M,N,K]
 
 Every timed call reads buffers that were not touched by the previous call (weights rotate
 through enough distinct copies to exceed the 126 MB L2; the attention caches are GBs), so the
 HBM figures are not L2 figures. The GEMM calls are recorded once (one call per weight copy)
 and replayed, so the figure is device time, not the host's submission rate. One JSON line
-per case.
+per case. `ew` times the element-wise surface in the six ways of the reference's own
+performance harness (Strict.Compiler.Cuda.Tests/TestPerformance.cs:13-61): one element at a
+time and in chunks, on one host thread and on all of them, on the GPU, and GPU + host together.
 """
 import argparse
 import json
@@ -119,6 +121,78 @@ def attn_cases(ctx, iters):
                       "peaks": kind}), flush=True)
 
 
+def ew_cases(ctx, count=1 << 24, chunk=100):
+    """The reference's six timings (TestPerformance.cs:16-21: SingleThread, SingleThreadChunks,
+    ParallelCpu, ParallelCpuChunks, CudaGpu, CudaGpuAndCpu) for out = a + b over `count` floats.
+    The host legs are numpy on slices (one element per call for the unchunked ones, on a bounded
+    prefix whose size is reported); the GPU legs include the copies in both directions, as the
+    reference's RunGpu does through CudaDeviceVariable (CSharpToCudaTranspilerTests.cs:64-77)."""
+    import time
+    from concurrent.futures import ThreadPoolExecutor
+    hbm, _, kind = _peaks()
+    rng = np.random.default_rng(6)
+    a, b = rng.standard_normal(count, np.float32), rng.standard_normal(count, np.float32)
+    out = np.empty_like(a)
+    threads = os.cpu_count() or 1
+    pool = ThreadPoolExecutor(threads)
+
+    def run_chunk(start, n):
+        np.add(a[start:start + n], b[start:start + n], out=out[start:start + n])
+
+    def spread(lo, hi, step):  # Parallel.For over [lo, hi) in steps of `step`, one span per thread
+        idx = list(range(lo, hi, step))
+        per = (len(idx) + threads - 1) // threads
+        list(pool.map(lambda part: [run_chunk(i, step) for i in part], [idx[t * per:(t + 1) * per] for t in range(threads)]))
+
+    da, db, do = DV(ctx, count), DV(ctx, count), DV(ctx, count)
+
+    def run_gpu(n):
+        if n <= 0:
+            return
+        N.check(L().strictb200_upload(ctx.h, da.p, N.ptr(a), 4 * n))
+        N.check(L().strictb200_upload(ctx.h, db.p, N.ptr(b), 4 * n))
+        N.check(L().strictb200_ew_binary(ctx.h, 0, da.p, db.p, do.p, n))
+        N.check(L().strictb200_download(ctx.h, N.ptr(out), do.p, 4 * n))
+
+    small = min(count, 1 << 18)  # one numpy call per element is ~1 us: bound the unchunked legs
+    legs = [
+        ("SingleThread", small, lambda: [run_chunk(i, 1) for i in range(small)]),
+        ("SingleThreadChunks", count, lambda: [run_chunk(i, chunk) for i in range(0, count - chunk + 1, chunk)]),
+        ("ParallelCpu", small, lambda: spread(0, small, 1)),
+        ("ParallelCpuChunks", count, lambda: spread(0, count - chunk + 1, chunk)),
+        ("CudaGpu", count, lambda: run_gpu(count)),
+    ]
+    gpu_n = int(count * 0.97) // chunk * chunk  # the reference's GpuFactor (TestPerformance.cs:56)
+
+    def both():
+        f = pool.submit(run_gpu, gpu_n)
+        for i in range(gpu_n, count - chunk + 1, chunk):
+            run_chunk(i, chunk)
+        f.result()
+    legs.append(("CudaGpuAndCpu", count, both))
+    run_gpu(count)  # warm the context and page the host arrays in
+    for name, n, fn in legs:
+        t0 = time.perf_counter()
+        fn()
+        dt = time.perf_counter() - t0
+        print(json.dumps({"case": "ew_add", "variant": name, "elements": n, "chunk": chunk, "host_threads": threads,
+                          "ms": dt * 1e3, "Melem_per_s": n / dt / 1e6}), flush=True)
+    assert np.array_equal(out[:count // chunk * chunk], (a + b)[:count // chunk * chunk])
+    # the kernel alone, device-resident (3 x 4 bytes per element), larger than L2
+    ctx.synchronize()
+    reps = 20
+    N.check(L().strictb200_ew_binary(ctx.h, 0, da.p, db.p, do.p, count))
+    ctx.timer_begin()
+    for _ in range(reps):
+        N.check(L().strictb200_ew_binary(ctx.h, 0, da.p, db.p, do.p, count))
+    ms = ctx.timer_end() / reps
+    print(json.dumps({"case": "ew_add", "variant": "kernel_only_device_resident", "elements": count, "us": ms * 1e3,
+                      "GBps": 12.0 * count / ms / 1e6, "hbm_frac": 12.0 * count / ms / 1e6 / hbm, "peaks": kind}), flush=True)
+    for v in (da, db, do):
+        v.free()
+    pool.shutdown()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="*", default=["gemm", "attn"])
@@ -130,6 +204,8 @@ def main():
         gemm_cases(ctx, args.iters, tuple(int(v) for v in args.shape.split(",")) if args.shape else None)
     if "attn" in args.what:
         attn_cases(ctx, args.iters)
+    if "ew" in args.what:
+        ew_cases(ctx)
     ctx.dispose()
 
 
