@@ -518,14 +518,16 @@ __global__ void kv_append_f32_kernel(const float* __restrict__ qkv, float* __res
     vc[dst] = qkv[t * 3 * hd + 2 * hd + e];
   }
 }
-// grid (H, T), 128 threads; scores of one (token, head) live in shared memory.
-__global__ void __launch_bounds__(128) attn_f32_kernel(const float* __restrict__ qkv, const float* __restrict__ kc, const float* __restrict__ vc,
+// grid (H, T), 256 threads; scores of one (token, head) live in shared memory.
+__global__ void __launch_bounds__(256) attn_f32_kernel(const float* __restrict__ qkv, const float* __restrict__ kc, const float* __restrict__ vc,
                                                        const int32_t* __restrict__ seq, const int32_t* __restrict__ pos,
                                                        const int32_t* __restrict__ lens, int H, int Dh, int maxlen, float scale,
-                                                       float* __restrict__ out) {
+                                                       float* __restrict__ out, float* kc_new, float* vc_new) {
+  // kc_new/vc_new (decode: every row is its own sequence) make this block also append its head's
+  // new key and value; it then takes position p from the projection output, not from the cache.
   pdl_trigger();
   pdl_wait();
-  extern __shared__ float sc[];  // [maxlen] scores, then [Dh] query
+  extern __shared__ __align__(16) float sc[];  // [maxlen rounded up to 4] scores, [Dh] query, [blockDim.x] float4 partial rows
   __shared__ float red[32];
   int h = blockIdx.x;
   int64_t t = blockIdx.y;
@@ -533,15 +535,24 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(const float* __restrict__
   int p = pos ? pos[t] : lens[b];
   if (p < 0 || p >= maxlen) return;
   int n = p + 1;
-  float* qs = sc + maxlen;
+  float* qs = sc + ((maxlen + 3) & ~3);
   int hd = H * Dh;
   for (int d = threadIdx.x; d < Dh; d += blockDim.x) qs[d] = qkv[t * 3 * hd + h * Dh + d];
   __syncthreads();
   const float* kb = kc + ((int64_t)b * H + h) * maxlen * Dh;
   const float* vb = vc + ((int64_t)b * H + h) * maxlen * Dh;
+  const float* k_own = qkv + t * 3 * hd + hd + h * Dh;
+  const float* v_own = k_own + hd;
+  const int own = kc_new ? p : -1;
+  if (kc_new)
+    for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
+      const int64_t dst = (((int64_t)b * H + h) * maxlen + p) * Dh + d;
+      kc_new[dst] = k_own[d];
+      vc_new[dst] = v_own[d];
+    }
   float mx = -INFINITY;
   for (int j = threadIdx.x; j < n; j += blockDim.x) {
-    const float4* kr = (const float4*)(kb + (int64_t)j * Dh);
+    const float4* kr = (const float4*)(j == own ? k_own : kb + (int64_t)j * Dh);
     float acc = 0.f;
     for (int d4 = 0; d4 < Dh / 4; d4++) {
       float4 kv = kr[d4];
@@ -561,10 +572,35 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(const float* __restrict__
   l = block_sum(l, red);
   __syncthreads();
   float inv = 1.0f / l;
-  for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < n; j++) acc += sc[j] * vb[(int64_t)j * Dh + d];
-    out[t * hd + h * Dh + d] = acc * inv;
+  // P.V: the block's threads form groups of Dh/4 lanes; group g adds the keys g, g+G, ... with one
+  // float4 of the value row per lane (a single query row would otherwise walk all keys on Dh
+  // threads, one dependent step per key), then the groups' partial rows are added in group order.
+  const int dl = Dh / 4, G = (int)blockDim.x / dl;
+  float* part = qs + Dh;  // [blockDim.x] float4
+  if (G >= 1) {
+    const int g = (int)threadIdx.x / dl, c = (int)threadIdx.x % dl;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (g < G) {
+#pragma unroll 4
+      for (int j = g; j < n; j += G) {
+        const float4 v = *(const float4*)((j == own ? v_own : vb + (int64_t)j * Dh) + 4 * c);
+        const float pj = sc[j];
+        acc.x += pj * v.x; acc.y += pj * v.y; acc.z += pj * v.z; acc.w += pj * v.w;
+      }
+    }
+    *(float4*)(part + 4 * threadIdx.x) = acc;
+    __syncthreads();
+    for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
+      float o = 0.f;
+      for (int gg = 0; gg < G; gg++) o += part[(gg * dl + d / 4) * 4 + (d & 3)];
+      out[t * hd + h * Dh + d] = o * inv;
+    }
+  } else {  // head wider than four times the block: one thread per output column
+    for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
+      float acc = 0.f;
+      for (int j = 0; j < n; j++) acc += sc[j] * (j == own ? v_own[d] : vb[(int64_t)j * Dh + d]);
+      out[t * hd + h * Dh + d] = acc * inv;
+    }
   }
 }
 
@@ -667,18 +703,25 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
 int k_attn_f32(strictb200_ctx* ctx, const float* qkv, float* kc, float* vc, const int32_t* seq, const int32_t* pos, const int32_t* lens,
                int64_t T, int H, int Dh, int maxlen, float scale, float* out) {
   if (Dh % 4) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: head_dim must be a multiple of 4");
-  size_t smem = ((size_t)maxlen + Dh) * sizeof(float);
+  const int threads = 256;
+  size_t smem = ((size_t)((maxlen + 3) & ~3) + Dh + 4 * threads) * sizeof(float);
   if (smem > 200 * 1024) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: fp32 path supports at most ~50k positions");
   static size_t attr_smem = 48 * 1024;
   if (smem > attr_smem) {
     SB_CUDA(cudaFuncSetAttribute(attn_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_smem = smem;
   }
-  SB_CUDA(sb_launch(ctx, kv_append_f32_kernel, dim3((unsigned)T), dim3(256), 0, qkv, kc, vc, seq, pos, lens, H, Dh, maxlen));
-  ctx->launches++;
   if (T > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: too many rows for the fp32 path");
+  // rows that are sequences of their own (decode) append inside the attention kernel; prompt rows
+  // need the keys of other rows of their sequence, so those are appended by a kernel of its own first
+  const bool fused_append = seq == nullptr;
+  if (!fused_append) {
+    SB_CUDA(sb_launch(ctx, kv_append_f32_kernel, dim3((unsigned)T), dim3(256), 0, qkv, kc, vc, seq, pos, lens, H, Dh, maxlen));
+    ctx->launches++;
+  }
   dim3 grid(H, (unsigned)T);
-  SB_CUDA(sb_launch(ctx, attn_f32_kernel, grid, dim3(128), smem, (const float*)qkv, (const float*)kc, (const float*)vc, seq, pos, lens, H, Dh, maxlen, scale, out));
+  SB_CUDA(sb_launch(ctx, attn_f32_kernel, grid, dim3(threads), smem, (const float*)qkv, (const float*)kc, (const float*)vc, seq, pos, lens, H, Dh, maxlen,
+                    scale, out, fused_append ? kc : (float*)nullptr, fused_append ? vc : (float*)nullptr));
   ctx->launches++;
   return STRICTB200_OK;
 }

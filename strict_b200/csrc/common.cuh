@@ -148,6 +148,13 @@ int k_swiglu(strictb200_ctx*, const bf16* gate_up, const float* gate_up_f32, int
 int k_swiglu_part(strictb200_ctx*, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t I, uint8_t* q,
                   float* qscale);
 int k_gelu_tanh(strictb200_ctx*, const float* x, int64_t n, float* y);
+#ifdef __CUDACC__
+// tanh-approximated GELU in fp32 with the operation order of the element-wise kernel
+__device__ __forceinline__ float sb_gelu_tanh(float v) {
+  const float u = __fmul_rn(0.797884583f, __fadd_rn(v, __fmul_rn(0.044715f, __fmul_rn(__fmul_rn(v, v), v))));
+  return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanhf(u)));
+}
+#endif
 // rope.cu
 struct RopeArgs {
   const bf16* qkv = nullptr;      // [T, nqkv] bf16 (used when part and qkv_f32 are null)

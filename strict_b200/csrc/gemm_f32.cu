@@ -1,6 +1,7 @@
 // fp32 linear layer of the GPT-2 path: Y[M,N] = X[M,K] . W[N,K]^T + bias. Decode (M = 1) is
 // a pure HBM stream over W; one warp per output channel, lanes split K with 128-bit loads,
-// warp-shuffle reduction. Up to 8 token rows share one pass over a weight row.
+// warp-shuffle reduction. Up to 8 token rows share one pass over a weight row. `accumulate`: 0
+// stores the result, 1 adds it to Y (residual), 2 stores GELU(result) (the MLP's first layer).
 #include "common.cuh"
 
 namespace {
@@ -48,7 +49,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(int M, int N, int K, cons
     if (lane == 0 && i < mt) {
       int64_t o = (int64_t)(m0 + i) * N + n;
       v += bn;
-      y[o] = accumulate ? y[o] + v : v;
+      y[o] = accumulate == 1 ? y[o] + v : accumulate == 2 ? sb_gelu_tanh(v) : v;
     }
   }
 }

@@ -398,9 +398,8 @@ int gpt2_layers(strictb200_model* m, strictb200_kv* kv, int64_t T, float* xf, fl
     SB_TRY(k_attn_f32(ctx, bf_, kv_kf(kv, l), kv_vf(kv, l), seq, pos, kv->d_lens, T, c.n_q_heads, c.head_dim, kv->maxlen, scale, af));
     SB_TRY(k_gemm_f32(ctx, T, d, d, af, w.fo.w, w.fo.b, xf, 1));
     SB_TRY(k_layernorm(ctx, xf, w.norm2_g, w.norm2_b, c.eps, T, d, af));
-    SB_TRY(k_gemm_f32(ctx, T, c.d_ff, d, af, w.ffc.w, w.ffc.b, bf_, 0));
-    SB_TRY(k_gelu_tanh(ctx, bf_, T * c.d_ff, af));
-    SB_TRY(k_gemm_f32(ctx, T, d, c.d_ff, af, w.fproj.w, w.fproj.b, xf, 1));
+    SB_TRY(k_gemm_f32(ctx, T, c.d_ff, d, af, w.ffc.w, w.ffc.b, bf_, 2));  // GELU in the epilogue
+    SB_TRY(k_gemm_f32(ctx, T, d, c.d_ff, bf_, w.fproj.w, w.fproj.b, xf, 1));
   }
   return STRICTB200_OK;
 }

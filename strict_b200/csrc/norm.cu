@@ -562,9 +562,7 @@ __global__ void gelu_tanh_kernel(const float* __restrict__ x, int64_t n, float* 
   pdl_wait();
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    float v = x[i];
-    float u = __fmul_rn(0.797884583f, __fadd_rn(v, __fmul_rn(0.044715f, __fmul_rn(__fmul_rn(v, v), v))));
-    y[i] = __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanhf(u)));
+    y[i] = sb_gelu_tanh(x[i]);
   }
 }
 
@@ -599,11 +597,11 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale, 0};
   // decode-step shapes: 4 columns per thread, at most 8 partials, no bf16 residual
   const bool narrow = d % 128 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
-  // Four or more ranks exchange in two shots (one shot sends world-1 copies of every row);
+  // Eight ranks exchange in two shots (one shot sends world-1 copies of every row);
   // STRICTB200_TP_TWO_SHOT=0/1 forces either (read per call: the tests run both on two GPUs).
   if (a.comm) {
     const char* ts = getenv("STRICTB200_TP_TWO_SHOT");
-    v.two_shot = (ts ? atoi(ts) != 0 : a.comm->world >= 4) && d % (a.comm->world * 128) == 0;
+    v.two_shot = (ts ? atoi(ts) != 0 : a.comm->world >= 8) && d % (a.comm->world * 128) == 0;
   }
   if (narrow && a.comm && a.part && a.groups == 1 && a.splits <= 8 && a.comm->world <= 8 && M <= a.comm->max_rows && M * d <= a.comm->row_elems) {
     SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<3>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
