@@ -581,7 +581,7 @@ __global__ void __launch_bounds__(256) attn_f32_kernel(const float* __restrict__
     const int g = (int)threadIdx.x / dl, c = (int)threadIdx.x % dl;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (g < G) {
-#pragma unroll 4
+#pragma unroll 8
       for (int j = g; j < n; j += G) {
         const float4 v = *(const float4*)((j == own ? v_own : vb + (int64_t)j * Dh) + 4 * c);
         const float pj = sc[j];

@@ -396,10 +396,40 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
 __global__ void __launch_bounds__(ROW_THREADS) layernorm_kernel(const float* __restrict__ x, const float* __restrict__ g,
                                                                 const float* __restrict__ b, float eps, int64_t d, float* __restrict__ y) {
   pdl_trigger();
-  pdl_wait();
   __shared__ float red[32];
   int64_t row = blockIdx.x;
   const float* xr = x + row * d;
+  if (d <= 4 * ROW_THREADS) {
+    // narrow rows: gain and bias are fetched before the dependency wait, the row is read once and
+    // stays in registers (same per-thread columns and order of additions as the loops below)
+    float gv[4], bv[4], xv[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int64_t k = threadIdx.x + (int64_t)i * ROW_THREADS;
+      if (k < d) { gv[i] = g[k]; bv[i] = b[k]; }
+    }
+    pdl_wait();
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int64_t k = threadIdx.x + (int64_t)i * ROW_THREADS;
+      if (k < d) { xv[i] = xr[k]; s += xv[i]; }
+    }
+    const float mean = __fdiv_rn(block_sum(s, red), (float)d);
+    float vs = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+      if (threadIdx.x + (int64_t)i * ROW_THREADS < d) { const float t = xv[i] - mean; vs += t * t; }
+    const float var = __fdiv_rn(block_sum(vs, red), (float)d);
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int64_t k = threadIdx.x + (int64_t)i * ROW_THREADS;
+      if (k < d) y[row * d + k] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(xv[i], mean), r), gv[i]), bv[i]);
+    }
+    return;
+  }
+  pdl_wait();
   float s = 0.f;
   for (int64_t k = threadIdx.x; k < d; k += ROW_THREADS) s += xr[k];
   float mean = __fdiv_rn(block_sum(s, red), (float)d);
