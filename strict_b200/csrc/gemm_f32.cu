@@ -25,10 +25,12 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(int M, int N, int K, cons
   const int k4_lo = slice * per, k4_hi = min(nk4, k4_lo + per);
   const float4* wr = (const float4*)(w + (int64_t)(live ? n : 0) * K);
   // the weights are constants: the head of the slice streams in while the previous kernel still runs
+  // (streaming loads: a step reads its 0.5 GB of weights once each, and they should not push the
+  // kernels' code and the activations out of L2)
   float4 wpre[F32_PRE];
 #pragma unroll
   for (int i = 0; i < F32_PRE; i++)
-    if (live && k4_lo + lane + 32 * i < k4_hi) wpre[i] = __ldg(wr + k4_lo + lane + 32 * i);
+    if (live && k4_lo + lane + 32 * i < k4_hi) wpre[i] = __ldcs(wr + k4_lo + lane + 32 * i);
   const float bn = bias && live ? bias[n] : 0.f;
   pdl_wait();
   float acc[F32_MT];
@@ -49,7 +51,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(int M, int N, int K, cons
     for (int i = 0; i < F32_PRE; i++)
       if (k4_lo + lane + 32 * i < k4_hi) fma_row(k4_lo + lane + 32 * i, wpre[i]);
 #pragma unroll 4
-    for (int k4 = k4_lo + lane + 32 * F32_PRE; k4 < k4_hi; k4 += 32) fma_row(k4, __ldg(wr + k4));
+    for (int k4 = k4_lo + lane + 32 * F32_PRE; k4 < k4_hi; k4 += 32) fma_row(k4, __ldcs(wr + k4));
   }
 #pragma unroll
   for (int i = 0; i < F32_MT; i++) {
