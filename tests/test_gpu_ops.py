@@ -257,7 +257,7 @@ def test_gemm_fp8w_entry(ctx, oracle, rng):
     assert np.abs(got - want).max() <= np.abs(want).max() * 2 ** -7 and (got != want).mean() < 1e-3
 
 
-@pytest.mark.parametrize("M,N_,K", [(1, 2304, 768), (3, 50257, 768), (128, 768, 3072), (9, 10, 4)])
+@pytest.mark.parametrize("M,N_,K", [(1, 2304, 768), (3, 50257, 768), (128, 768, 3072), (9, 10, 4), (5, 7, 1500), (2, 13, 8200)])
 def test_gemm_f32_vs_oracle(ctx, oracle, rng, M, N_, K):
     x = rng.standard_normal((M, K)).astype(np.float32)
     w = (rng.standard_normal((N_, K)) * 0.02).astype(np.float32)
