@@ -627,11 +627,11 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale, 0};
   // decode-step shapes: 4 columns per thread, at most 8 partials, no bf16 residual
   const bool narrow = d % 128 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
-  // Eight ranks exchange in two shots (one shot sends world-1 copies of every row);
+  // Four or more ranks exchange in two shots (one shot sends world-1 copies of every row);
   // STRICTB200_TP_TWO_SHOT=0/1 forces either (read per call: the tests run both on two GPUs).
   if (a.comm) {
     const char* ts = getenv("STRICTB200_TP_TWO_SHOT");
-    v.two_shot = (ts ? atoi(ts) != 0 : a.comm->world >= 8) && d % (a.comm->world * 128) == 0;
+    v.two_shot = (ts ? atoi(ts) != 0 : a.comm->world >= 4) && d % (a.comm->world * 128) == 0;
   }
   if (narrow && a.comm && a.part && a.groups == 1 && a.splits <= 8 && a.comm->world <= 8 && M <= a.comm->max_rows && M * d <= a.comm->row_elems) {
     SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<3>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
