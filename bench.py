@@ -36,92 +36,88 @@ def peaks():
     return 6650.0, "fallback"
 
 
-class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, device):
-        self.device, self.proc, self.lines = device, None, []
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "200"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
-            self.t.start()
-        except OSError:
-            self.proc = None
-
-    def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
-        self.proc.terminate()
-        self.t.join(timeout=2)
-        sm, mx, reasons = [], [], set()
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+from strict_b200.clocks import ClockSampler  # noqa: E402
 
 
 # ---------------------------------------------------------------------------------- CPU arm
+CPU_TIME_BUDGET_S = 150.0  # wall time the timed steps of the CPU arm may take; fewer steps are run (and reported) beyond it
+
+
+def workload_config(n_gpus):
+    """The keys that name the workload; identical in both arms."""
+    return {"workload": WORKLOAD, "batch": BATCH, "prompt": PROMPT, "layers": 36, "parallelism": f"tp{n_gpus}",
+            "l2": "inputs larger than L2 (17.8 GB streamed per step)"}
+
+
+def mem_available_gb():
+    try:
+        for ln in open("/proc/meminfo"):
+            if ln.startswith("MemAvailable:"):
+                return int(ln.split()[1]) / 1e6
+    except OSError:
+        pass
+    return None
+
+
 def cpu_reference(steps, warmup):
     """The reference has no implementation of this path; its stand-in is this repository's CPU
-    oracle (kind "port"). Bounded sample of one decode step at batch 32: the four E4M3 linears
-    of ONE layer + decode attention of one layer at context 2048 + the LM head are timed on all
-    host threads; a full step is 36 identical layers + the head."""
+    oracle (kind "port"). What is timed is the oracle's own decode step of the whole model — all
+    36 layers with their norms, RoPE, SwiGLU and attention, the LM head and the greedy pick — at
+    batch 32 and context 2048 on all host threads, step after step, each step feeding the next.
+    Set-up (untimed): the seeded weights of the full architecture; the cache is filled with
+    pseudo-random keys and values instead of a CPU prefill of 65,536 tokens, which would take
+    hours. Every reported step was executed; nothing is multiplied. If the requested steps would
+    take longer than CPU_TIME_BUDGET_S, fewer are run and the line says how many."""
     from oracle import oracle as O
     import strict_b200 as sb
     O.build()
-    cfg = sb.CONFIGS["qwen3-8b"]
-    d, D, Hq, Hkv, I, V, Ln = cfg["d_model"], cfg["head_dim"], cfg["n_q_heads"], cfg["n_kv_heads"], cfg["d_ff"], cfg["vocab"], cfg["n_layers"]
-    nq, nkv = Hq * D, Hkv * D
-    shapes = {"qkv": (nq + 2 * nkv, d), "o": (d, nq), "gate_up": (2 * I, d), "down": (d, I)}
-    W = {k: O.gen_qlinear(SEED, 100 + i, n, kk) for i, (k, (n, kk)) in enumerate(shapes.items())}
-    head = O.gen_qlinear(SEED, 3, V, d)
-    rng = np.random.default_rng(0)
-    acts = {k: O.round_bf16(rng.standard_normal((BATCH, kk)).astype(np.float32)) for k, (n, kk) in shapes.items()}
-    q = rng.standard_normal((BATCH, Hq, D)).astype(np.float32)
-    kc = rng.standard_normal((BATCH, Hkv, PROMPT, D)).astype(np.float32)
-    vc = rng.standard_normal((BATCH, Hkv, PROMPT, D)).astype(np.float32)
-    lens = np.full(BATCH, PROMPT, np.int32)
+    cfg = dict(sb.CONFIGS["qwen3-8b"])
+    ctx_len = PROMPT
+    n_max = warmup + steps + 1
+    kv_gb = 2 * cfg["n_layers"] * BATCH * cfg["n_kv_heads"] * (ctx_len + n_max) * cfg["head_dim"] * 4 / 1e9
+    need_gb = kv_gb + 7.6 + 2.5 + 4.0
+    avail = mem_available_gb()
+    note = ""
+    if avail is not None and avail < need_gb:
+        # keep the host alive: shorten the context to what fits and say so
+        per_pos_gb = 2 * cfg["n_layers"] * BATCH * cfg["n_kv_heads"] * cfg["head_dim"] * 4 / 1e9
+        ctx_len = max(64, int((avail - 16.0) / per_pos_gb) - n_max)
+        note = f"; host has {avail:.0f} GB free, context cut to {ctx_len}"
+    t0 = time.perf_counter()
+    om = O.Model(cfg, SEED)
+    st = om.new_state(BATCH, ctx_len + n_max)
+    st.fill_synthetic(SEED + 2, ctx_len)
+    setup_s = time.perf_counter() - t0
+    ids = O.gen_tokens(SEED + 1, 2, BATCH, cfg["vocab"])
     times = []
+    t_begin = None
     for it in range(warmup + steps):
-        t0 = time.perf_counter()
-        for k in shapes:
-            O.linear_fp8w(acts[k], W[k][0], W[k][1])
-        O.attn_decode(q, kc, vc, lens, 1.0 / np.sqrt(D))
+        if it == warmup:
+            t_begin = time.perf_counter()
+        if it > warmup and time.perf_counter() - t_begin > CPU_TIME_BUDGET_S:
+            break
         t1 = time.perf_counter()
-        O.linear_fp8w(acts["qkv"], head[0], head[1])
-        t2 = time.perf_counter()
+        ids = O.argmax(st.decode(ids))
         if it >= warmup:
-            times.append((t1 - t0) * Ln + (t2 - t1))
+            times.append(time.perf_counter() - t1)
+    st.close(), om.close()
     step_s = float(np.mean(times))
     return {"value": BATCH / step_s, "unit": "tokens/s", "cores": O.num_threads(), "kind": "port",
-            "sample": f"per step: one layer's 4 linears + decode attention (ctx {PROMPT}) + LM head at batch {BATCH}, timed on "
-                      f"{O.num_threads()} threads; full step = {Ln} x layer + head; {steps} steps after {warmup} warm-up"}, step_s
+            "sample": f"{len(times)} whole decode steps (36 layers + LM head + greedy pick, batch {BATCH}, context {ctx_len}+) of the CPU oracle on "
+                      f"{O.num_threads()} threads after {warmup} warm-up steps; every step executed, wall clock; set-up {setup_s:.0f} s untimed "
+                      f"(seeded weights, pseudo-random cache){note}",
+            "steps_run": len(times), "timed_s": float(np.sum(times))}, step_s
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
     base, step_s = cpu_reference(max(1, args.steps), max(0, args.warmup))
-    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16 x fp8_e4m3 -> f32", "data": "synthetic", "config": {"workload": WORKLOAD, "timing": "host wall clock"},
-            "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": base["steps_run"],
+            "steps_requested": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 x fp8_e4m3 -> f32", "data": "synthetic", "config": workload_config(args.gpus),
+            "timing": "host wall clock around every step", "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
@@ -161,16 +157,18 @@ def run_ours(args, rank, world, local_rank):
             N.check(N.lib().strictb200_tp_unique_id(N.ptr(h)))
             return h
         ctx.tp_init(world, rank, N.ptr(tp.share_unique_id(dist, rank, make_id, "cuda")))
-        if os.environ.get("STRICTB200_FUSED_AR", "1") != "0":
+        if not args.nccl_allreduce:
             # decode all-reduces: one-shot over peer memory, fused into the consuming row kernel
             ctx.tp_open_peer_buffers(lambda mine: tp.all_gather_bytes(dist, mine, "cuda"))
+    if args.two_shot >= 0:
+        ctx.set_option("tp_two_shot", args.two_shot)
     cfg = dict(sb.CONFIGS["qwen3-8b"])
     if args.layers:
         cfg["n_layers"] = args.layers  # profiling aid: same kernels and shapes, fewer layers resident
     model = sb.Model(ctx, cfg).init_random(SEED)
     if args.no_graph:
         model.set_graph(False)
-    total_steps = 2 * (max(args.warmup, 3) + args.steps) + 16
+    total_steps = 2 * (max(args.warmup, 3) + args.steps) + 16 + (NEW_TOKENS if not args.no_sustained else 0)
     kv = model.new_cache(BATCH, PROMPT + total_steps + 8)
     # prompts: 32 x 2048 uniform ids from the seeded generator; real prefill fills the cache
     toks = np.empty((BATCH, PROMPT), np.int32)
@@ -179,17 +177,23 @@ def run_ours(args, rank, world, local_rank):
     toks[:] = d_tok.to_host().reshape(BATCH, PROMPT)
     d_tok.free()
     t0 = time.perf_counter()
-    prefill_dev_s = None
+    prefill_dev_s, prefill_clocks = None, None
     if args.synthetic_kv:
         kv.fill_synthetic(SEED + 2, PROMPT)  # profiling aid: seeded N(0,1) keys/values instead of the prefill
         first = toks[:, -1].copy()
     else:
+        pf_sampler = ClockSampler(local_rank)
+        if rank == 0:
+            pf_sampler.start()
         ctx.timer_begin()
         first, _ = kv.prefill(toks)
         prefill_dev_s = ctx.timer_end() / 1e3
+        if rank == 0:
+            prefill_clocks = pf_sampler.stop()  # the prefill is tensor-bound: its time follows the SM clock under the power cap
+            if prefill_clocks.get("sm_mhz"):
+                prefill_clocks["device_s_x_sm_mhz"] = prefill_dev_s * prefill_clocks["sm_mhz"]
     ctx.synchronize()
     prefill_s = time.perf_counter() - t0
-    time.sleep(1.0)  # set-up: let the power state settle after ~2 s of tensor-bound prefill before the memory-bound decode is timed
 
     # ---- value: device-resident ids, graph replay
     ids_dev = first.copy()
@@ -212,6 +216,22 @@ def run_ours(args, rank, world, local_rank):
     ms = max_over_ranks(ms)
     clocks = sampler.stop() if rank == 0 else None
     value = BATCH * args.steps / (ms / 1e3)
+
+    # ---- sustained: the specification's 256 decoded tokens in one timed region (same method, graph replay)
+    sustained = None
+    if not args.no_sustained:
+        barrier()
+        s_sampler = ClockSampler(local_rank)
+        if rank == 0:
+            s_sampler.start()
+        ctx.synchronize()
+        barrier()
+        ctx.timer_begin()
+        kv.decode_steps_device(NEW_TOKENS)
+        s_ms = max_over_ranks(ctx.timer_end())
+        barrier()
+        sustained = {"value": BATCH * NEW_TOKENS / (s_ms / 1e3), "unit": "tokens/s", "steps": NEW_TOKENS, "ms_per_step": s_ms / NEW_TOKENS,
+                     "clocks": s_sampler.stop() if rank == 0 else None}
 
     # ---- e2e: host ids in, host ids out, every step, through the public decode_step call
     h_in = np.zeros(BATCH, np.int32)
@@ -267,14 +287,16 @@ def run_ours(args, rank, world, local_rank):
         return
     if dist:
         barrier()
+    status = ctx.device_status()  # raises if a bounded device-side wait expired anywhere in the run
     base, _ = cpu_reference(2, 1) if world == 1 and not args.no_cpu else (None, None)
     line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 x fp8_e4m3 -> f32 (activations as two E4M3 terms on the FP8 tensor cores; bf16 KV)", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch": BATCH, "context": int(lens_now.mean()), "parallelism": f"tp{world}",
-                       "l2": "inputs larger than L2 (17.8 GB streamed per step)", "prefill_s": prefill_s, "prefill_device_s": prefill_dev_s, "cuda_graph": not args.no_graph,
-                       "layers": cfg["n_layers"], "kv": "synthetic" if args.synthetic_kv else "prefill of the seeded prompts"},
-            "roofline": roofline, "kernels": kernels, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks}
+            "config": dict(workload_config(world), layers=cfg["n_layers"]),
+            "setup": {"context": int(lens_now.mean()), "prefill_s": prefill_s, "prefill_device_s": prefill_dev_s, "prefill_clocks": prefill_clocks,
+                      "cuda_graph": not args.no_graph, "kv": "synthetic" if args.synthetic_kv else "prefill of the seeded prompts"},
+            "roofline": roofline, "kernels": kernels, "e2e": e2e, "sustained": sustained, "gpu_launches": int(launches), "clocks": clocks,
+            "device_status": status}
     if base:
         line["cpu_baseline"] = base
     sys.stdout.flush()
@@ -297,6 +319,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: run only this many of the 36 layers")
     ap.add_argument("--synthetic-kv", action="store_true", help="profiling aid: fill the cache with seeded values instead of the prefill")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the 256-step sustained leg")
+    ap.add_argument("--nccl-allreduce", action="store_true", help="decode all-reduces through NCCL instead of the fused peer-memory exchange")
+    ap.add_argument("--two-shot", type=int, default=-1, help="fused all-reduce: 0 one shot, 1 two shots (default: two from four ranks on)")
     ap.add_argument("--no-graph", action="store_true", help="plain launches instead of CUDA-graph replay of the decode step")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

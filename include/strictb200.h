@@ -66,10 +66,23 @@ int strictb200_timer_end(strictb200_ctx* ctx, float* ms_out);
 /* Number of kernels this context launched since creation (library kernels only). */
 int strictb200_launch_count(strictb200_ctx* ctx, uint64_t* out);
 /* Waits for the stream, then returns (and clears) the error word kernels set when one of their
- * bounded waits expired: 0 = none; non-zero also returns ERR_TIMEOUT. */
+ * bounded waits expired: 0 = none; non-zero also returns ERR_TIMEOUT. strictb200_prefill,
+ * _decode_step and _generate make the same check themselves after their own synchronise, so a
+ * rank that never arrived shows as ERR_TIMEOUT from the call, not as silently wrong tokens. */
 int strictb200_device_status(strictb200_ctx* ctx, int* out);
 /* Writes `bytes` to a private buffer (> L2) so the next kernel starts with a cold L2. */
 int strictb200_flush_l2(strictb200_ctx* ctx);
+/* Switches of a context. Each is read ONCE from the environment variable STRICTB200_<NAME IN
+ * CAPITALS> when the context is created; no launch path reads the environment. -1 = the
+ * library's own choice. Names: "pdl" (programmatic dependent launch, 1), "attn_tc" (prefill
+ * attention kernel: 0 mma.sync, 1 tcgen05 one query tile per block, 2 two tiles per block, -1),
+ * "gemm_pair" (many-token GEMM on SM pairs, 1), "prefetch" (1), "deep_ring" (1),
+ * "attn_blocks_per_sm" (0), "split_target" (0), "tp_two_shot" (fused all-reduce in two shots,
+ * -1: from four ranks on), "wait_limit" (polls of a cross-rank wait before it gives up,
+ * 4194304), "prefill_chunk" (token rows per prefill chunk, 16384). Unknown name -> ERR_INVALID_ARG.
+ * The reference has no counterpart (its one switch is a compile flag, Kernel.cs:43). */
+int strictb200_set_option(strictb200_ctx* ctx, const char* name, int value);
+int strictb200_get_option(strictb200_ctx* ctx, const char* name, int* out);
 
 /* ---- recorded call sequences. The reference launches one kernel per `kernel.Run` call
  * (Strict.Compiler.Cuda.Tests/CSharpToCudaTranspilerTests.cs:77,86) and has no counterpart of
@@ -100,6 +113,25 @@ int strictb200_ew_binary(strictb200_ctx* ctx, int op, const float* d_a, const fl
 int strictb200_ew_program(strictb200_ctx* ctx, const int32_t* h_code, int n_instr, const float* const* h_arrays,
                           int n_arrays, const float* h_scalars, int n_scalars, const float* h_consts, int n_consts,
                           float* d_out, int64_t count);
+
+/* ---- image workloads of the reference's samples ---- */
+/* 5x5 box blur over interleaved RGB bytes, d_src -> d_dst (two different buffers of
+ * width*height*3 bytes): what the reference's CPU harness computes
+ * (Strict.Compiler.Assembly.Tests/BlurPerformanceTests.cs:52-141 — sum/25 where all 25
+ * neighbours exist, sum/count of the neighbours inside the image at the edges, integer division
+ * per channel) and what its CUDA harness was meant to (its kernel is a byte copy,
+ * Strict.Compiler.Cuda.Tests/BlurPerformanceTests.cs:111-117). Bit-exact with the CPU form.
+ * Rows whose byte length is a multiple of 16 (width % 16 == 0) with 16-byte aligned buffers
+ * take the packed strip kernel; other images take the generic per-byte kernel. */
+int strictb200_blur5x5_rgb8(strictb200_ctx* ctx, const uint8_t* d_src, uint8_t* d_dst, int width, int height);
+/* AdjustBrightness (ImageProcessing/AdjustBrightness.strict:10,16) over the flat number layout of
+ * Strict.Expressions/ValueArrayInstance.cs:9-16,128,339: fp32 array of structs, element i member
+ * m at d_flat[offset + i*flat_width + m]; the first `channels` members of `count` elements get
+ * `brightness` added in place (Color: flat_width 4 = Red, Green, Blue, Alpha; channels 3). The
+ * sum is taken in double and stored as float, as the reference's VM does. clamp01 != 0 keeps
+ * results inside [0,1] (the range Color.strict allows; the .strict code does not clamp). */
+int strictb200_adjust_brightness(strictb200_ctx* ctx, float* d_flat, int64_t offset, int64_t count, int flat_width, int channels,
+                                 double brightness, int clamp01);
 
 /* ---- seeded generator (device side of the synthetic-tensor specification) ---- */
 int strictb200_gen_normal_f32(strictb200_ctx* ctx, uint64_t seed, uint64_t tensor, int64_t first, int64_t count, float std, float* d_out);
@@ -257,16 +289,36 @@ int strictb200_tp_unique_id(void* h_id128);
 /* Must be called before model_create on that context. world in {1,2,4,8}. */
 int strictb200_tp_init(strictb200_ctx* ctx, int world, int rank, const void* h_id128);
 int strictb200_tp_info(strictb200_ctx* ctx, int* world, int* rank);
-/* Optional one-shot all-reduce over peer memory for the decode step (messages of a few hundred KB,
- * where NCCL's launch latency dominates): after tp_init every rank asks for the 64-byte CUDA IPC
- * handle of its exchange buffer, the host gathers the handles of all ranks (rank order, world x 64
- * bytes) and hands them to every rank. From then on the decode step publishes each rank's fp32
- * partial projection in its buffer and the following row kernel sums the ranks' buffers with plain
- * peer loads over NVLink (bounded wait on epoch flags; ERR_TIMEOUT through device_status if a rank
- * never shows up). All ranks must be processes on one NVLink-connected box. Without these two
- * calls the decode step uses NCCL. */
+/* Optional all-reduce over peer memory for the decode step (messages of a few hundred KB, where
+ * NCCL's launch latency dominates): after tp_init every rank asks for the 64-byte CUDA IPC handle
+ * of its exchange buffer, the host gathers the handles of all ranks (rank order, world x 64 bytes)
+ * and hands them to every rank. From then on the all-reduce after o_proj and down_proj happens
+ * inside the residual/RMSNorm kernel that consumes the sum: the block of a token row adds the
+ * rank's own split-K partials, pushes every value into the peers' buffers over NVLink as an
+ * 8-byte packet {value, epoch} (plain stores; no multicast), polls its own buffer until the same
+ * row's packets of every peer carry the current epoch, and adds the ranks' values in rank order,
+ * so every rank computes bit-identical sums. With four or more ranks the exchange takes two
+ * shots: each column slice goes to the rank that owns it, which returns the finished sums.
+ * Every poll is bounded ("wait_limit"); if a rank never shows up the kernel sets the error word
+ * and the call that synchronises next returns ERR_TIMEOUT. All ranks must be processes on one
+ * NVLink-connected box. Batches that do not fit the buffers (more than 1M values per result)
+ * and contexts without these two calls use NCCL. */
 int strictb200_tp_comm_handle(strictb200_ctx* ctx, void* h_handle64);
 int strictb200_tp_comm_open(strictb200_ctx* ctx, const void* h_handles);
+/* The fused op by itself: out = RMSNorm(residual + sum over ranks of ((sum of this rank's
+ * `splits` partials [splits][M,d]) * sx[M] * sw[d])) * gain. d_residual_f32 (may be NULL) is
+ * updated in place; the normalised row is written as bf16 (d_y, may be NULL) and/or as the
+ * two-term E4M3 split with its scales (d_split + d_split_scale, may both be NULL). Every rank
+ * calls it with the same shapes, in the same order. Needs open peer buffers. */
+int strictb200_tp_allreduce_rownorm(strictb200_ctx* ctx, const float* d_part, int splits, const float* d_sx, const float* d_sw,
+                                    float* d_residual_f32, const float* d_gain, float eps, int64_t M, int64_t d, uint16_t* d_y,
+                                    uint8_t* d_split, float* d_split_scale);
+/* Failure injection on the host side, for tests of the bounded waits: sets the context up as
+ * rank 0 of `world` ranks whose peers are local buffers that nothing ever writes, i.e. ranks
+ * that never show up. No NCCL, no other process; only strictb200_tp_allreduce_rownorm may be
+ * used on such a context, and with a small "wait_limit" it returns its (meaningless) result
+ * quickly while strictb200_device_status reports ERR_TIMEOUT. Nothing faults or hangs. */
+int strictb200_tp_comm_open_absent_peers(strictb200_ctx* ctx, int world);
 /* fp32 sum all-reduce in place on the context's stream (the collective the model uses). */
 int strictb200_tp_allreduce_f32(strictb200_ctx* ctx, float* d_buf, int64_t count);
 

@@ -36,6 +36,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <string>
+#include <memory>
 #include <vector>
 
 #include "oracle_num.h"
@@ -43,6 +44,21 @@
 using namespace oracle;
 
 namespace {
+
+// Allocator for the multi-gigabyte buffers (weights, embedding, KV cache): resize() leaves the
+// elements untouched, so the first touch of every page is the parallel loop that fills it
+// instead of a serial zero-fill that a second pass then overwrites.
+template <class T>
+struct NoInit : std::allocator<T> {
+  template <class U> struct rebind { using other = NoInit<U>; };
+  template <class U, class... A>
+  void construct(U* p, A&&... a) {
+    if constexpr (sizeof...(A) == 0) ::new ((void*)p) U;
+    else ::new ((void*)p) U(std::forward<A>(a)...);
+  }
+};
+using BigF = std::vector<float, NoInit<float>>;
+using BigB = std::vector<uint8_t, NoInit<uint8_t>>;
 
 struct Config {
   int arch;  // 0 = GPT-2 (fp32 weights), 1 = Qwen3 (E4M3 weights)
@@ -209,7 +225,7 @@ void attend_one(const float* q, const float* k, const float* v, int len, int D, 
 
 struct QLinear {  // E4M3 weight [N,K] with per-row scale
   int64_t N = 0, K = 0;
-  std::vector<uint8_t> q;
+  BigB q;
   std::vector<float> s;
 };
 struct FLinear {  // fp32 weight [N,K] with bias
@@ -226,7 +242,7 @@ struct Layer {
 struct Model {
   Config c;
   std::vector<Layer> L;
-  std::vector<float> embed;  // Qwen: bf16 values held as fp32; GPT-2: fp32  [V,d]
+  BigF embed;  // Qwen: bf16 values held as fp32; GPT-2: fp32  [V,d]
   std::vector<float> wpe;    // GPT-2 [max_pos,d]
   std::vector<float> normf_g, normf_b;
   QLinear head;  // Qwen LM head (untied: own tensor; tied: quantised embedding)
@@ -235,7 +251,7 @@ struct Model {
 struct State {
   int B, maxlen;
   std::vector<int> len;
-  std::vector<float> k, v;  // [L][B][Hkv][maxlen][D]
+  BigF k, v;  // [L][B][Hkv][maxlen][D]
 };
 
 void gen_normal_rows(uint64_t key, int64_t rows, int64_t K, float std_, float* out) {
@@ -304,7 +320,12 @@ Model* model_create(const Config& c, uint64_t seed) {
     m->wpe.resize((size_t)c.max_pos * d);
     gen_normal_rows(stream_key(seed, G_WPE), c.max_pos, d, SD, m->wpe.data());
   } else {
-    for (auto& e : m->embed) e = round_bf16(e);
+    {
+      float* e = m->embed.data();
+      const int64_t n = (int64_t)m->embed.size();
+#pragma omp parallel for schedule(static)
+      for (int64_t i = 0; i < n; i++) e[i] = round_bf16(e[i]);
+    }
     if (c.tied) quant_head_from_embed(m);
     else {
       m->head.N = c.vocab; m->head.K = d;
@@ -354,7 +375,7 @@ void qlinear(const QLinear& w, const float* x, int64_t T, float* out) {
   gemm_q(eff.data(), sa.data(), w.q.data(), w.K, w.s.data(), T, w.N, w.K, out, w.N);
 }
 
-float* kv_at(std::vector<float>& buf, const Model* m, const State* st, int l, int b, int h) {
+float* kv_at(BigF& buf, const Model* m, const State* st, int l, int b, int h) {
   const Config& c = m->c;
   return buf.data() + ((((int64_t)l * st->B + b) * c.n_kv_heads + h) * st->maxlen) * c.head_dim;
 }
@@ -477,8 +498,8 @@ void forward(Model* m, State* st, const int* tokens, const int* n_new, int B, in
 struct NamedTensor { void* ptr; int64_t bytes; };
 
 NamedTensor find_tensor(Model* m, const std::string& name) {
-  auto F = [](std::vector<float>& v) { return NamedTensor{v.data(), (int64_t)v.size() * 4}; };
-  auto U = [](std::vector<uint8_t>& v) { return NamedTensor{v.data(), (int64_t)v.size()}; };
+  auto F = [](auto& v) { return NamedTensor{v.data(), (int64_t)v.size() * 4}; };
+  auto U = [](auto& v) { return NamedTensor{v.data(), (int64_t)v.size()}; };
   if (name == "embed") return F(m->embed);
   if (name == "wpe") return F(m->wpe);
   if (name == "normf.g") return F(m->normf_g);
@@ -683,12 +704,95 @@ void* or_state_create(void* mv, int B, int maxlen) {
   State* s = new State;
   s->B = B; s->maxlen = maxlen; s->len.assign(B, 0);
   size_t n = (size_t)m->c.n_layers * B * m->c.n_kv_heads * maxlen * m->c.head_dim;
-  s->k.assign(n, 0.f); s->v.assign(n, 0.f);
+  s->k.resize(n); s->v.resize(n);
+  float *kp = s->k.data(), *vp = s->v.data();
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < (int64_t)n; i++) { kp[i] = 0.f; vp[i] = 0.f; }
   return s;
 }
 void or_state_free(void* s) { delete (State*)s; }
 void or_state_reset(void* s) { State* st = (State*)s; std::fill(st->len.begin(), st->len.end(), 0); }
 void or_state_lens(void* s, int32_t* out) { State* st = (State*)s; for (int b = 0; b < st->B; b++) out[b] = st->len[b]; }
+// 5x5 box blur over interleaved RGB bytes, restating
+// Strict.Compiler.Assembly.Tests/BlurPerformanceTests.cs:52-141: a pixel with all 25 neighbours
+// inside the image (row and column in [2, size-2)) gets sum / 25 per channel (BlurInteriorPixel,
+// :85-120), any other pixel the sum of the neighbours that exist divided by their count
+// (BlurEdgePixel, :122-141); integer division, result written to a second buffer.
+void or_blur5x5_rgb8(const uint8_t* src, uint8_t* dst, int width, int height) {
+  const int64_t stride = (int64_t)width * 3;
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < height; row++)
+    for (int column = 0; column < width; column++) {
+      const int64_t base = row * stride + (int64_t)column * 3;
+      const bool interior = row >= 2 && row < height - 2 && column >= 2 && column < width - 2;
+      for (int channel = 0; channel < 3; channel++) {
+        if (interior) {
+          int sum = 0;
+          for (int ky = -2; ky <= 2; ky++)
+            for (int kx = -2; kx <= 2; kx++) sum += src[base + ky * stride + kx * 3 + channel];
+          dst[base + channel] = (uint8_t)(sum / 25);
+        } else {
+          int sum = 0, count = 0;
+          for (int ky = -2; ky <= 2; ky++)
+            for (int kx = -2; kx <= 2; kx++) {
+              const int nx = column + kx, ny = row + ky;
+              if ((unsigned)nx >= (unsigned)width || (unsigned)ny >= (unsigned)height) continue;
+              sum += src[ny * stride + (int64_t)nx * 3 + channel];
+              count++;
+            }
+          dst[base + channel] = (uint8_t)(sum / count);
+        }
+      }
+    }
+}
+// The reference's harness blurs in place, iteration after iteration (ApplyBlurSingleThread copies
+// its output over the input, :66): `iterations` passes, result in `pixels`.
+void or_blur5x5_rgb8_inplace(uint8_t* pixels, int width, int height, int iterations) {
+  std::vector<uint8_t> out((size_t)width * height * 3);
+  for (int it = 0; it < iterations; it++) {
+    or_blur5x5_rgb8(pixels, out.data(), width, height);
+    std::copy(out.begin(), out.end(), pixels);
+  }
+}
+// AdjustBrightness over the flat number layout of ValueArrayInstance (element i, member m at
+// offset + i*flat_width + m, fp32; Strict.Expressions/ValueArrayInstance.cs:128,339): the first
+// `channels` members of every element get `brightness` added
+// (ImageProcessing/AdjustBrightness.strict:16), in double as the VM computes
+// (Strict/VirtualMachine.Loops.cs:312-327), stored back as float
+// (ValueArrayInstance.cs:105). clamp01 keeps the result inside [0,1], the range Color.strict
+// allows; the .strict code itself does not clamp.
+void or_adjust_brightness(float* flat, int64_t offset, int64_t count, int flat_width, int channels, double brightness, int clamp01) {
+  for (int64_t i = 0; i < count; i++)
+    for (int m = 0; m < channels; m++) {
+      double s = (double)flat[offset + i * flat_width + m] + brightness;
+      if (clamp01) s = s < 0.0 ? 0.0 : (s > 1.0 ? 1.0 : s);
+      flat[offset + i * flat_width + m] = (float)s;
+    }
+}
+
+// Benchmark set-up only: positions [0,len) of every sequence get cheap pseudo-random values in
+// [-1,1) (a multiplicative hash of the element index; the values do not matter for timing) and
+// the lengths are set to len, so that a decode step at a long context can be timed without the
+// hours a CPU prefill of that context would take.
+int or_state_fill_synthetic(void* mv, void* sv, uint64_t seed, int len) {
+  Model* m = (Model*)mv;
+  State* st = (State*)sv;
+  if (len < 0 || len > st->maxlen) return 1;
+  const int64_t D = m->c.head_dim, rows = (int64_t)m->c.n_layers * st->B * m->c.n_kv_heads;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; r++) {
+    for (int which = 0; which < 2; which++) {
+      float* base = (which ? st->v.data() : st->k.data()) + r * st->maxlen * D;
+      uint64_t x = (seed + 1) * 0x9E3779B97F4A7C15ull + (uint64_t)(2 * r + which) * 0xD1B54A32D192ED03ull;
+      for (int64_t i = 0; i < (int64_t)len * D; i++) {
+        x = x * 6364136223846793005ull + 1442695040888963407ull;
+        base[i] = (float)(int32_t)(x >> 32) * (1.0f / 2147483648.0f);
+      }
+    }
+  }
+  std::fill(st->len.begin(), st->len.end(), len);
+  return 0;
+}
 int or_prefill(void* m, void* s, const int32_t* tokens, const int32_t* lens, int B, int S, float* logits) {
   State* st = (State*)s;
   for (int b = 0; b < B; b++) if (st->len[b] + lens[b] > st->maxlen || lens[b] > S) return 1;

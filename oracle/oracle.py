@@ -44,6 +44,7 @@ def lib():
         for f in (L.or_state_free, L.or_state_reset):
             f.argtypes = [C.c_void_p]
         L.or_state_lens.argtypes = [C.c_void_p, C.c_void_p]
+        L.or_state_fill_synthetic.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int]
         L.or_prefill.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         L.or_decode.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
     return _LIB
@@ -127,6 +128,22 @@ def ew_program(code, arrays, scalars, consts, n):
     out = np.empty(n, np.float32)
     if lib().or_ew_program(_p(code), C.c_int(len(code)), ptrs, _p(sc), _p(co), _p(out), C.c_int64(n)):
         raise NotImplementedError("opcode")
+    return out
+
+
+# ------------------------------------------------------------------ image workloads
+def blur5x5_rgb8(pixels, width, height, iterations=1):
+    """pixels uint8 [height*width*3]; returns the image after `iterations` in-place blur passes."""
+    px = np.array(pixels, dtype=np.uint8).reshape(-1).copy()
+    assert px.size == width * height * 3
+    lib().or_blur5x5_rgb8_inplace(_p(px), C.c_int(width), C.c_int(height), C.c_int(iterations))
+    return px
+
+
+def adjust_brightness(flat, offset, count, flat_width, channels, brightness, clamp01=False):
+    out = _f32(flat).reshape(-1).copy()
+    lib().or_adjust_brightness(_p(out), C.c_int64(offset), C.c_int64(count), C.c_int(flat_width), C.c_int(channels),
+                               C.c_double(brightness), C.c_int(1 if clamp01 else 0))
     return out
 
 
@@ -312,6 +329,11 @@ class State:
         if lib().or_decode(self.model.h, self.h, _p(ids), C.c_int(self.B), _p(logits)):
             raise ValueError("cache full")
         return logits
+
+    def fill_synthetic(self, seed, length):
+        """Benchmark set-up: cheap pseudo-random keys/values at positions [0,length)."""
+        if lib().or_state_fill_synthetic(self.model.h, self.h, C.c_uint64(seed), C.c_int(length)):
+            raise ValueError("length outside the cache")
 
     def lens(self):
         out = np.empty(self.B, np.int32)

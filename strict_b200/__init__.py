@@ -4,7 +4,7 @@ Importing the package does not load the native library; the first Context()/lib(
 and raises if the library has not been built or no B200 is present (there is no CPU path).
 """
 from .native import KernelException, lib, LIB_PATH  # noqa: F401
-from .kernel import Context, DeviceVariable, Kernel  # noqa: F401
+from .kernel import Context, DeviceVariable, FlatNumbers, Kernel, blur5x5_rgb8  # noqa: F401
 from .instructions_to_cuda import (CSharpToCudaTranspiler, CSharpType, InstructionsToCuda, InvalidCode, Method,  # noqa: F401
                                    MissingReturnStatement)
 from .model import CONFIGS, GPT2, QWEN3, KvCache, Model  # noqa: F401

@@ -1,4 +1,5 @@
 // Context, memory and op-level C entry points of libstrictb200.so.
+#include <cctype>
 #include <cstdlib>
 #include <cstring>
 #include <vector>
@@ -13,8 +14,45 @@ int sb_fail(int code, const std::string& msg) {
   return code;
 }
 
+namespace {
+struct OptionName { const char* name; int SbOptions::*field; };
+const OptionName kOptions[] = {
+    {"pdl", &SbOptions::pdl},
+    {"attn_tc", &SbOptions::attn_tc},
+    {"gemm_pair", &SbOptions::gemm_pair},
+    {"prefetch", &SbOptions::prefetch},
+    {"deep_ring", &SbOptions::deep_ring},
+    {"attn_blocks_per_sm", &SbOptions::attn_blocks_per_sm},
+    {"split_target", &SbOptions::split_target},
+    {"tp_two_shot", &SbOptions::tp_two_shot},
+    {"wait_limit", &SbOptions::wait_limit},
+    {"prefill_chunk", &SbOptions::prefill_chunk},
+};
+// STRICTB200_<NAME> of every option, read once, here
+void options_from_environment(SbOptions* o) {
+  for (const OptionName& n : kOptions) {
+    std::string env = "STRICTB200_";
+    for (const char* c = n.name; *c; c++) env += (char)toupper((unsigned char)*c);
+    if (const char* v = getenv(env.c_str())) o->*(n.field) = atoi(v);
+  }
+}
+}  // namespace
+
+// Reads and clears the error word the kernels of this context set when a bounded wait expired.
+// The stream must have been synchronised by the caller.
+int sb_check_status(strictb200_ctx* ctx, const char* what) {
+  const int code = *(volatile int*)ctx->h_status;
+  if (!code) return STRICTB200_OK;
+  *(volatile int*)ctx->h_status = 0;
+  // a GEMM block that gave up may have left its stream-K tile counters mid-count
+  if (ctx->gemm_ws && ctx->gemm_count_bytes) cudaMemsetAsync(ctx->gemm_ws, 0, ctx->gemm_count_bytes, ctx->stream);
+  return sb_fail(STRICTB200_ERR_TIMEOUT, std::string(what) + ": a bounded device-side wait expired (code " + std::to_string(code) +
+                                             "); the results of this call are not valid");
+}
+
 int sb_ws(strictb200_ctx* ctx, size_t bytes, void** out) {
   if (bytes > ctx->ws_bytes) {
+    ctx->ws_generation++;
     SB_CUDA(cudaStreamSynchronize(ctx->stream));
     if (ctx->ws) SB_CUDA(cudaFree(ctx->ws));
     ctx->ws = nullptr;
@@ -29,6 +67,7 @@ int sb_ws(strictb200_ctx* ctx, size_t bytes, void** out) {
 
 int sb_ws2(strictb200_ctx* ctx, size_t bytes, void** out) {
   if (bytes > ctx->ws2_bytes) {
+    ctx->ws_generation++;
     SB_CUDA(cudaStreamSynchronize(ctx->stream));
     if (ctx->ws2) SB_CUDA(cudaFree(ctx->ws2));
     ctx->ws2 = nullptr;
@@ -69,7 +108,7 @@ int strictb200_create(int device, strictb200_ctx** out) {
   strictb200_ctx* c = new strictb200_ctx;
   c->device = device;
   c->sm_count = prop.multiProcessorCount;
-  if (const char* e = getenv("STRICTB200_PDL")) c->pdl = atoi(e) != 0;
+  options_from_environment(&c->opt);
   SB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   SB_CUDA(cudaEventCreate(&c->ev0));
   SB_CUDA(cudaEventCreate(&c->ev1));
@@ -89,6 +128,7 @@ int strictb200_destroy(strictb200_ctx* ctx) {
   if (ctx->flush_buf) cudaFree(ctx->flush_buf);
   if (ctx->gemm_ws) cudaFree(ctx->gemm_ws);
   if (ctx->ws2) cudaFree(ctx->ws2);
+  if (ctx->prefill_ws) cudaFree(ctx->prefill_ws);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   cudaEventDestroy(ctx->ev0);
   cudaEventDestroy(ctx->ev1);
@@ -102,6 +142,7 @@ struct strictb200_graph {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   uint64_t launches = 0;  // kernels in the recorded sequence
+  uint64_t ws_generation = 0;  // the context's scratch generation the recorded pointers belong to
 };
 int strictb200_graph_begin(strictb200_ctx* ctx) {
   SB_ENTER(ctx);
@@ -123,6 +164,7 @@ int strictb200_graph_end(strictb200_ctx* ctx, strictb200_graph** out) {
   strictb200_graph* r = new strictb200_graph;
   r->graph = g;
   r->launches = recorded;
+  r->ws_generation = ctx->ws_generation;
   e = cudaGraphInstantiate(&r->exec, g, 0);
   if (e != cudaSuccess) {
     cudaGraphDestroy(g);
@@ -135,6 +177,9 @@ int strictb200_graph_end(strictb200_ctx* ctx, strictb200_graph** out) {
 int strictb200_graph_launch(strictb200_ctx* ctx, strictb200_graph* g, int times) {
   SB_ENTER(ctx);
   SB_REQUIRE(g && g->exec && times >= 0, "bad graph or repeat count");
+  if (g->ws_generation != ctx->ws_generation)
+    return sb_fail(STRICTB200_ERR_INVALID_ARG,
+                   "the context's scratch memory was re-allocated by a larger call after this sequence was recorded; record it again");
   for (int i = 0; i < times; i++) SB_CUDA(cudaGraphLaunch(g->exec, ctx->stream));
   ctx->launches += g->launches * (uint64_t)times;
   return STRICTB200_OK;
@@ -239,9 +284,25 @@ int strictb200_device_status(strictb200_ctx* ctx, int* out) {
   SB_REQUIRE(out, "null out pointer");
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
   *out = *(volatile int*)ctx->h_status;
-  *ctx->h_status = 0;
-  if (*out) return sb_fail(STRICTB200_ERR_TIMEOUT, "a bounded device-side wait expired (code " + std::to_string(*out) + ")");
-  return STRICTB200_OK;
+  return sb_check_status(ctx, "device_status");
+}
+int strictb200_set_option(strictb200_ctx* ctx, const char* name, int value) {
+  if (!ctx || !name) return sb_fail(STRICTB200_ERR_INVALID_ARG, "null argument");
+  for (const OptionName& n : kOptions)
+    if (!strcmp(n.name, name)) {
+      ctx->opt.*(n.field) = value;
+      return STRICTB200_OK;
+    }
+  return sb_fail(STRICTB200_ERR_INVALID_ARG, std::string("unknown option ") + name);
+}
+int strictb200_get_option(strictb200_ctx* ctx, const char* name, int* out) {
+  if (!ctx || !name || !out) return sb_fail(STRICTB200_ERR_INVALID_ARG, "null argument");
+  for (const OptionName& n : kOptions)
+    if (!strcmp(n.name, name)) {
+      *out = ctx->opt.*(n.field);
+      return STRICTB200_OK;
+    }
+  return sb_fail(STRICTB200_ERR_INVALID_ARG, std::string("unknown option ") + name);
 }
 int strictb200_flush_l2(strictb200_ctx* ctx) {
   SB_ENTER(ctx);

@@ -613,18 +613,13 @@ int k_attn_prefill(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf1
                    const int32_t* qstart, int B, int S, int64_t q_rows, int Hq, int Hkv, int Dh, int maxlen, float scale, bf16* out) {
   if (Dh != D) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: head_dim must be 128");
   // tcgen05 kernel first; the mma.sync kernel below takes what it declines
-  const char* tc_env = getenv("STRICTB200_ATTN_TC");  // read per call: the tests switch between the two kernels
-  const int use_tc = tc_env ? atoi(tc_env) : 1;
-  if (use_tc) {
+  if (ctx->opt.attn_tc != 0) {
     int st = k_attn_prefill_tc(ctx, q, kc, vc, lens, past, qstart, B, S, q_rows, Hq, Hkv, maxlen, scale, out);
     if (st != STRICTB200_ERR_UNSUPPORTED) return st;
   }
-  static bool attr = false;
+  static SbDeviceOnce once;
   size_t smem = 64 * 256 + 4 * KT * 256;
-  if (!attr) {
-    SB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = true;
-  }
+  SB_CUDA(once.run(ctx->device, [&] { return cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); }));
   if (Hq > 65535 || B > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: too many heads or sequences");
   dim3 grid((S + 63) / 64, Hq, B);
   attn_prefill_kernel<<<grid, 128, smem, ctx->stream>>>(q, kc, vc, lens, past, qstart, S, Hq, Hkv, maxlen, scale * LOG2E, out);
@@ -638,7 +633,7 @@ int k_attn_prefill(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf1
 // sizes that leave at most 8 chunks per sequence. STRICTB200_ATTN_BLOCKS_PER_SM restores the
 // plain "that many blocks per SM" rule.
 static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
-  static const int per_sm = getenv("STRICTB200_ATTN_BLOCKS_PER_SM") ? atoi(getenv("STRICTB200_ATTN_BLOCKS_PER_SM")) : 0;
+  const int per_sm = ctx->opt.attn_blocks_per_sm;
   const int tiles = (maxlen + KT - 1) / KT;
   if (per_sm > 0) {
     int64_t c = (int64_t)maxlen * B * Hkv / ((int64_t)ctx->sm_count * per_sm);
@@ -647,12 +642,17 @@ static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
     if (c > maxlen) c = (int64_t)tiles * KT;
     return (int)c;
   }
-  static int resident = 0;
-  if (!resident) {
-    const size_t smem = 2 * DEC_STAGES * KT * 256;
-    cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, attn_decode_kernel, 128, smem) != cudaSuccess || resident < 1) resident = 1;
-  }
+  static SbDeviceOnce once;
+  static int resident_of[64] = {};  // blocks of the kernel an SM holds, per device
+  const size_t smem_dec = 2 * DEC_STAGES * KT * 256;
+  once.run(ctx->device, [&] {
+    cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dec);
+    int r = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, attn_decode_kernel, 128, smem_dec) != cudaSuccess || r < 1) r = 1;
+    resident_of[ctx->device & 63] = r;
+    return cudaSuccess;
+  });
+  const int resident = resident_of[ctx->device & 63] > 0 ? resident_of[ctx->device & 63] : 1;
   const int64_t slots = (int64_t)ctx->sm_count * resident, pairs = (int64_t)B * Hkv;
   int best = tiles;
   double best_cost = 1e30;
@@ -677,12 +677,7 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
   if (Hq * (D / 8) > CB_THREADS * CB_ITEMS) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: at most 64 query heads per rank");
   int chunk = decode_chunk(ctx, B, Hkv, maxlen);
   if ((maxlen + chunk - 1) / chunk != nsplit) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: split count does not match the cache size");
-  static bool attr = false;
-  size_t smem = 2 * DEC_STAGES * KT * 256;  // K and V rings; also covers the 34 KB merge area
-  if (!attr) {
-    SB_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = true;
-  }
+  size_t smem = 2 * DEC_STAGES * KT * 256;  // K and V rings; also covers the 34 KB merge area (the attribute is set by decode_chunk above)
   float* o_part = scratch;
   float* ml_part = scratch + (size_t)B * Hq * nsplit * D;
   if (Hkv > 65535 || B > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: too many heads or sequences");
@@ -706,10 +701,16 @@ int k_attn_f32(strictb200_ctx* ctx, const float* qkv, float* kc, float* vc, cons
   const int threads = 256;
   size_t smem = ((size_t)((maxlen + 3) & ~3) + Dh + 4 * threads) * sizeof(float);
   if (smem > 200 * 1024) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: fp32 path supports at most ~50k positions");
-  static size_t attr_smem = 48 * 1024;
-  if (smem > attr_smem) {
-    SB_CUDA(cudaFuncSetAttribute(attn_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_smem = smem;
+  {
+    static std::mutex mu;
+    static size_t attr_smem[64] = {};  // largest size this device's kernel has been opened for
+    std::lock_guard<std::mutex> lock(mu);
+    size_t& have = attr_smem[ctx->device & 63];
+    if (have < 48 * 1024) have = 48 * 1024;
+    if (smem > have) {
+      SB_CUDA(cudaFuncSetAttribute(attn_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      have = smem;
+    }
   }
   if (T > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: too many rows for the fp32 path");
   // rows that are sequences of their own (decode) append inside the attention kernel; prompt rows

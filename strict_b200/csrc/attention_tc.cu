@@ -671,22 +671,15 @@ int k_attn_prefill_tc(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const 
   SB_TRY(make_map(&mk, kc, (int64_t)B * Hkv * maxlen, D, D));
   SB_TRY(make_map(&mv, vc, (int64_t)B * Hkv * maxlen, D, D));
   const size_t smem = 3 * TILE_BYTES + 1024;
-  static bool attr = false;
-  if (!attr) {
-    SB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = true;
-  }
+  static SbDeviceOnce once;
+  SB_CUDA(once.run(ctx->device, [&] { return cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); }));
   TcAttnArgs a{lens, past, qstart, S, Hq, Hkv, maxlen, scale * LOG2E, out, ctx->d_status};
-  // two query tiles per block (ping-pong) from 256 new tokens per sequence on; STRICTB200_ATTN_TC=1 / 2 forces a kernel
-  const char* mode = getenv("STRICTB200_ATTN_TC");
-  const int forced = mode ? atoi(mode) : 0;
+  // two query tiles per block (ping-pong) from 256 new tokens per sequence on; the attn_tc option (1 / 2) forces a kernel
+  const int forced = ctx->opt.attn_tc;
   if (forced == 2 || (forced != 1 && S >= 2 * BQ)) {
     const size_t smem2 = 6 * TILE_BYTES + 1024;
-    static bool attr2 = false;
-    if (!attr2) {
-      SB_CUDA(cudaFuncSetAttribute(attn_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
-      attr2 = true;
-    }
+    static SbDeviceOnce once2;
+    SB_CUDA(once2.run(ctx->device, [&] { return cudaFuncSetAttribute(attn_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2); }));
     dim3 grid2((unsigned)((S + 2 * BQ - 1) / (2 * BQ)), (unsigned)Hq, (unsigned)B);
     attn_prefill_tc2_kernel<<<grid2, TC2_THREADS, smem2, ctx->stream>>>(mq, mk, mv, a);
     SB_LAUNCHED(ctx);

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
 #include <string>
 #include <utility>
 
@@ -13,10 +14,16 @@
 
 struct TpState;     // tp.cpp
 
-// One-shot all-reduce over peer memory (tp.cpp): every rank owns a buffer that all ranks of the
-// box map (CUDA IPC); a rank publishes its fp32 partial result in its own buffer and raises an
-// epoch flag in every peer's buffer, the consumer kernel waits (bounded) for all flags and adds the
-// ranks' data in rank order with plain peer loads. Passed to kernels by value.
+// All-reduce over peer memory (tp.cpp): every rank owns a buffer that all ranks of the box map
+// (CUDA IPC). Passed to kernels by value. Two exchanges use it:
+//   row-granular (the decode step's default): the row kernel that consumes the sum pushes each of
+//     its values into the peers' buffers as an 8-byte packet {value, epoch} and polls its own
+//     buffer until the packets of every peer carry the row's current epoch (row_data, row_epoch);
+//   whole-result (shapes the row exchange does not take): a publish kernel writes the rank's fp32
+//     partial result into its own buffer and raises an epoch flag in every peer's buffer; the
+//     consumer waits for all flags and adds the ranks' data in rank order with plain peer loads
+//     (data, flags, epoch, done).
+// Every wait is bounded by wait_limit polls; on expiry the kernel sets *status and goes on.
 struct TpCommDev {
   float* data[8];   // rank r's data area, two epoch parities of max_elems floats each
   int* flags[8];    // rank r's flag area: flags[parity * 8 + source rank] = last epoch published
@@ -32,8 +39,42 @@ struct TpCommDev {
   int* row_epoch;       // this rank's per-row epoch counters (device memory, one writer per row)
   long long row_elems;  // values per (parity, source rank)
   int max_rows;
+  unsigned wait_limit;  // polls before a wait gives up (the context's wait_limit option, copied at launch)
 };
 struct SbProfiler;  // model.cu
+
+// Switches of a context. Each is read once from the environment (STRICTB200_<NAME IN CAPITALS>)
+// when the context is created and can be changed afterwards with strictb200_set_option; no
+// launch path reads the environment. -1 stands for the library's own choice.
+struct SbOptions {
+  int pdl = 1;                 // launch the decode-path kernels with programmatic dependent launch
+  int attn_tc = -1;            // prefill attention: 0 mma.sync, 1 tcgen05 one query tile per block, 2 two tiles per block
+  int gemm_pair = 1;           // many-token GEMM on SM pairs (0: the one-SM persistent kernel)
+  int prefetch = 1;            // GEMMs request their first ring of weight tiles before the dependency wait
+  int deep_ring = 1;           // few-token GEMM: a ring that fills the SM when the grid is one block per SM
+  int attn_blocks_per_sm = 0;  // >0: size decode-attention key chunks for that many blocks per SM
+  int split_target = 0;        // >0: blocks a few-token GEMM's K splits aim at
+  int tp_two_shot = -1;        // fused all-reduce: 0 one shot, 1 two shots
+  int wait_limit = 1 << 22;    // polls of a cross-rank wait before the kernel gives up and sets the error word
+  int prefill_chunk = 16384;   // token rows per prefill chunk
+};
+
+// One-time set-up that belongs to a device (function attributes are set per device): run(device, f)
+// calls f the first time it is reached for that device, under a lock, and again on a later call
+// if it failed. Contexts on different devices, driven from different threads, each get their turn.
+struct SbDeviceOnce {
+  std::mutex mu;
+  bool done[64] = {};
+  template <typename F>
+  cudaError_t run(int device, F&& f) {
+    if (device < 0 || device >= 64) return f();
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[device]) return cudaSuccess;
+    cudaError_t e = f();
+    if (e == cudaSuccess) done[device] = true;
+    return e;
+  }
+};
 
 struct strictb200_ctx {
   int device = 0;
@@ -56,11 +97,16 @@ struct strictb200_ctx {
   int* d_status = nullptr;
   void* gemm_ws = nullptr;  // stream-K tile counters + partial tiles of the tensor-memory GEMM
   size_t gemm_count_bytes = 0, gemm_part_bytes = 0;
-  int pdl = 1;  // launch the decode-path kernels with programmatic dependent launch
+  SbOptions opt;
+  // scratch of the prefill chunks (activations of up to opt.prefill_chunk token rows), grow-only
+  void* prefill_ws = nullptr;
+  size_t prefill_ws_bytes = 0;
+  uint64_t ws_generation = 0;  // advanced whenever a scratch buffer is re-allocated (recorded sequences check it)
 };
 
 void sb_set_error(const std::string& msg);
 int sb_fail(int code, const std::string& msg);
+int sb_check_status(strictb200_ctx* ctx, const char* what);  // after a stream synchronise: ERR_TIMEOUT if a kernel's wait expired
 int sb_ws(strictb200_ctx* ctx, size_t bytes, void** out);  // grow-only context scratch
 int sb_ws2(strictb200_ctx* ctx, size_t bytes, void** out);  // a second one, for calls that already hold the first
 
@@ -221,6 +267,8 @@ int k_f32_to_bf16(strictb200_ctx*, const float* x, int64_t n, bf16* y);
 int k_bf16_to_f32(strictb200_ctx*, const bf16* x, int64_t n, float* y);
 // tp.cpp
 const TpCommDev* sb_tp_comm(strictb200_ctx*);  // null unless the peer buffers were opened
+bool sb_tp_comm_fits(strictb200_ctx*, int64_t M, int64_t d);  // the peer-memory all-reduce takes an [M,d] result
+bool sb_tp_row_exchange_ok(strictb200_ctx*, int64_t M, int64_t d);  // ... with the row-granular exchange (one row width per context)
 // out[m,n] = (sum_s part[s][m,n]) * sx[m] * sw[n] written to this rank's peer buffer, then published
 int k_tp_publish(strictb200_ctx*, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N);
 int sb_tp_allreduce_f32(strictb200_ctx*, float* buf, int64_t count);
@@ -256,7 +304,7 @@ inline cudaError_t sb_launch(strictb200_ctx* ctx, void (*kernel)(KArgs...), dim3
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  cfg.numAttrs = ctx->opt.pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 // Same, as thread-block clusters of `cluster` blocks (the grid must be a multiple of it).
@@ -275,7 +323,7 @@ inline cudaError_t sb_launch_cluster(strictb200_ctx* ctx, void (*kernel)(KArgs..
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = ctx->pdl ? 2 : 1;
+  cfg.numAttrs = ctx->opt.pdl ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 // One-value-per-block exchange inside a thread-block cluster of at most 8 blocks: every block

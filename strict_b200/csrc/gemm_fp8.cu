@@ -250,11 +250,8 @@ int launch_skinny(strictb200_ctx* ctx, const GemmDev& d) {
   if (kc_max > Ks) kc_max = (Ks + 64 * SK_PF - 1) / (64 * SK_PF) * (64 * SK_PF);
   int stride = (kc_max % 128 == 0) ? kc_max + 64 : kc_max;
   size_t smem = (size_t)MP * stride;
-  static bool attr_set[9] = {false};
-  if (!attr_set[NT]) {
-    SB_CUDA(cudaFuncSetAttribute(gemm_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-    attr_set[NT] = true;
-  }
+  static SbDeviceOnce once;  // one per instantiation
+  SB_CUDA(once.run(ctx->device, [&] { return cudaFuncSetAttribute(gemm_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); }));
   dim3 grid((d.N + SK_ROWS - 1) / SK_ROWS, d.splits);
   gemm_skinny_kernel<NT><<<grid, SK_WARPS * 32, smem, ctx->stream>>>(d, kc_max);
   SB_LAUNCHED(ctx);
@@ -276,7 +273,7 @@ int sb_gemm_pick_splits(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K) {
   // About 1.6 blocks per SM (two blocks of this kernel fit an SM, so all of them are resident
   // at once and share its bandwidth) measured best on the decode shapes; more than 8 partial
   // results are not taken by the kernels that sum them.
-  static int target = getenv("STRICTB200_SPLIT_TARGET") ? atoi(getenv("STRICTB200_SPLIT_TARGET")) : 0;
+  const int target = ctx->opt.split_target;
   const int64_t want = target ? target : (int64_t)ctx->sm_count * 13 / 8;
   int64_t s = (want + tiles - 1) / tiles;
   while (s > 1 && tiles * s > 2 * (int64_t)ctx->sm_count) s--;
@@ -306,12 +303,9 @@ int k_gemm_fp8(strictb200_ctx* ctx, const GemmArgs& g) {
     if (g.M <= 16) return launch_skinny<4>(ctx, d);
     return launch_skinny<8>(ctx, d);
   }
-  static bool attr = false;
+  static SbDeviceOnce once;
   size_t smem = (size_t)TL_STAGES * (TL_BN + TL_BM) * 64;
-  if (!attr) {
-    SB_CUDA(cudaFuncSetAttribute(gemm_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = true;
-  }
+  SB_CUDA(once.run(ctx->device, [&] { return cudaFuncSetAttribute(gemm_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); }));
   dim3 grid((unsigned)((g.N + TL_BN - 1) / TL_BN), (unsigned)((d.Mq + TL_BM - 1) / TL_BM), g.splits);
   if (grid.y > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: M too large for the tile kernel");
   gemm_tiles_kernel<<<grid, 256, smem, ctx->stream>>>(d);

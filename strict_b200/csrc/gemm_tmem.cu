@@ -373,6 +373,7 @@ int gemm_workspace(strictb200_ctx* ctx, size_t count_bytes, size_t part_bytes, i
   count_bytes = (count_bytes + 255) & ~(size_t)255;
   if (count_bytes > ctx->gemm_count_bytes || part_bytes > ctx->gemm_part_bytes) {
     SB_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->ws_generation++;
     if (ctx->gemm_ws) SB_CUDA(cudaFree(ctx->gemm_ws));
     ctx->gemm_ws = nullptr;
     size_t cb = count_bytes > ctx->gemm_count_bytes ? count_bytes * 2 : ctx->gemm_count_bytes;
@@ -392,11 +393,8 @@ template <int BT, int STAGES>
 int launch(strictb200_ctx* ctx, const GemmArgs& g, TmemArgs ta) {
   constexpr int STAGE_BYTES = BN * BK + BT * BK;
   size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;  // + slack for the 1024-byte round-up
-  static bool attr = false;
-  if (!attr) {
-    SB_CUDA(cudaFuncSetAttribute(gemm_tmem_kernel<BT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = true;
-  }
+  static SbDeviceOnce once;  // one per instantiation
+  SB_CUDA(once.run(ctx->device, [&] { return cudaFuncSetAttribute(gemm_tmem_kernel<BT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); }));
   CUtensorMap mw, mx;
   SB_TRY(make_map(&mw, g.wq, g.N, g.K, g.ldw, BN));
   SB_TRY(make_map(&mx, g.xq, ta.Mq, g.K, g.ldx, BT));
@@ -425,11 +423,9 @@ int k_gemm_fp8_tmem(strictb200_ctx* ctx, const GemmArgs& g) {
   if (((uintptr_t)g.xq | (uintptr_t)g.wq | (uintptr_t)g.ldx | (uintptr_t)g.ldw) & 15)
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: operands and row strides must be 16-byte aligned");
   // many tokens: two SMs per 256 x 256 tile (half the operand bytes per flop through each SM)
-  const char* pair_env = getenv("STRICTB200_GEMM_PAIR");  // read per call: the tests switch between the two kernels
-  const int pair = pair_env ? atoi(pair_env) : 1;
-  if (pair && g.N >= 256 && ctx->sm_count >= 2) return k_gemm_fp8_tmem_pair(ctx, g);
+  if (ctx->opt.gemm_pair && g.N >= 256 && ctx->sm_count >= 2) return k_gemm_fp8_tmem_pair(ctx, g);
   SB_TRY(get_encode());
-  static const int prefetch = getenv("STRICTB200_PREFETCH") ? atoi(getenv("STRICTB200_PREFETCH")) : 1;
+  const int prefetch = ctx->opt.prefetch;
   TmemArgs ta{};
   ta.M = (int)g.M; ta.Mq = (int)sb_qrows(g.M); ta.N = (int)g.N; ta.K = (int)g.K;
   ta.sx = g.sx; ta.sw = g.sw; ta.out = g.out; ta.out_f32 = g.out_f32; ta.status = ctx->d_status; ta.prefetch = prefetch;

@@ -296,11 +296,8 @@ int k_gemm_fp8_tmem_pair(strictb200_ctx* ctx, const GemmArgs& g) {
   const int64_t tiles_n = (g.N + 2 * BN - 1) / (2 * BN), tiles_t = (Mq + 2 * BTH - 1) / (2 * BTH), tiles = tiles_n * tiles_t;
   if (tiles > INT32_MAX / 2) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: too many output tiles");
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;  // + slack for the 1024-byte round-up
-  static bool attr = false;
-  if (!attr) {
-    SB_CUDA(cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = true;
-  }
+  static SbDeviceOnce once;
+  SB_CUDA(once.run(ctx->device, [&] { return cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); }));
   CUtensorMap mw, mx;
   SB_TRY(make_map(&mw, g.wq, g.N, g.K, g.ldw));
   SB_TRY(make_map(&mx, g.xq, Mq, g.K, g.ldx));

@@ -259,11 +259,8 @@ template <int BT, int STAGES>
 int launch(strictb200_ctx* ctx, const GemmArgs& g, const TmemArgs& ta) {
   constexpr int STAGE_BYTES = BN * BK + BT * BK;
   size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;  // + slack for the 1024-byte round-up
-  static bool attr = false;
-  if (!attr) {
-    SB_CUDA(cudaFuncSetAttribute(gemm_tmem_kernel<BT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = true;
-  }
+  static SbDeviceOnce once;  // one per instantiation
+  SB_CUDA(once.run(ctx->device, [&] { return cudaFuncSetAttribute(gemm_tmem_kernel<BT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); }));
   CUtensorMap mw, mx;
   SB_TRY(make_map(&mw, g.wq, g.N, g.K, g.ldw, BN));
   SB_TRY(make_map(&mx, g.xq, ta.Mq, g.K, g.ldx, BT));
@@ -283,13 +280,13 @@ int k_gemm_fp8_tmem_split(strictb200_ctx* ctx, const GemmArgs& g) {
     return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: operands and row strides must be 16-byte aligned");
   if ((g.splits > 1 || g.raw) && !g.part) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: split-K needs a partial buffer");
   SB_TRY(get_encode());
-  TmemArgs ta{(int)g.M, (int)sb_qrows(g.M), (int)g.N, (int)g.K, g.sx, g.sw, g.out, g.out_f32, g.part, g.splits, g.raw, ctx->d_status, getenv("STRICTB200_PREFETCH") ? atoi(getenv("STRICTB200_PREFETCH")) : 1};
+  TmemArgs ta{(int)g.M, (int)sb_qrows(g.M), (int)g.N, (int)g.K, g.sx, g.sw, g.out, g.out_f32, g.part, g.splits, g.raw, ctx->d_status, ctx->opt.prefetch};
   // BT = operand rows per block = the whole (split) batch
   // A grid of at most one block per SM gets a ring that fills the SM's shared memory (the whole
   // ring of weight tiles is in flight before the dependency wait); larger grids keep two blocks
   // per SM resident.
   const int64_t blocks = ((g.N + BN - 1) / BN) * g.splits;
-  static const int deep = getenv("STRICTB200_DEEP_RING") ? atoi(getenv("STRICTB200_DEEP_RING")) : 1;
+  const int deep = ctx->opt.deep_ring;
   if (ta.Mq <= 32) return deep && blocks <= ctx->sm_count ? launch<32, 10>(ctx, g, ta) : launch<32, 5>(ctx, g, ta);
   if (ta.Mq <= 64) return deep && blocks <= ctx->sm_count ? launch<64, 9>(ctx, g, ta) : launch<64, 4>(ctx, g, ta);
   if (ta.Mq <= 128) return launch<128, 4>(ctx, g, ta);

@@ -251,13 +251,12 @@ int head_and_pick(strictb200_model* m, int64_t M, const uint8_t* aq, const float
   SB_LAUNCHED(ctx);
   if (h_logits) {
     SB_TRY(sb_tp_allgather(ctx, b.logits, b.logits_all, M * m->V_l * 4));
-    float* tmp;
-    SB_CUDA(cudaMalloc((void**)&tmp, (size_t)m->world * M * m->V_l * 4));
-    interleave_logits_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(b.logits_all, m->world, (int)M, m->V_l, tmp);
+    void* tmp;  // grow-only context scratch: no allocation once it has reached this size
+    SB_TRY(sb_ws2(ctx, (size_t)m->world * M * m->V_l * 4, &tmp));
+    interleave_logits_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(b.logits_all, m->world, (int)M, m->V_l, (float*)tmp);
     SB_LAUNCHED(ctx);
     SB_CUDA(cudaMemcpyAsync(h_logits, tmp, (size_t)m->world * M * m->V_l * 4, cudaMemcpyDeviceToHost, ctx->stream));
     SB_CUDA(cudaStreamSynchronize(ctx->stream));
-    SB_CUDA(cudaFree(tmp));
   }
   return STRICTB200_OK;
 }
@@ -332,8 +331,8 @@ int qwen_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
     PROF(STRICTB200_K_GEMM_O, run_gemm(m, B, w.wo, b.aq, b.sa, nullptr, 0, b.part, s2, 1));
     {
       RowNormArgs a;
-      if (tp && sb_tp_comm(ctx)) {
-        // one-shot all-reduce over peer memory inside the row kernel that consumes it
+      if (tp && sb_tp_comm_fits(ctx, B, d)) {
+        // all-reduce over peer memory inside the row kernel that consumes it (NCCL below when the batch does not fit the peer buffers)
         a.comm = sb_tp_comm(ctx);
         a.part = b.part; a.splits = s2; a.sx = b.sa; a.sw = w.wo.s;
       } else if (tp) {
@@ -361,7 +360,7 @@ int qwen_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
     PROF(STRICTB200_K_GEMM_DOWN, run_gemm(m, B, w.wdown, b.aq, b.sa, nullptr, 0, b.part, s4, 1));
     {
       RowNormArgs a;
-      if (tp && sb_tp_comm(ctx)) {
+      if (tp && sb_tp_comm_fits(ctx, B, d)) {
         a.comm = sb_tp_comm(ctx);
         a.part = b.part; a.splits = s4; a.sx = b.sa; a.sw = w.wdown.s;
       } else if (tp) {
@@ -457,46 +456,80 @@ int decode_enqueue(strictb200_model* m, strictb200_kv* kv) {
 }
 
 // ------------------------------------------------------------------ prefill
-struct ChunkBufs {
-  std::vector<void*> ptrs;
-  strictb200_ctx* ctx;
-  ~ChunkBufs() {
-    cudaStreamSynchronize(ctx->stream);
-    for (void* p : ptrs) cudaFree(p);
+// Activations and index arrays of a prefill chunk are carved out of one grow-only scratch
+// buffer of the context: after the first prompt of a given size no prefill allocates.
+int prefill_scratch(strictb200_ctx* ctx, size_t bytes, char** out) {
+  if (bytes > ctx->prefill_ws_bytes) {
+    SB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->prefill_ws) SB_CUDA(cudaFree(ctx->prefill_ws));
+    ctx->prefill_ws = nullptr;
+    ctx->prefill_ws_bytes = 0;
+    SB_CUDA(cudaMalloc(&ctx->prefill_ws, bytes));
+    ctx->prefill_ws_bytes = bytes;
   }
-  template <typename T>
-  int get(T** p, size_t count) {
-    void* v;
-    SB_CUDA(cudaMalloc(&v, std::max<size_t>(count, 1) * sizeof(T)));
-    ptrs.push_back(v);
-    *p = (T*)v;
-    return STRICTB200_OK;
-  }
+  *out = (char*)ctx->prefill_ws;
+  return STRICTB200_OK;
+}
+struct ChunkIdx {
+  int32_t *tok, *seq, *pos, *la, *past, *qs, *last;
 };
+void carve_idx(Carver& cv, int64_t T, int nb, ChunkIdx* o) {
+  o->tok = cv.take<int32_t>(T); o->seq = cv.take<int32_t>(T); o->pos = cv.take<int32_t>(T);
+  o->la = cv.take<int32_t>(nb); o->past = cv.take<int32_t>(nb); o->qs = cv.take<int32_t>(nb); o->last = cv.take<int32_t>(nb);
+}
+struct QwenChunk {
+  float *x, *qkv, *gu, *y, *sa, *last;
+  bf16 *qb, *att;
+  uint8_t* aq;
+  DecBuf hb;
+};
+void carve_qwen_chunk(strictb200_model* m, Carver& cv, int64_t T, int nb, QwenChunk* o) {
+  const int64_t d = m->c.d_model, D = m->c.head_dim;
+  const int64_t nq = (int64_t)m->Hq_l * D, nqkv = nq + 2 * (int64_t)m->Hkv_l * D;
+  const int64_t amax = std::max<int64_t>(d, std::max<int64_t>(nq, m->I_l));
+  o->x = cv.take<float>(T * d);
+  o->qkv = cv.take<float>(T * nqkv);
+  o->qb = cv.take<bf16>(T * nq);
+  o->att = cv.take<bf16>(T * nq);
+  o->gu = cv.take<float>(T * 2 * m->I_l);
+  o->y = cv.take<float>(T * d);
+  o->aq = cv.take<uint8_t>(sb_qrows(T) * amax);
+  o->sa = cv.take<float>(T);
+  o->last = cv.take<float>((size_t)nb * d);
+  o->hb = DecBuf{};
+  o->hb.logits = cv.take<float>((size_t)nb * m->V_l);
+  o->hb.logits_all = cv.take<float>(m->world > 1 ? (size_t)m->world * nb * m->V_l : 1);
+  o->hb.best_val = cv.take<float>((size_t)m->world * nb);
+  o->hb.best_idx = cv.take<int32_t>((size_t)m->world * nb);
+  o->hb.am_ws = cv.take<uint8_t>(sb_argmax_scratch(nb, m->V_l));
+}
+struct Gpt2Chunk {
+  float *xf, *af, *bf_, *last, *lastn, *logits;
+  void* am_ws;
+};
+void carve_gpt2_chunk(strictb200_model* m, Carver& cv, int64_t T, int nb, Gpt2Chunk* o) {
+  const int64_t d = m->c.d_model, wd = std::max<int64_t>(3 * d, m->c.d_ff);
+  o->xf = cv.take<float>(T * d);
+  o->af = cv.take<float>(T * wd);
+  o->bf_ = cv.take<float>(T * wd);
+  o->last = cv.take<float>((size_t)nb * d);
+  o->lastn = cv.take<float>((size_t)nb * d);
+  o->logits = cv.take<float>((size_t)nb * m->c.vocab);
+  o->am_ws = cv.take<uint8_t>(sb_argmax_scratch(nb, m->c.vocab));
+}
 
 int qwen_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb, const int32_t* d_tok, const int32_t* d_seq,
                        const int32_t* d_pos, const int32_t* d_lens_after, const int32_t* d_past, const int32_t* d_qstart,
-                       const int32_t* d_last_rows, int b0, int32_t* d_next, float* h_logits, int max_new) {
+                       const int32_t* d_last_rows, int b0, int32_t* d_next, float* h_logits, int max_new, QwenChunk& cb) {
   strictb200_ctx* ctx = m->ctx;
   const auto& c = m->c;
   const int64_t d = c.d_model, D = c.head_dim;
-  const int64_t nq = (int64_t)m->Hq_l * D, nqkv = nq + 2 * (int64_t)m->Hkv_l * D;
+  const int64_t nq = (int64_t)m->Hq_l * D;
   const float scale = 1.0f / sqrtf((float)D);
   const bool tp = m->world > 1;
-  ChunkBufs cb;
-  cb.ctx = ctx;
-  bf16 *qb, *att;
-  uint8_t* aq;
-  float *x, *y, *sa, *qkv, *gu;
-  int64_t amax = std::max<int64_t>(d, std::max<int64_t>(nq, m->I_l));
-  SB_TRY(cb.get(&x, T * d));
-  SB_TRY(cb.get(&qkv, T * nqkv));
-  SB_TRY(cb.get(&qb, T * nq));
-  SB_TRY(cb.get(&att, T * nq));
-  SB_TRY(cb.get(&gu, T * 2 * m->I_l));
-  SB_TRY(cb.get(&y, T * d));
-  SB_TRY(cb.get(&aq, sb_qrows(T) * amax));
-  SB_TRY(cb.get(&sa, T));
+  bf16 *qb = cb.qb, *att = cb.att;
+  uint8_t* aq = cb.aq;
+  float *x = cb.x, *y = cb.y, *sa = cb.sa, *qkv = cb.qkv, *gu = cb.gu;
   SB_TRY(k_embedding_bf16_f32(ctx, m->embed, d_tok, T, d, c.vocab, x));
   {
     RowNormArgs a;
@@ -540,46 +573,30 @@ int qwen_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb
     }
   }
   // last real row of every sequence -> final norm -> head -> greedy pick
-  float* last;
-  SB_TRY(cb.get(&last, (size_t)nb * d));
+  float* last = cb.last;
   SB_TRY(k_gather_rows(ctx, x, d_last_rows, nb, d * 4, last));
   {
     RowNormArgs a;
     a.x_f32 = last; a.gain = m->normf_g; a.eps = c.eps; a.q = aq; a.qscale = sa;
     SB_TRY(k_rownorm(ctx, a, nb, d));
   }
-  DecBuf hb{};
-  SB_TRY(cb.get(&hb.logits, (size_t)nb * m->V_l));
-  SB_TRY(cb.get(&hb.logits_all, m->world > 1 ? (size_t)m->world * nb * m->V_l : 1));
-  SB_TRY(cb.get(&hb.best_val, (size_t)m->world * nb));
-  SB_TRY(cb.get(&hb.best_idx, (size_t)m->world * nb));
-  SB_TRY(cb.get((uint8_t**)&hb.am_ws, sb_argmax_scratch(nb, m->V_l)));
-  SB_TRY(head_and_pick(m, nb, aq, sa, hb, d_next, h_logits, nb));
+  SB_TRY(head_and_pick(m, nb, aq, sa, cb.hb, d_next, h_logits, nb));
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
   return STRICTB200_OK;
 }
 
 int gpt2_prefill_chunk(strictb200_model* m, strictb200_kv* kv, int64_t T, int nb, const int32_t* d_tok, const int32_t* d_seq,
-                       const int32_t* d_pos, const int32_t* d_last_rows, int32_t* d_next, float* h_logits) {
+                       const int32_t* d_pos, const int32_t* d_last_rows, int32_t* d_next, float* h_logits, Gpt2Chunk& cb) {
   strictb200_ctx* ctx = m->ctx;
   const auto& c = m->c;
   const int64_t d = c.d_model;
-  ChunkBufs cb;
-  cb.ctx = ctx;
-  int64_t wd = std::max<int64_t>(3 * d, c.d_ff);
-  float *xf, *af, *bf_, *last, *lastn, *logits;
-  SB_TRY(cb.get(&xf, T * d));
-  SB_TRY(cb.get(&af, T * wd));
-  SB_TRY(cb.get(&bf_, T * wd));
-  SB_TRY(cb.get(&last, (size_t)nb * d));
-  SB_TRY(cb.get(&lastn, (size_t)nb * d));
-  SB_TRY(cb.get(&logits, (size_t)nb * c.vocab));
+  float *xf = cb.xf, *af = cb.af, *bf_ = cb.bf_, *last = cb.last, *lastn = cb.lastn, *logits = cb.logits;
   SB_TRY(k_embedding_f32(ctx, m->wte, m->wpe, d_tok, d_pos, nullptr, T, d, c.vocab, c.max_pos, xf));
   SB_TRY(gpt2_layers(m, kv, T, xf, af, bf_, d_seq, d_pos));
   SB_TRY(k_gather_rows(ctx, xf, d_last_rows, nb, d * 4, last));
   SB_TRY(k_layernorm(ctx, last, m->normf_g, m->normf_b, c.eps, nb, d, lastn));
   SB_TRY(k_gemm_f32(ctx, nb, c.vocab, d, lastn, m->wte, nullptr, logits, 0));
-  SB_TRY(k_argmax(ctx, logits, nb, c.vocab, c.vocab, d_next, nullptr, nullptr));
+  SB_TRY(k_argmax(ctx, logits, nb, c.vocab, c.vocab, d_next, nullptr, cb.am_ws));
   if (h_logits) SB_CUDA(cudaMemcpyAsync(h_logits, logits, (size_t)nb * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
   return STRICTB200_OK;
@@ -990,12 +1007,9 @@ int strictb200_prefill(strictb200_model* m, strictb200_kv* kv, const int32_t* h_
     for (int i = 0; i < h_lens[b]; i++)
       SB_REQUIRE(h_tokens[(size_t)b * S + i] >= 0 && h_tokens[(size_t)b * S + i] < c.vocab, "token id outside the vocabulary");
   }
-  const int64_t MAX_T = 16384;  // token rows per chunk (bounds the activation scratch)
+  const int64_t MAX_T = ctx->opt.prefill_chunk > 0 ? ctx->opt.prefill_chunk : 16384;  // token rows per chunk (bounds the activation scratch)
   int b0 = 0;
-  std::vector<int32_t> next(B);
-  int32_t* d_next;
-  SB_CUDA(cudaMalloc((void**)&d_next, (size_t)B * 4));
-  struct Guard { void* p; ~Guard() { cudaFree(p); } } guard{d_next};
+  int32_t* d_next = kv->d_next;  // the decode step's own buffer: nothing else uses it during a prefill
   while (b0 < B) {
     int nb = 0;
     int64_t T = 0;
@@ -1011,39 +1025,45 @@ int strictb200_prefill(strictb200_model* m, strictb200_kv* kv, const int32_t* h_
       max_new = std::max(max_new, h_lens[b]);
       for (int i = 0; i < h_lens[b]; i++, t++) {
         tok[t] = h_tokens[(size_t)b * S + i];
-        seq[t] = j;  // relative to the chunk's first sequence
+        seq[t] = c.arch == STRICTB200_QWEN3 ? j : b;  // the fp32 path addresses the cache by absolute sequence index
         pos[t] = kv->h_lens[b] + i;
       }
       last[j] = (int32_t)t - 1;
     }
-    ChunkBufs cb;
-    cb.ctx = ctx;
-    int32_t *d_tok, *d_seq, *d_pos, *d_la, *d_past, *d_qs, *d_last;
-    SB_TRY(cb.get(&d_tok, T)); SB_TRY(cb.get(&d_seq, T)); SB_TRY(cb.get(&d_pos, T));
-    SB_TRY(cb.get(&d_la, nb)); SB_TRY(cb.get(&d_past, nb)); SB_TRY(cb.get(&d_qs, nb)); SB_TRY(cb.get(&d_last, nb));
-    SB_CUDA(cudaMemcpyAsync(d_tok, tok.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
-    SB_CUDA(cudaMemcpyAsync(d_seq, seq.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
-    SB_CUDA(cudaMemcpyAsync(d_pos, pos.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
-    SB_CUDA(cudaMemcpyAsync(d_la, la.data(), nb * 4, cudaMemcpyHostToDevice, ctx->stream));
-    SB_CUDA(cudaMemcpyAsync(d_past, past.data(), nb * 4, cudaMemcpyHostToDevice, ctx->stream));
-    SB_CUDA(cudaMemcpyAsync(d_qs, qstart.data(), nb * 4, cudaMemcpyHostToDevice, ctx->stream));
-    SB_CUDA(cudaMemcpyAsync(d_last, last.data(), nb * 4, cudaMemcpyHostToDevice, ctx->stream));
-    float* hl = h_logits ? h_logits + (size_t)b0 * c.vocab : nullptr;
-    if (c.arch == STRICTB200_QWEN3) {
-      SB_TRY(qwen_prefill_chunk(m, kv, T, nb, d_tok, d_seq, d_pos, d_la, d_past, d_qs, d_last, b0, d_next + b0, hl, max_new));
-    } else {
-      // the fp32 path addresses the cache by absolute sequence index
-      for (auto& s : seq) s += b0;
-      SB_CUDA(cudaMemcpyAsync(d_seq, seq.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
-      SB_TRY(gpt2_prefill_chunk(m, kv, T, nb, d_tok, d_seq, d_pos, d_last, d_next + b0, hl));
+    // one carve pass to size the scratch, one to place the buffers
+    ChunkIdx ix;
+    QwenChunk qc;
+    Gpt2Chunk gc;
+    char* base = nullptr;
+    for (int pass = 0; pass < 2; pass++) {
+      Carver cv{base};
+      carve_idx(cv, T, nb, &ix);
+      if (c.arch == STRICTB200_QWEN3) carve_qwen_chunk(m, cv, T, nb, &qc);
+      else carve_gpt2_chunk(m, cv, T, nb, &gc);
+      if (pass == 0) SB_TRY(prefill_scratch(ctx, cv.off, &base));
     }
+    SB_CUDA(cudaMemcpyAsync(ix.tok, tok.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
+    SB_CUDA(cudaMemcpyAsync(ix.seq, seq.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
+    SB_CUDA(cudaMemcpyAsync(ix.pos, pos.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
+    SB_CUDA(cudaMemcpyAsync(ix.la, la.data(), nb * 4, cudaMemcpyHostToDevice, ctx->stream));
+    SB_CUDA(cudaMemcpyAsync(ix.past, past.data(), nb * 4, cudaMemcpyHostToDevice, ctx->stream));
+    SB_CUDA(cudaMemcpyAsync(ix.qs, qstart.data(), nb * 4, cudaMemcpyHostToDevice, ctx->stream));
+    SB_CUDA(cudaMemcpyAsync(ix.last, last.data(), nb * 4, cudaMemcpyHostToDevice, ctx->stream));
+    float* hl = h_logits ? h_logits + (size_t)b0 * c.vocab : nullptr;
+    // both chunk functions end with a stream synchronise, so the host vectors above outlive their copies
+    if (c.arch == STRICTB200_QWEN3) {
+      SB_TRY(qwen_prefill_chunk(m, kv, T, nb, ix.tok, ix.seq, ix.pos, ix.la, ix.past, ix.qs, ix.last, b0, d_next + b0, hl, max_new, qc));
+    } else {
+      SB_TRY(gpt2_prefill_chunk(m, kv, T, nb, ix.tok, ix.seq, ix.pos, ix.last, d_next + b0, hl, gc));
+    }
+    SB_TRY(sb_check_status(ctx, "prefill"));
     for (int j = 0; j < nb; j++) kv->h_lens[b0 + j] += h_lens[b0 + j];
     b0 += nb;
   }
   SB_CUDA(cudaMemcpyAsync(kv->d_lens, kv->h_lens.data(), (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
   SB_CUDA(cudaMemcpyAsync(h_next, d_next, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
-  return STRICTB200_OK;
+  return sb_check_status(ctx, "prefill");
 }
 
 int strictb200_decode_step(strictb200_model* m, strictb200_kv* kv, const int32_t* h_ids, int32_t* h_next, float* h_logits) {
@@ -1063,18 +1083,15 @@ int strictb200_decode_step(strictb200_model* m, strictb200_kv* kv, const int32_t
       SB_CUDA(cudaMemcpyAsync(h_logits, b.logits, (size_t)kv->B * m->V_l * 4, cudaMemcpyDeviceToHost, ctx->stream));
     } else {
       SB_TRY(sb_tp_allgather(ctx, b.logits, b.logits_all, (int64_t)kv->B * m->V_l * 4));
-      float* tmp;
-      SB_CUDA(cudaMalloc((void**)&tmp, (size_t)m->world * kv->B * m->V_l * 4));
-      interleave_logits_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(b.logits_all, m->world, kv->B, m->V_l, tmp);
-      ctx->launches++;
-      cudaError_t e = cudaMemcpyAsync(h_logits, tmp, (size_t)m->world * kv->B * m->V_l * 4, cudaMemcpyDeviceToHost, ctx->stream);
-      cudaStreamSynchronize(ctx->stream);
-      cudaFree(tmp);
-      if (e != cudaSuccess) return sb_fail(STRICTB200_ERR_CUDA, cudaGetErrorString(e));
+      void* tmp;  // grow-only context scratch
+      SB_TRY(sb_ws2(ctx, (size_t)m->world * kv->B * m->V_l * 4, &tmp));
+      interleave_logits_kernel<<<ctx->sm_count * 4, 256, 0, ctx->stream>>>(b.logits_all, m->world, kv->B, m->V_l, (float*)tmp);
+      SB_LAUNCHED(ctx);
+      SB_CUDA(cudaMemcpyAsync(h_logits, tmp, (size_t)m->world * kv->B * m->V_l * 4, cudaMemcpyDeviceToHost, ctx->stream));
     }
   }
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
-  return STRICTB200_OK;
+  return sb_check_status(ctx, "decode_step");
 }
 
 int strictb200_decode_steps_device(strictb200_model* m, strictb200_kv* kv, int32_t* d_ids, int n_steps) {
@@ -1117,7 +1134,7 @@ int strictb200_generate(strictb200_model* m, strictb200_kv* kv, const int32_t* h
   SB_TRY(strictb200_decode_steps_device(m, kv, nullptr, n_steps));
   SB_CUDA(cudaMemcpyAsync(h_out, kv->d_hist, (size_t)n_steps * kv->B * 4, cudaMemcpyDeviceToHost, ctx->stream));
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
-  return STRICTB200_OK;
+  return sb_check_status(ctx, "generate");
 }
 
 int strictb200_profile_decode(strictb200_model* m, strictb200_kv* kv, int n_steps, float* ms_out, uint64_t* calls_out, int n_classes) {

@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(512) rownorm_kernel(RowNormDev a, int64_t M, i
       volatile int* f = a.comm.flags[a.comm.rank] + (comm_e & 1) * 8 + threadIdx.x;
       uint32_t spins = 0;
       while (*f - comm_e < 0) {
-        if (++spins > (1u << 24)) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
+        if (++spins > a.comm.wait_limit) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
         __nanosleep(64);
       }
     }
@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
         q0 = ld_peer4(src + off0);
         q1 = ld_peer4(src + off1);
         if (__float_as_int(q0.y) == e && __float_as_int(q0.w) == e && __float_as_int(q1.y) == e && __float_as_int(q1.w) == e) break;
-        if (++spins > (1u << 22)) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
+        if (++spins > a.comm.wait_limit) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
         if ((spins & 4095u) == 0 && *(volatile int*)a.comm.status) break;  // another wait already expired: do not wait it out again
       }
       v4[0] = q0.x; v4[1] = q0.z; v4[2] = q1.x; v4[3] = q1.z;
@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
       volatile int* f = a.comm.flags[a.comm.rank] + (comm_e & 1) * 8 + threadIdx.x;
       uint32_t spins = 0;
       while (*f - comm_e < 0) {
-        if (++spins > (1u << 24)) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
+        if (++spins > a.comm.wait_limit) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
         __nanosleep(64);
       }
     }
@@ -628,12 +628,13 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   // decode-step shapes: 4 columns per thread, at most 8 partials, no bf16 residual
   const bool narrow = d % 128 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
   // Four or more ranks exchange in two shots (one shot sends world-1 copies of every row);
-  // STRICTB200_TP_TWO_SHOT=0/1 forces either (read per call: the tests run both on two GPUs).
+  // the tp_two_shot option (0 / 1) forces either.
   if (a.comm) {
-    const char* ts = getenv("STRICTB200_TP_TWO_SHOT");
-    v.two_shot = (ts ? atoi(ts) != 0 : a.comm->world >= 4) && d % (a.comm->world * 128) == 0;
+    v.comm.wait_limit = ctx->opt.wait_limit > 0 ? (unsigned)ctx->opt.wait_limit : 1u;
+    const int ts = ctx->opt.tp_two_shot;
+    v.two_shot = (ts >= 0 ? ts != 0 : a.comm->world >= 4) && d % (a.comm->world * 128) == 0;
   }
-  if (narrow && a.comm && a.part && a.groups == 1 && a.splits <= 8 && a.comm->world <= 8 && M <= a.comm->max_rows && M * d <= a.comm->row_elems) {
+  if (narrow && a.comm && a.part && a.groups == 1 && a.splits <= 8 && a.comm->world <= 8 && sb_tp_row_exchange_ok(ctx, M, d)) {
     SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<3>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
     ctx->launches++;
     return STRICTB200_OK;

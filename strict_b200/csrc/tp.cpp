@@ -62,6 +62,8 @@ struct TpState {
   void* peer_buf[8] = {nullptr};  // every rank's buffer as mapped into this process
   int* local = nullptr;           // [epoch, done, ... | per-row epochs at int 64]
   bool opened = false;
+  bool absent_peers = false;      // failure-injection set-up: the "peers" are local areas nobody writes
+  long long row_d = 0;            // row width the row-granular exchange is tied to (0: not used yet)
   TpCommDev dev{};
 };
 
@@ -121,6 +123,17 @@ int sb_tp_allgather(strictb200_ctx* ctx, const void* send, void* recv, int64_t b
   return STRICTB200_OK;
 }
 const TpCommDev* sb_tp_comm(strictb200_ctx* ctx) { return ctx->tp && ctx->tp->opened ? &ctx->tp->dev : nullptr; }
+bool sb_tp_comm_fits(strictb200_ctx* ctx, int64_t M, int64_t d) {
+  return ctx->tp && ctx->tp->opened && d % 4 == 0 && M * d <= COMM_MAX_ELEMS;
+}
+// The packet area is addressed by row * d + column and validated by per-row epochs, so two row
+// widths on one context could take each other's stale packets for fresh ones: the first width
+// that uses the exchange owns it, other widths go through the publish kernel and its flags.
+bool sb_tp_row_exchange_ok(strictb200_ctx* ctx, int64_t M, int64_t d) {
+  if (!ctx->tp || !ctx->tp->opened || M > COMM_ROWS || M * d > COMM_ROW_ELEMS) return false;
+  if (!ctx->tp->row_d) ctx->tp->row_d = d;
+  return ctx->tp->row_d == d;
+}
 
 int k_tp_publish(strictb200_ctx* ctx, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N) {
   if (!ctx->tp || !ctx->tp->opened) return sb_fail(STRICTB200_ERR_INVALID_ARG, "peer buffers are not open");
@@ -135,7 +148,10 @@ int k_tp_publish(strictb200_ctx* ctx, const float* part, int splits, const float
 void sb_tp_destroy(strictb200_ctx* ctx) {
   if (ctx->tp) {
     for (int r = 0; r < 8; r++)
-      if (ctx->tp->peer_buf[r] && ctx->tp->peer_buf[r] != ctx->tp->comm_buf) cudaIpcCloseMemHandle(ctx->tp->peer_buf[r]);
+      if (ctx->tp->peer_buf[r] && ctx->tp->peer_buf[r] != ctx->tp->comm_buf) {
+        if (ctx->tp->absent_peers) cudaFree(ctx->tp->peer_buf[r]);
+        else cudaIpcCloseMemHandle(ctx->tp->peer_buf[r]);
+      }
     if (ctx->tp->comm_buf) cudaFree(ctx->tp->comm_buf);
     if (ctx->tp->local) cudaFree(ctx->tp->local);
     if (ctx->tp->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->tp->comm);
@@ -192,6 +208,7 @@ int strictb200_tp_comm_handle(strictb200_ctx* ctx, void* h_handle64) {
   memcpy(h_handle64, &h, 64);
   return STRICTB200_OK;
 }
+static void fill_comm_dev(strictb200_ctx* ctx);
 int strictb200_tp_comm_open(strictb200_ctx* ctx, const void* h_handles) {
   SB_ENTER(ctx);
   SB_REQUIRE(h_handles, "null handle buffer");
@@ -204,6 +221,30 @@ int strictb200_tp_comm_open(strictb200_ctx* ctx, const void* h_handles) {
     memcpy(&h, (const char*)h_handles + 64 * r, 64);
     SB_CUDA(cudaIpcOpenMemHandle(&tp->peer_buf[r], h, cudaIpcMemLazyEnablePeerAccess));
   }
+  fill_comm_dev(ctx);
+  return STRICTB200_OK;
+}
+int strictb200_tp_comm_open_absent_peers(strictb200_ctx* ctx, int world) {
+  SB_ENTER(ctx);
+  SB_REQUIRE(world == 2 || world == 4 || world == 8, "world must be 2, 4 or 8");
+  SB_REQUIRE(!ctx->tp, "tensor parallelism already initialised on this context");
+  TpState* tp = new TpState;
+  tp->absent_peers = true;
+  ctx->tp = tp;
+  ctx->tp_world = world;
+  ctx->tp_rank = 0;
+  for (int r = 0; r < world; r++) {
+    SB_CUDA(cudaMalloc(&tp->peer_buf[r], COMM_BYTES));
+    SB_CUDA(cudaMemset(tp->peer_buf[r], 0, COMM_BYTES));
+  }
+  tp->comm_buf = tp->peer_buf[0];
+  SB_CUDA(cudaMalloc((void**)&tp->local, 256 + COMM_ROWS * sizeof(int)));
+  SB_CUDA(cudaMemset(tp->local, 0, 256 + COMM_ROWS * sizeof(int)));
+  fill_comm_dev(ctx);
+  return STRICTB200_OK;
+}
+static void fill_comm_dev(strictb200_ctx* ctx) {
+  TpState* tp = ctx->tp;
   TpCommDev& d = tp->dev;
   for (int r = 0; r < ctx->tp_world; r++) {
     d.flags[r] = (int*)tp->peer_buf[r];
@@ -219,8 +260,25 @@ int strictb200_tp_comm_open(strictb200_ctx* ctx, const void* h_handles) {
   d.world = ctx->tp_world;
   d.rank = ctx->tp_rank;
   d.max_elems = COMM_MAX_ELEMS;
+  d.wait_limit = 1u << 22;
   tp->opened = true;
-  return STRICTB200_OK;
+}
+int strictb200_tp_allreduce_rownorm(strictb200_ctx* ctx, const float* d_part, int splits, const float* d_sx, const float* d_sw,
+                                    float* d_residual_f32, const float* d_gain, float eps, int64_t M, int64_t d, uint16_t* d_y,
+                                    uint8_t* d_split, float* d_split_scale) {
+  SB_ENTER(ctx);
+  SB_REQUIRE(M >= 0 && d > 0 && d % 8 == 0 && d <= 16384 && splits >= 1, "bad shape");
+  if (!M) return STRICTB200_OK;
+  SB_REQUIRE(d_part && d_sx && d_sw && d_gain, "null pointer");
+  SB_REQUIRE((d_split == nullptr) == (d_split_scale == nullptr), "the split output needs both its buffers");
+  SB_REQUIRE(ctx->tp_world > 1, "tensor parallelism is not initialised on this context");
+  if (!sb_tp_comm_fits(ctx, M, d)) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "tp_allreduce_rownorm needs open peer buffers and M*d <= 1M values");
+  RowNormArgs a;
+  a.comm = sb_tp_comm(ctx);
+  a.part = d_part; a.splits = splits; a.sx = d_sx; a.sw = d_sw;
+  a.residual_f32 = d_residual_f32; a.gain = d_gain; a.eps = eps;
+  a.y = (bf16*)d_y; a.q = d_split; a.qscale = d_split_scale;
+  return k_rownorm(ctx, a, M, d);
 }
 int strictb200_tp_info(strictb200_ctx* ctx, int* world, int* rank) {
   if (!ctx) return sb_fail(STRICTB200_ERR_INVALID_ARG, "null context");

@@ -68,6 +68,31 @@ class Context:
         N.check(N.lib().strictb200_device_status(self.h, C.byref(code)))
         return code.value
 
+    def set_option(self, name, value):
+        """A switch of this context (see strictb200_set_option); also settable once, at creation,
+        through the environment variable STRICTB200_<NAME>."""
+        N.check(N.lib().strictb200_set_option(self.h, name.encode(), int(value)))
+
+    def get_option(self, name):
+        v = C.c_int()
+        N.check(N.lib().strictb200_get_option(self.h, name.encode(), C.byref(v)))
+        return v.value
+
+    def option(self, name, value):
+        """Context manager: the option holds `value` inside the block and its old value after it."""
+        ctx = self
+
+        class _Opt:
+            def __enter__(self):
+                self.old = ctx.get_option(name)
+                ctx.set_option(name, value)
+
+            def __exit__(self, *a):
+                ctx.set_option(name, self.old)
+                return False
+
+        return _Opt()
+
     def flush_l2(self):
         N.check(N.lib().strictb200_flush_l2(self.h))
 
@@ -148,6 +173,71 @@ class DeviceVariable:
         if self.p:
             N.lib().strictb200_free(self.ctx.h, self.p)
             self.p = C.c_void_p()
+
+
+class FlatNumbers:
+    """Device-side counterpart of the flat numeric backing of ValueArrayInstance
+    (Strict.Expressions/ValueArrayInstance.cs:9-16): one contiguous fp32 array holding `Count`
+    elements of `FlatWidth` numbers each (an array of structs, e.g. Color = 4 floats), element i
+    member m at ``offset + i*FlatWidth + m`` (ValueArrayInstance.cs:128,339). Slices share the
+    backing array and only move `offset` (ValueArrayInstance.cs:63-64); the host array is uploaded
+    unchanged."""
+
+    def __init__(self, backing, flat_width, offset=0, count=None):
+        if flat_width < 1 or offset < 0:
+            raise ValueError("FlatWidth must be positive and offset non-negative")
+        self.backing, self.FlatWidth, self.offset = backing, int(flat_width), int(offset)
+        self.Count = (backing.count - self.offset) // self.FlatWidth if count is None else int(count)
+        if self.Count < 0 or self.offset + self.Count * self.FlatWidth > backing.count:
+            raise ValueError("view exceeds the backing array")
+
+    @classmethod
+    def of(cls, ctx, flat_numbers, flat_width, offset=0, count=None):
+        host = np.ascontiguousarray(flat_numbers, dtype=np.float32).reshape(-1)
+        return cls(DeviceVariable.of(ctx, host), flat_width, offset, count)
+
+    def slice(self, first, count):
+        """Elements [first, first+count) as a view over the same device memory."""
+        if first < 0 or count < 0 or first + count > self.Count:
+            raise IndexError((first, count))
+        return FlatNumbers(self.backing, self.FlatWidth, self.offset + first * self.FlatWidth, count)
+
+    def GetFlat(self, index):
+        """One number by flat index, as ValueArrayInstance.GetFlat (flatNumbers[offset + index])."""
+        return self.backing[self.offset + index]
+
+    def __getitem__(self, i):
+        """Element i as a tuple of its FlatWidth members."""
+        if not 0 <= i < self.Count:
+            raise IndexError(i)
+        return tuple(float(self.backing[self.offset + i * self.FlatWidth + m]) for m in range(self.FlatWidth))
+
+    def to_host(self):
+        """[Count, FlatWidth] host copy of the view."""
+        flat = self.backing.to_host()
+        return flat[self.offset:self.offset + self.Count * self.FlatWidth].reshape(self.Count, self.FlatWidth).copy()
+
+    def adjust_brightness(self, brightness, channels=3, clamp=False):
+        """ImageProcessing/AdjustBrightness.strict over this view, in place on the device."""
+        N.check(N.lib().strictb200_adjust_brightness(self.backing.ctx.h, self.backing.p, self.offset, self.Count, self.FlatWidth, channels,
+                                                     float(brightness), 1 if clamp else 0))
+        return self
+
+
+def blur5x5_rgb8(ctx, pixels, width, height, iterations=1):
+    """The reference harness's in-place 5x5 box blur (BlurPerformanceTests.cs:52-67) on the device:
+    uploads `pixels` (uint8, width*height*3), runs `iterations` passes between two device buffers,
+    returns the blurred bytes."""
+    host = np.ascontiguousarray(pixels, dtype=np.uint8).reshape(-1)
+    if host.size != width * height * 3:
+        raise ValueError("pixels must hold width*height*3 bytes")
+    a, b = DeviceVariable.of(ctx, host), DeviceVariable(ctx, max(host.size, 1), np.uint8)
+    for _ in range(iterations):
+        N.check(N.lib().strictb200_blur5x5_rgb8(ctx.h, a.p, b.p, width, height))
+        a, b = b, a
+    out = a.to_host()[:host.size]
+    a.free(), b.free()
+    return out
 
 
 class Kernel:

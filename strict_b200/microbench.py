@@ -19,9 +19,28 @@ import sys
 import numpy as np
 
 from . import native as N
+from .clocks import ClockSampler
 from .kernel import Context, DeviceVariable as DV
 
 L = N.lib
+MIN_TIMED_S = 0.6  # every timed region lasts at least this long, so that the 200 ms clock samples fall inside it
+
+
+def timed(ctx, run, first_reps):
+    """run(reps) enqueues the work; returns (ms per rep-unit of the long run, clock record)."""
+    run(max(1, first_reps // 4))  # warm-up
+    ctx.synchronize()
+    ctx.timer_begin()
+    run(first_reps)
+    ms = ctx.timer_end()
+    reps = max(first_reps, int(first_reps * MIN_TIMED_S * 1e3 / max(ms, 1e-3)) + 1)
+    sampler = ClockSampler(ctx.device)
+    sampler.start()
+    ctx.synchronize()
+    ctx.timer_begin()
+    run(reps)
+    ms = ctx.timer_end()
+    return ms / reps, sampler.stop()
 
 
 def _peaks():
@@ -54,18 +73,14 @@ def gemm_cases(ctx, iters, shape=None):
                 for it in range(copies):
                     N.check(L().strictb200_gemm_fp8(ctx.h, M, N_, K, xq.p, sx.p, wq[it].p, sw.p, y.p, 0, 0))
             graph = ctx.last_graph
-            reps = max(1, iters // copies)
-            ctx.replay(graph, 2)
-            ctx.synchronize()
-            ctx.timer_begin()
-            ctx.replay(graph, reps)
-            ms = ctx.timer_end() / (reps * copies)
+            ms, clocks = timed(ctx, lambda reps: ctx.replay(graph, reps), max(1, iters // copies))
+            ms /= copies
             ctx.free_graph(graph)
             byts = N_ * K + 4 * N_ + 2 * M * K + 2 * M * N_
             flops = 2.0 * M * N_ * K
             print(json.dumps({"case": "gemm_fp8w", "M": M, "N": N_, "K": K, "us": ms * 1e3, "GBps": byts / ms / 1e6, "hbm_frac": byts / ms / 1e6 / hbm,
                               "useful_TFLOPs": flops / ms / 1e9, "executed_fp8_TFLOPs": 2 * flops / ms / 1e9,
-                              "frac_of_bf16_peak": flops / ms / 1e9 / bf16_tf, "peaks": kind,
+                              "frac_of_bf16_peak": flops / ms / 1e9 / bf16_tf, "peaks": kind, "clocks": clocks,
                               "note": "split of the activations not included; weights rotate over %d copies" % copies}), flush=True)
             for v in (x, y, xq, sx):
                 v.free()
@@ -89,16 +104,13 @@ def attn_cases(ctx, iters):
     N.check(L().strictb200_gen_normal_bf16(ctx.h, 3, 2, 0, B * Hkv * maxlen * D, 1.0, kc.p))
     N.check(L().strictb200_gen_normal_bf16(ctx.h, 3, 3, 0, B * Hkv * maxlen * D, 1.0, vc.p))
     dl, out = DV.of(ctx, lens), DV(ctx, B * Hq * D, np.uint16)
-    for _ in range(3):
-        N.check(L().strictb200_attn_decode(ctx.h, q.p, kc.p, vc.p, dl.p, B, Hq, Hkv, D, maxlen, scale, out.p))
-    ctx.synchronize()
-    ctx.timer_begin()
-    for _ in range(iters):
-        N.check(L().strictb200_attn_decode(ctx.h, q.p, kc.p, vc.p, dl.p, B, Hq, Hkv, D, maxlen, scale, out.p))
-    ms = ctx.timer_end() / iters
+    def run_decode(reps):
+        for _ in range(reps):
+            N.check(L().strictb200_attn_decode(ctx.h, q.p, kc.p, vc.p, dl.p, B, Hq, Hkv, D, maxlen, scale, out.p))
+    ms, clocks = timed(ctx, run_decode, iters)
     byts = int(lens.sum()) * Hkv * D * 2 * 2
     print(json.dumps({"case": "attn_decode", "B": B, "sum_len": int(lens.sum()), "us": ms * 1e3, "GBps": byts / ms / 1e6, "hbm_frac": byts / ms / 1e6 / hbm,
-                      "peaks": kind, "note": "4.4 GB of K/V per call, far beyond L2"}), flush=True)
+                      "peaks": kind, "clocks": clocks, "note": "4.4 GB of K/V per call, far beyond L2"}), flush=True)
     for v in (q, kc, vc, dl, out, tok):
         v.free()
     # prefill: batch 4 x 8192, causal
@@ -109,16 +121,13 @@ def attn_cases(ctx, iters):
     N.check(L().strictb200_gen_normal_bf16(ctx.h, 3, 5, 0, B * Hkv * S * D, 1.0, kc.p))
     N.check(L().strictb200_gen_normal_bf16(ctx.h, 3, 6, 0, B * Hkv * S * D, 1.0, vc.p))
     dl, out = DV.of(ctx, np.full(B, S, np.int32)), DV(ctx, B * S * Hq * D, np.uint16)
-    n = max(2, iters // 5)
-    N.check(L().strictb200_attn_prefill(ctx.h, q.p, kc.p, vc.p, dl.p, None, B, S, Hq, Hkv, D, S, scale, out.p))
-    ctx.synchronize()
-    ctx.timer_begin()
-    for _ in range(n):
-        N.check(L().strictb200_attn_prefill(ctx.h, q.p, kc.p, vc.p, dl.p, None, B, S, Hq, Hkv, D, S, scale, out.p))
-    ms = ctx.timer_end() / n
+    def run_prefill(reps):
+        for _ in range(reps):
+            N.check(L().strictb200_attn_prefill(ctx.h, q.p, kc.p, vc.p, dl.p, None, B, S, Hq, Hkv, D, S, scale, out.p))
+    ms, clocks = timed(ctx, run_prefill, max(2, iters // 5))
     flops = 4.0 * B * Hq * D * S * S / 2
     print(json.dumps({"case": "attn_prefill", "B": B, "S": S, "ms": ms, "useful_TFLOPs": flops / ms / 1e9, "frac_of_bf16_peak": flops / ms / 1e9 / bf16_tf,
-                      "peaks": kind}), flush=True)
+                      "peaks": kind, "clocks": clocks}), flush=True)
 
 
 def ew_cases(ctx, count=1 << 24, chunk=100):

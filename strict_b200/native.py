@@ -51,12 +51,16 @@ SIGNATURES = {
     "strictb200_launch_count": [vp, C.POINTER(u64)],
     "strictb200_flush_l2": [vp],
     "strictb200_device_status": [vp, C.POINTER(i32)],
+    "strictb200_set_option": [vp, C.c_char_p, i32],
+    "strictb200_get_option": [vp, C.c_char_p, C.POINTER(i32)],
     "strictb200_graph_begin": [vp],
     "strictb200_graph_end": [vp, C.POINTER(vp)],
     "strictb200_graph_launch": [vp, vp, i32],
     "strictb200_graph_destroy": [vp],
     "strictb200_ew_binary": [vp, i32, vp, vp, vp, i64],
     "strictb200_ew_program": [vp, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64],
+    "strictb200_blur5x5_rgb8": [vp, vp, vp, i32, i32],
+    "strictb200_adjust_brightness": [vp, vp, i64, i64, i32, i32, C.c_double, i32],
     "strictb200_gen_normal_f32": [vp, u64, u64, i64, i64, f32, vp],
     "strictb200_gen_normal_bf16": [vp, u64, u64, i64, i64, f32, vp],
     "strictb200_gen_tokens": [vp, u64, u64, i64, u32, vp],
@@ -100,6 +104,8 @@ SIGNATURES = {
     "strictb200_tp_comm_handle": [vp, vp],
     "strictb200_tp_comm_open": [vp, vp],
     "strictb200_tp_allreduce_f32": [vp, vp, i64],
+    "strictb200_tp_allreduce_rownorm": [vp, vp, i32, vp, vp, vp, vp, f32, i64, i64, vp, vp, vp],
+    "strictb200_tp_comm_open_absent_peers": [vp, i32],
 }
 
 

@@ -29,6 +29,26 @@ def ctx():
     c.dispose()
 
 
+@pytest.fixture(scope="session")
+def parity_log():
+    """Appends one JSON line per parity record (logit errors, near-tie divergences with the
+    oracle's margin) to $STRICTB200_PARITY_LOG when that is set; always keeps them in memory and
+    prints them at the end of the session (visible with -s / -rA)."""
+    import json
+    records = []
+    path = os.environ.get("STRICTB200_PARITY_LOG")
+
+    def log(rec):
+        records.append(rec)
+        if path:
+            with open(path, "a") as f:
+                f.write(json.dumps(rec) + "\n")
+
+    yield log
+    for r in records:
+        print("parity:", json.dumps(r))
+
+
 @pytest.fixture
 def rng():
     return np.random.default_rng(1234)

@@ -176,11 +176,41 @@ def test_gemm_tiles_vs_oracle(ctx, oracle, rng, M, N_, K, kernel):
 
 
 @pytest.mark.parametrize("M,N_,K", [(300, 1008, 1536), (2048, 4096, 4096)])
-def test_gemm_one_sm_persistent_kernel_vs_oracle(ctx, oracle, rng, M, N_, K, monkeypatch):
+def test_gemm_one_sm_persistent_kernel_vs_oracle(ctx, oracle, rng, M, N_, K):
     """The one-SM persistent tcgen05 kernel (the fallback of the paired kernel) stays correct."""
-    monkeypatch.setenv("STRICTB200_GEMM_PAIR", "0")
-    got, want = _gemm_case(ctx, oracle, rng, M, N_, K, kernel=3, out_dtype=1)
+    with ctx.option("gemm_pair", 0):
+        got, want = _gemm_case(ctx, oracle, rng, M, N_, K, kernel=3, out_dtype=1)
     assert np.allclose(got, want, rtol=2e-5, atol=1e-5 * np.abs(want).max())
+
+
+@pytest.mark.parametrize("pair", [1, 0], ids=["sm-pairs", "one-sm"])
+def test_gemm_prefill_benchmark_shape_vs_oracle(ctx, oracle, rng, pair):
+    """The many-token tcgen05 kernels at the benchmark's second shape (M=2048, N=14336, K=4096,
+    device-generated weights from seed 2): 256 random output channels against the oracle, and
+    every channel against the few-token kernel path run on a slice of the rows."""
+    M, N_, K = 2048, 14336, 4096
+    x = oracle.round_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    xq, sx = oracle.split_rows_device_layout(x)
+    dwq, dsw = DV(ctx, N_ * K, np.uint8), DV(ctx, N_)
+    N.check(L().strictb200_gen_weight_e4m3(ctx.h, 2, 7, 0, N_, K, 0, K, 0.02, dwq.p, dsw.p))
+    dxq, dsx, out = DV.of(ctx, xq), DV.of(ctx, sx), DV(ctx, M * N_)
+    with ctx.option("gemm_pair", pair):
+        N.check(L().strictb200_gemm_fp8(ctx.h, M, N_, K, dxq.p, dsx.p, dwq.p, dsw.p, out.p, 1, 3))
+    got = out.to_host().reshape(M, N_)
+    cols = np.sort(rng.choice(N_, 256, replace=False))
+    cols[:4] = [0, 127, 128, N_ - 1]  # tile edges
+    wq = dwq.to_host().reshape(N_, K)[cols]
+    want = oracle.linear_fp8w(x, wq, dsw.to_host()[cols])
+    assert np.allclose(got[:, cols], want, rtol=2e-5, atol=1e-5 * np.abs(want).max())
+    # all 14336 channels of 32 rows spread over the token tiles, against the few-token kernel
+    rows = np.sort(rng.choice(M, 32, replace=False))
+    xq2, sx2 = oracle.split_rows_device_layout(x[rows])
+    d2, s2, o2 = DV.of(ctx, xq2), DV.of(ctx, sx2), DV(ctx, 32 * N_)
+    N.check(L().strictb200_gemm_fp8(ctx.h, 32, N_, K, d2.p, s2.p, dwq.p, dsw.p, o2.p, 1, 1))
+    small = o2.to_host().reshape(32, N_)
+    assert np.allclose(got[rows], small, rtol=2e-5, atol=1e-5 * np.abs(small).max())
+    for v in (dwq, dsw, dxq, dsx, out, d2, s2, o2):
+        v.free()
 
 
 def test_gemm_kernels_agree_and_linearity(ctx, oracle, rng):
@@ -352,9 +382,14 @@ def _attn_tol(got, want):
 
 @pytest.mark.parametrize("B,S,Hq,Hkv,lens", [(1, 1, 4, 2, [1]), (2, 65, 4, 1, [65, 3]), (2, 200, 8, 2, [200, 129]), (1, 64, 2, 2, [64]),
                                              (2, 256, 4, 2, [256, 130]), (1, 250, 8, 8, [250])])
-@pytest.mark.parametrize("tensor_memory_kernel", ["1", "0", "2"])
-def test_attn_prefill_vs_oracle(ctx, oracle, rng, B, S, Hq, Hkv, lens, tensor_memory_kernel, monkeypatch):
-    monkeypatch.setenv("STRICTB200_ATTN_TC", tensor_memory_kernel)  # tcgen05 one tile per block / mma.sync / tcgen05 two tiles per block
+@pytest.mark.parametrize("tensor_memory_kernel", [1, 0, 2])
+def test_attn_prefill_vs_oracle(ctx, oracle, rng, B, S, Hq, Hkv, lens, tensor_memory_kernel):
+    # tcgen05 one tile per block / mma.sync / tcgen05 two tiles per block
+    with ctx.option("attn_tc", tensor_memory_kernel):
+        _attn_prefill_case(ctx, oracle, rng, B, S, Hq, Hkv, lens)
+
+
+def _attn_prefill_case(ctx, oracle, rng, B, S, Hq, Hkv, lens):
     D, maxlen = 128, 256
     q = oracle.round_bf16(rng.standard_normal((B, S, Hq, D)).astype(np.float32))
     k = oracle.round_bf16(rng.standard_normal((B, S, Hkv, D)).astype(np.float32))
@@ -384,6 +419,64 @@ def test_attn_prefill_vs_oracle(ctx, oracle, rng, B, S, Hq, Hkv, lens, tensor_me
         got2 = bf16_host(oracle, do2, (B, 5, Hq, D))
         for b in range(B):
             assert _attn_tol(got2[b], want[b, past[b]:lens[b]])
+
+
+def _spiked_qkv(oracle, rng, B, S, Hq, Hkv, lens, spikes):
+    """bf16-valued N(0,1) q, k, v [B,S,H,128]. `spikes` = (sequence, query row, key index < row):
+    that key is set to 2.5 x the query of head 0 of every KV group, so the row's running maximum
+    jumps by ~28 (40 in the exp2 domain) when the key's tile comes up, late in the row's pass."""
+    D = 128
+    q = oracle.round_bf16(rng.standard_normal((B, S, Hq, D)).astype(np.float32))
+    k = oracle.round_bf16(rng.standard_normal((B, S, Hkv, D)).astype(np.float32))
+    v = oracle.round_bf16(rng.standard_normal((B, S, Hkv, D)).astype(np.float32))
+    G = Hq // Hkv
+    for b, row, key in spikes:
+        assert key <= row < lens[b]
+        for hk in range(Hkv):
+            k[b, key, hk] = oracle.round_bf16(2.5 * q[b, row, hk * G])
+    return q, k, v
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,lens", [(2, 1024, 8, 2, [1024, 700]), (2, 2048, 8, 2, [2048, 1337]), (1, 8192, 4, 1, [8192])],
+                         ids=["s1024", "s2048", "s8192"])
+def test_attn_prefill_long_vs_oracle(ctx, oracle, rng, B, S, Hq, Hkv, lens):
+    """Prefill attention at the prompt lengths of the benchmark (8 to 64 key tiles per query
+    tile), four query heads per KV head, ragged lengths, for both tcgen05 kernels; rows whose
+    maximum grows by far more than 2^8 late in the sequence exercise the lazy rescaling of the
+    running output; a continuation with past > 0 of 300 new tokens reproduces the same rows."""
+    D, maxlen = 128, S
+    lens = np.array(lens, np.int32)
+    spikes = []
+    for b in range(B):
+        n = int(lens[b])
+        spikes += [(b, n - 1, n - 7), (b, n - 130, n - 135), (b, n // 2 + 3, n // 2 - 40), (b, n - 50, 5), (b, 200, 199)]
+    q, k, v = _spiked_qkv(oracle, rng, B, S, Hq, Hkv, lens, spikes)
+    scale = 1.0 / np.sqrt(D)
+    want = oracle.round_bf16(oracle.attn_prefill(q, k, v, lens, scale))
+    kc = np.ascontiguousarray(k.transpose(0, 2, 1, 3))
+    vc = np.ascontiguousarray(v.transpose(0, 2, 1, 3))
+    dq, dk, dv, dl = bf16_dev(ctx, oracle, q), bf16_dev(ctx, oracle, kc), bf16_dev(ctx, oracle, vc), DV.of(ctx, lens)
+    do = DV(ctx, B * S * Hq * D, np.uint16)
+    new = 300
+    past = (lens - new).astype(np.int32)
+    q2 = np.stack([q[b, past[b]:lens[b]] for b in range(B)])
+    dq2, dp, do2 = bf16_dev(ctx, oracle, q2), DV.of(ctx, past), DV(ctx, B * new * Hq * D, np.uint16)
+    for mode in (1, 2, -1):
+        with ctx.option("attn_tc", mode):
+            do.zero()
+            N.check(L().strictb200_attn_prefill(ctx.h, dq.p, dk.p, dv.p, dl.p, None, B, S, Hq, Hkv, D, maxlen, scale, do.p))
+            got = bf16_host(oracle, do, (B, S, Hq, D))
+            N.check(L().strictb200_attn_prefill(ctx.h, dq2.p, dk.p, dv.p, dl.p, dp.p, B, new, Hq, Hkv, D, maxlen, scale, do2.p))
+            got2 = bf16_host(oracle, do2, (B, new, Hq, D))
+        for b in range(B):
+            assert _attn_tol(got[b, :lens[b]], want[b, :lens[b]]), (mode, b)
+            assert not got[b, lens[b]:].any()
+            assert _attn_tol(got2[b], want[b, past[b]:lens[b]]), (mode, b, "continuation")
+            for _, row, _ in [s for s in spikes if s[0] == b]:  # the spiked rows one by one
+                assert np.abs(got[b, row] - want[b, row]).max() <= 2e-2, (mode, b, row)
+    assert ctx.device_status() == 0
+    for x in (dq, dk, dv, dl, do, dq2, dp, do2):
+        x.free()
 
 
 @pytest.mark.parametrize("B,Hq,Hkv,maxlen,lens", [(1, 4, 2, 64, [1]), (3, 8, 2, 1024, [1, 64, 1000]), (2, 32, 8, 4096, [4096, 2049]),

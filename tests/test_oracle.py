@@ -336,3 +336,57 @@ def test_decode_continues_prefill(oracle, cfg, seed):
     for s in (full, inc):
         s.close()
     m.close()
+
+
+# ------------------------------------------------------------------ image workloads (reference-pinned)
+def test_adjust_brightness_known_answers(oracle):
+    """ImageProcessing/AdjustBrightness.strict:6-7,12-14,23 and Strict.Tests/RunnerTests.cs:270-289."""
+    g = GOLD["adjust_brightness"]
+    for case in g["cases"]:
+        out = oracle.adjust_brightness(np.array(g["test_color"], np.float32), 0, 1, 4, 3, case["brightness"])
+        assert out.tolist() == case["expected"]
+    run = g["run"]
+    n = run["width"] * run["height"]
+    image = np.tile(np.array(run["default_color"], np.float32), n)
+    out = oracle.adjust_brightness(image, 0, n, 4, 3, run["brightness"]).reshape(run["height"], run["width"], 4)
+    assert out[run["height"] // 2, run["width"] // 2, :3].tolist() == run["expected_centre"]
+    assert (out[..., 3] == 1.0).all()  # Alpha is not touched
+    # a view that starts inside the backing array (offset) and a struct of another width
+    flat = np.arange(20, dtype=np.float32)
+    out = oracle.adjust_brightness(flat, 2, 3, 5, 2, 0.5)
+    want = flat.copy()
+    for i in range(3):
+        want[2 + 5 * i:2 + 5 * i + 2] += 0.5
+    assert np.array_equal(out, want)
+    # double sum, one rounding: 0.1 is not a float, so float(x) + float(0.1) would differ
+    x = np.array([1.0000001, 0, 0, 1], np.float32)
+    assert oracle.adjust_brightness(x, 0, 1, 4, 3, 0.1)[0] == np.float32(np.float64(x[0]) + 0.1)
+    assert oracle.adjust_brightness(np.array([0.9, 0.5, 0.1, 1], np.float32), 0, 1, 4, 3, 0.25, clamp01=True).tolist()[:3] == [1.0, 0.75, np.float32(np.float64(np.float32(0.1)) + 0.25)]
+
+
+def _blur_python(px, w, h):
+    """Pixel-by-pixel restatement in Python of BlurInteriorPixel / BlurEdgePixel for small images."""
+    src = px.reshape(h, w, 3).astype(np.int64)
+    out = np.zeros_like(src)
+    for r in range(h):
+        for c in range(w):
+            r0, r1, c0, c1 = max(r - 2, 0), min(r + 3, h), max(c - 2, 0), min(c + 3, w)
+            win = src[r0:r1, c0:c1]
+            out[r, c] = win.sum(axis=(0, 1)) // ((r1 - r0) * (c1 - c0))
+    return out.astype(np.uint8).reshape(-1)
+
+
+@pytest.mark.parametrize("w,h", [tuple(s) for s in GOLD["blur"]["sizes"][:3]] + [(1, 1), (3, 7), (5, 5), (6, 4)])
+def test_blur_restatement_matches_python_and_is_thread_independent(oracle, w, h):
+    """The reference's own check (BlurProducesCorrectResults, :193-206) is that the single-thread
+    and the row-parallel blur agree byte for byte; here the C restatement on all threads, on one
+    thread, and a Python restatement of the two pixel functions agree on seeded bytes."""
+    px = (oracle.gen_tokens(42, 9, w * h * 3, 256)).astype(np.uint8)
+    many = oracle.blur5x5_rgb8(px, w, h)
+    oracle.lib().or_set_threads(1)
+    one = oracle.blur5x5_rgb8(px, w, h)
+    oracle.lib().or_set_threads(oracle.num_threads() if oracle.num_threads() > 1 else os.cpu_count() or 1)
+    assert np.array_equal(many, one)
+    assert np.array_equal(many, _blur_python(px, w, h))
+    twice = oracle.blur5x5_rgb8(px, w, h, iterations=2)
+    assert np.array_equal(twice, _blur_python(_blur_python(px, w, h), w, h))
