@@ -41,6 +41,16 @@ typedef struct strictb200_kv strictb200_kv;
 int strictb200_version(void);
 const char* strictb200_last_error(void);
 
+/* Compiles CUDA C text to PTX with NVRTC, as the reference does through ManagedCuda's
+ * CudaRuntimeCompiler(code, name).Compile(options) / GetPTXAsString / GetLogAsString
+ * (Strict.Compiler.Cuda/Kernel.cs:29-33,43,57). Needs no GPU and no context. `options` are NVRTC
+ * options such as "--gpu-architecture=compute_100a". With d_ptx_out NULL only *ptx_size (bytes
+ * including the final NUL) is returned. A compile error returns ERR_INVALID_ARG with the
+ * compiler's log as last_error; a machine without libnvrtc returns ERR_UNSUPPORTED. The kernels
+ * this library runs are compiled ahead of time and do not go through this call. */
+int strictb200_compile_to_ptx(const char* cuda_c, const char* name, const char* const* options, int n_options, char* ptx_out,
+                              size_t ptx_capacity, size_t* ptx_size);
+
 /* ---- context: replaces `new CudaContext(0)` (Strict.Compiler.Cuda/Kernel.cs:9) and
  * Kernel.Dispose (Kernel.cs:13-17). destroy(NULL) is a no-op. */
 int strictb200_create(int device, strictb200_ctx** out);
@@ -113,6 +123,22 @@ int strictb200_ew_binary(strictb200_ctx* ctx, int op, const float* d_a, const fl
 int strictb200_ew_program(strictb200_ctx* ctx, const int32_t* h_code, int n_instr, const float* const* h_arrays,
                           int n_arrays, const float* h_scalars, int n_scalars, const float* h_consts, int n_consts,
                           float* d_out, int64_t count);
+
+/* The larger instruction set: what the reference's plan lists as missing from its emitter for real
+ * data-parallel kernels (Strict.Compiler.Assembly/GpuSupportPlan.md:63-67) — conditionals, loops,
+ * variables, loads at computed indices (calls are placed inline by the host). Same quadruples and
+ * the opcodes 0..7 of strictb200_ew_program, over 32 slots (16 registers + 16 variables), plus
+ *   8 MODULO r[c] = fmodf(r[a], r[b])        9 EQUAL 10 NOT_EQUAL 11 LESS 12 GREATER   flag = r[a] op r[b]
+ *   13 JUMP pc = a     14 JUMP_IF_TRUE     15 JUMP_IF_FALSE      (absolute targets, 0..n_instr)
+ *   16 LOOP_BEGIN  r[a] iterations (at most 2^20), b = pc after the loop, r[c] = the index, from 0
+ *   17 LOOP_END    a = pc of its LOOP_BEGIN (at most 4 nested)
+ *   18 LOAD_AT     r[c] = arrays[a][(int)r[b]], 0.0f where that index is outside [0, count)
+ *   19 MOVE        r[c] = r[a]                20 LOAD_INDEX  r[c] = (float)idx
+ * RETURN ends the program for the element. At most 256 instructions. A thread that executes more
+ * than 65536 instructions for one element writes 0 and sets the context's error word
+ * (strictb200_device_status then returns ERR_TIMEOUT): no program can hang the GPU. */
+int strictb200_ew_program2(strictb200_ctx* ctx, const int32_t* h_code, int n_instr, const float* const* h_arrays, int n_arrays,
+                           const float* h_scalars, int n_scalars, const float* h_consts, int n_consts, float* d_out, int64_t count);
 
 /* ---- image workloads of the reference's samples ---- */
 /* 5x5 box blur over interleaved RGB bytes, d_src -> d_dst (two different buffers of

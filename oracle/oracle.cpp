@@ -713,6 +713,69 @@ void* or_state_create(void* mv, int B, int maxlen) {
 void or_state_free(void* s) { delete (State*)s; }
 void or_state_reset(void* s) { State* st = (State*)s; std::fill(st->len.begin(), st->len.end(), 0); }
 void or_state_lens(void* s, int32_t* out) { State* st = (State*)s; for (int b = 0; b < st->B; b++) out[b] = st->len[b]; }
+// The larger instruction set of the element-wise surface (conditionals, loops, variables, loads
+// at computed indices): CPU meaning of the same quadruples the device interpreter runs. The
+// arithmetic is C float as in the emitted CUDA C (InstructionsToCuda.cs:101-109); the condition
+// flag, jumps and loops follow the reference VM's instruction set (Strict.Bytecode/InstructionType.cs:
+// 9-47: Modulo, Equal..GreaterThan, Jump*, LoopBegin/LoopEnd, ListCall). Returns 2 if an element
+// ran past the step budget.
+int or_ew_program2(const int32_t* code, int n_instr, const float* const* arrays, const float* scalars,
+                   const float* consts, float* out, int64_t n) {
+  int rc = 0;
+  for (int64_t idx = 0; idx < n; idx++) {
+    float r[32] = {0};
+    int loop_begin[4], loop_count[4], loop_i[4], depth = 0;
+    bool flag = false;
+    float res = 0.0f;
+    int pc = 0, steps = 0;
+    while (pc < n_instr) {
+      if (++steps > (1 << 16)) { res = 0.0f; rc = 2; break; }
+      const int32_t* q = code + 4 * pc;
+      const int op = q[0], a = q[1], b = q[2], c = q[3];
+      int next = pc + 1;
+      switch (op) {
+        case 0: r[c] = arrays[a][idx]; break;
+        case 1: r[c] = scalars[a]; break;
+        case 2: r[c] = consts[a]; break;
+        case 3: r[c] = r[a] + r[b]; break;
+        case 4: r[c] = r[a] - r[b]; break;
+        case 5: r[c] = r[a] * r[b]; break;
+        case 6: r[c] = r[a] / r[b]; break;
+        case 7: res = r[a]; next = n_instr; break;
+        case 8: r[c] = std::fmod(r[a], r[b]); break;
+        case 9: flag = r[a] == r[b]; break;
+        case 10: flag = r[a] != r[b]; break;
+        case 11: flag = r[a] < r[b]; break;
+        case 12: flag = r[a] > r[b]; break;
+        case 13: next = a; break;
+        case 14: if (flag) next = a; break;
+        case 15: if (!flag) next = a; break;
+        case 16: {
+          const float cf = r[a];
+          const int count = cf >= 1.0f ? (cf < 1048576.0f ? (int)cf : 1048576) : 0;
+          if (count <= 0 || depth >= 4) { next = b; break; }
+          loop_begin[depth] = pc; loop_count[depth] = count; loop_i[depth] = 0; depth++;
+          r[c] = 0.0f;
+          break;
+        }
+        case 17:
+          if (depth > 0 && loop_begin[depth - 1] == a) {
+            if (++loop_i[depth - 1] < loop_count[depth - 1]) { r[code[4 * a + 3]] = (float)loop_i[depth - 1]; next = a + 1; }
+            else depth--;
+          }
+          break;
+        case 18: { const float f = r[b]; r[c] = (f >= 0.0f && f < (float)n) ? arrays[a][(int64_t)f] : 0.0f; break; }
+        case 19: r[c] = r[a]; break;
+        case 20: r[c] = (float)idx; break;
+        default: return 1;
+      }
+      pc = next;
+    }
+    out[idx] = res;
+  }
+  return rc;
+}
+
 // 5x5 box blur over interleaved RGB bytes, restating
 // Strict.Compiler.Assembly.Tests/BlurPerformanceTests.cs:52-141: a pixel with all 25 neighbours
 // inside the image (row and column in [2, size-2)) gets sum / 25 per channel (BlurInteriorPixel,

@@ -131,6 +131,23 @@ def ew_program(code, arrays, scalars, consts, n):
     return out
 
 
+def ew_program2(code, arrays, scalars, consts, n):
+    """The larger instruction set (conditionals, loops, indexed loads); raises RuntimeError if an
+    element ran past the step budget."""
+    code = np.ascontiguousarray(code, dtype=np.int32).reshape(-1, 4)
+    arrs = [_f32(a) for a in arrays]
+    ptrs = (C.c_void_p * max(1, len(arrs)))(*[a.ctypes.data for a in arrs])
+    sc = _f32(scalars if len(scalars) else [0])
+    co = _f32(consts if len(consts) else [0])
+    out = np.empty(n, np.float32)
+    rc = lib().or_ew_program2(_p(code), C.c_int(len(code)), ptrs, _p(sc), _p(co), _p(out), C.c_int64(n))
+    if rc == 1:
+        raise NotImplementedError("opcode")
+    if rc == 2:
+        raise RuntimeError("step budget exceeded")
+    return out
+
+
 # ------------------------------------------------------------------ image workloads
 def blur5x5_rgb8(pixels, width, height, iterations=1):
     """pixels uint8 [height*width*3]; returns the image after `iterations` in-place blur passes."""

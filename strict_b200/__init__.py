@@ -5,6 +5,8 @@ and raises if the library has not been built or no B200 is present (there is no 
 """
 from .native import KernelException, lib, LIB_PATH  # noqa: F401
 from .kernel import Context, DeviceVariable, FlatNumbers, Kernel, blur5x5_rgb8  # noqa: F401
-from .instructions_to_cuda import (CSharpToCudaTranspiler, CSharpType, InstructionsToCuda, InvalidCode, Method,  # noqa: F401
-                                   MissingReturnStatement)
+from .instructions_to_cuda import (BinaryExecutable, CSharpToCudaTranspiler, CSharpType, InstructionsCompiler,  # noqa: F401
+                                   InstructionsToCuda, InvalidCode, Method, MissingReturnStatement, Platform, StrictType)
 from .model import CONFIGS, GPT2, QWEN3, KvCache, Model  # noqa: F401
+from .runner import ChooseStrategy, CompilerBackend, ComplexityThreshold, EstimateComplexity, GpuComplexityThreshold, Runner  # noqa: F401
+from . import packaging  # noqa: F401

@@ -334,6 +334,16 @@ int strictb200_ew_program(strictb200_ctx* ctx, const int32_t* code, int n_instr,
   return k_ew_program(ctx, code, n_instr, arrays, n_arrays, scalars, n_scalars, consts, n_consts, out, count);
 }
 
+int strictb200_ew_program2(strictb200_ctx* ctx, const int32_t* code, int n_instr, const float* const* arrays, int n_arrays,
+                           const float* scalars, int n_scalars, const float* consts, int n_consts, float* out, int64_t count) {
+  SB_ENTER(ctx);
+  SB_REQUIRE(count >= 0 && n_instr >= 0 && n_arrays >= 0 && n_scalars >= 0 && n_consts >= 0, "negative size");
+  SB_REQUIRE(n_instr <= 256 && n_arrays <= 8 && n_scalars <= 8 && n_consts <= 16, "program too large");
+  if (count == 0) return STRICTB200_OK;
+  SB_REQUIRE(out && (n_instr == 0 || code), "null pointer");
+  return k_ew_program2(ctx, code, n_instr, arrays, n_arrays, scalars, n_scalars, consts, n_consts, out, count);
+}
+
 // ---------------------------------------------------------------- generator
 int strictb200_gen_normal_f32(strictb200_ctx* ctx, uint64_t seed, uint64_t tensor, int64_t first, int64_t count, float std_, float* out) {
   SB_ENTER(ctx);

@@ -146,6 +146,8 @@ typedef __nv_bfloat16 bf16;
 int k_ew_binary(strictb200_ctx*, int op, const float* a, const float* b, float* out, int64_t n);
 int k_ew_program(strictb200_ctx*, const int32_t* h_code, int n_instr, const float* const* h_arrays, int n_arrays,
                  const float* h_scalars, int n_scalars, const float* h_consts, int n_consts, float* out, int64_t n);
+int k_ew_program2(strictb200_ctx*, const int32_t* h_code, int n_instr, const float* const* h_arrays, int n_arrays,
+                  const float* h_scalars, int n_scalars, const float* h_consts, int n_consts, float* out, int64_t n);
 // gen.cu
 int k_gen_normal_f32(strictb200_ctx*, uint64_t key, int64_t first, int64_t count, float std_, float* out);
 int k_gen_normal_bf16(strictb200_ctx*, uint64_t key, int64_t first, int64_t count, float std_, bf16* out);

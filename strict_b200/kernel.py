@@ -240,14 +240,58 @@ def blur5x5_rgb8(ctx, pixels, width, height, iterations=1):
     return out
 
 
+class CudaBlasHandle:
+    """Stand-in for the lazily created cuBLAS handle of the reference's Kernel (Kernel.cs:10-11).
+    The reference never calls a cuBLAS routine through it; the GEMMs of this library are its own
+    kernels, so the handle only carries the context it belongs to and a Dispose."""
+
+    def __init__(self, context):
+        self.Context = context
+        self.disposed = False
+
+    def Dispose(self):
+        self.disposed = True
+
+
 class Kernel:
-    """Mirror of Strict.Compiler.Cuda.Kernel: `Context` is opened on device 0 at construction
-    and released by Dispose (Kernel.cs:9,13-17). The cuBLAS `Handle` of the reference is never
-    used for any routine (Kernel.cs:10-11) and has no counterpart here; kernels are compiled ahead
-    of time, so CompileKernelAndSaveAsPtxFile has nothing to compile and `run` launches directly."""
+    """Mirror of Strict.Compiler.Cuda.Kernel (Kernel.cs:7-58): `Context` is opened on device 0 at
+    construction and released by Dispose together with the handle (Kernel.cs:13-17); `Handle` is
+    created on first use (Kernel.cs:10-11); CompileKernelAndSaveAsPtxFile compiles the same saxpy
+    text with NVRTC and writes VectorAdd.ptx (Kernel.cs:19-33,54-58), for compute_100a instead of
+    the reference's compute_61. Kernels that run are compiled ahead of time: `Run` launches the
+    ahead-of-time equivalent of an emitted kernel."""
+
+    # the text the reference compiles (Kernel.cs:22-28)
+    SAXPY = ('extern "C" __global__ void saxpy(float a, float *x, float *y, float *out, size_t n)\n'
+             "{\n"
+             "  size_t tid = blockIdx.x * blockDim.x + threadIdx.x;\n"
+             "  if (tid < n) {\n"
+             "    out[tid] = a * x[tid] + y[tid];\n"
+             "  }\n"
+             "}")
+    GPU_ARCHITECTURE = "--gpu-architecture=compute_100a"
 
     def __init__(self, device=0):
         self.Context = Context(device)
+        self._handle = None
+
+    @property
+    def Handle(self):
+        if self._handle is None:
+            self._handle = CudaBlasHandle(self.Context)
+        return self._handle
+
+    def CompileKernelAndSaveAsPtxFile(self, path="VectorAdd.ptx"):
+        """Returns True and writes the PTX on success; False on a compile error, which the
+        reference swallows into an nvrtcResult (Kernel.cs:35-52). NotImplementedError where
+        NVRTC is not installed."""
+        try:
+            ptx = N.compile_to_ptx(self.SAXPY, "saxpy", (self.GPU_ARCHITECTURE,))
+        except ValueError:
+            return False
+        with open(path, "w") as f:
+            f.write(ptx)
+        return True
 
     def run(self, method, *args):
         """Launch the ahead-of-time equivalent of a kernel emitted by InstructionsToCuda: `method`
@@ -260,6 +304,8 @@ class Kernel:
 
     def dispose(self):
         self.Context.dispose()
+        if self._handle is not None:
+            self._handle.Dispose()
 
     Dispose = dispose
 

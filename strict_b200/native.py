@@ -34,6 +34,7 @@ vp, i32, i64, u64, f32, u32, sz = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.
 
 # name -> argtypes; every function returns int except where noted
 SIGNATURES = {
+    "strictb200_compile_to_ptx": [C.c_char_p, C.c_char_p, C.POINTER(C.c_char_p), i32, vp, sz, C.POINTER(sz)],
     "strictb200_create": [i32, C.POINTER(vp)],
     "strictb200_destroy": [vp],
     "strictb200_synchronize": [vp],
@@ -59,6 +60,7 @@ SIGNATURES = {
     "strictb200_graph_destroy": [vp],
     "strictb200_ew_binary": [vp, i32, vp, vp, vp, i64],
     "strictb200_ew_program": [vp, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64],
+    "strictb200_ew_program2": [vp, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64],
     "strictb200_blur5x5_rgb8": [vp, vp, vp, i32, i32],
     "strictb200_adjust_brightness": [vp, vp, i64, i64, i32, i32, C.c_double, i32],
     "strictb200_gen_normal_f32": [vp, u64, u64, i64, i64, f32, vp],
@@ -139,6 +141,17 @@ def check(status):
     if status == ERR_OOM:
         raise MemoryError(msg)
     raise KernelException(status, msg)
+
+
+def compile_to_ptx(cuda_c, name, options=("--gpu-architecture=compute_100a",)):
+    """CUDA C text -> PTX text through NVRTC (no GPU needed). Raises ValueError with the compiler's
+    log on a compile error, NotImplementedError where NVRTC is not installed."""
+    opts = (C.c_char_p * max(1, len(options)))(*[o.encode() for o in options])
+    size = sz()
+    check(lib().strictb200_compile_to_ptx(cuda_c.encode(), name.encode(), opts, len(options), None, 0, C.byref(size)))
+    buf = C.create_string_buffer(size.value)
+    check(lib().strictb200_compile_to_ptx(cuda_c.encode(), name.encode(), opts, len(options), buf, size.value, C.byref(size)))
+    return buf.value.decode()
 
 
 def ptr(a):

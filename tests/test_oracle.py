@@ -390,3 +390,31 @@ def test_blur_restatement_matches_python_and_is_thread_independent(oracle, w, h)
     assert np.array_equal(many, _blur_python(px, w, h))
     twice = oracle.blur5x5_rgb8(px, w, h, iterations=2)
     assert np.array_equal(twice, _blur_python(_blur_python(px, w, h), w, h))
+
+
+def test_noise_floor_of_the_numerics_contract_at_qwen3_8b_width(oracle):
+    """The contract rounds activations to bf16 between operators. At Qwen3-8B's width, four layers
+    deep, an oracle whose RMSNorm gains are 1 + 1e-6 (eight fp32 ulps) instead of 1 ends up with
+    logits that differ from the unperturbed oracle's by about 7e-3 mean-rel: a difference far
+    below a bf16 ulp flips some roundings, every flip is a whole bf16 ulp, the next operator
+    spreads it. Two faithful implementations with different fp32 summation orders are therefore
+    this far apart, which is above the 5e-3 mean-rel bar of the FP8 path; the GPU parity tests
+    take 1.25 x this measured floor as their bar where it exceeds 5e-3. (Vocabulary cut to 32768
+    rows so that the test runs in seconds; the logits' statistics do not depend on it.)"""
+    cfg = dict(arch=1, n_layers=4, d_model=4096, n_q_heads=32, n_kv_heads=8, head_dim=128, d_ff=12288, vocab=32768, max_pos=128, tied=0,
+               eps=1e-6, rope_theta=1e6)
+    toks = oracle.gen_tokens(105, 1, 32, cfg["vocab"]).reshape(1, 32)
+    lens = np.array([32], np.int32)
+    logits = []
+    for gain in (1.0, 1.0 + 1e-6):
+        om = oracle.Model(cfg, 5)
+        for l in range(cfg["n_layers"]):
+            for name in ("norm1.g", "norm2.g"):
+                om.tensor(f"layers.{l}.{name}", np.float32)[:] = np.float32(gain)
+        st = om.new_state(1, 40)
+        logits.append(st.prefill(toks, lens).copy())
+        st.close(), om.close()
+    err = np.abs(logits[0] - logits[1])
+    mean_rel = err.mean() / np.abs(logits[0]).mean()
+    assert 3e-3 < mean_rel < 2e-2, mean_rel   # at or above the 5e-3 bar's order of magnitude, far above fp32 noise (1e-6)
+    assert err.max() < 5e-2                    # the max-abs bar of the FP8 path still holds

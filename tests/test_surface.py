@@ -39,7 +39,7 @@ def test_lowering_to_register_program():
     assert ops == [0, 0, 3, 0, 5, 2, 4, 7]
     assert "output[idx] = ((a[idx] + b[idx]) * c[idx]) - 1" in m.cuda
     with pytest.raises(NotImplementedError):
-        sb.Method("F(a Number) Number", ["\ta % 2"])
+        sb.Method("F(a Number) Number", ["\ta ^ 2"])
     with pytest.raises(NotImplementedError):
         sb.InstructionsToCuda().compile(sb.Method("F(a Number) Number", ["\tb + 1"]))
 
