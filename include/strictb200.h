@@ -89,7 +89,10 @@ int strictb200_flush_l2(strictb200_ctx* ctx);
  * "gemm_pair" (many-token GEMM on SM pairs, 1), "prefetch" (1), "deep_ring" (1),
  * "attn_blocks_per_sm" (0), "split_target" (0), "tp_two_shot" (fused all-reduce in two shots,
  * -1: from four ranks on), "wait_limit" (polls of a cross-rank wait before it gives up,
- * 4194304), "prefill_chunk" (token rows per prefill chunk, 16384). Unknown name -> ERR_INVALID_ARG.
+ * 4194304), "prefill_chunk" (token rows per prefill chunk, 16384), "host_timeout_ms" (under tensor
+ * parallelism: a synchronising call polls the stream and NCCL's asynchronous error state and, after
+ * this many milliseconds, aborts the communicator and returns ERR_TIMEOUT instead of waiting for
+ * ever; 0 = wait without limit). Unknown name -> ERR_INVALID_ARG.
  * The reference has no counterpart (its one switch is a compile flag, Kernel.cs:43). */
 int strictb200_set_option(strictb200_ctx* ctx, const char* name, int value);
 int strictb200_get_option(strictb200_ctx* ctx, const char* name, int* out);

@@ -2,6 +2,8 @@
 #include <cctype>
 #include <cstdlib>
 #include <cstring>
+#include <chrono>
+#include <thread>
 #include <vector>
 
 #include "common.cuh"
@@ -27,6 +29,7 @@ const OptionName kOptions[] = {
     {"tp_two_shot", &SbOptions::tp_two_shot},
     {"wait_limit", &SbOptions::wait_limit},
     {"prefill_chunk", &SbOptions::prefill_chunk},
+    {"host_timeout_ms", &SbOptions::host_timeout_ms},
 };
 // STRICTB200_<NAME> of every option, read once, here
 void options_from_environment(SbOptions* o) {
@@ -37,6 +40,38 @@ void options_from_environment(SbOptions* o) {
   }
 }
 }  // namespace
+
+int sb_sync(strictb200_ctx* ctx, const char* what) {
+  if (!ctx->tp || ctx->tp_world == 1) {
+    SB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return STRICTB200_OK;
+  }
+  if (ctx->opt.host_timeout_ms <= 0) {
+    SB_CUDA(cudaStreamSynchronize(ctx->stream));
+  } else {
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(ctx->opt.host_timeout_ms);
+    for (int polls = 0;; polls++) {
+      cudaError_t e = cudaStreamQuery(ctx->stream);
+      if (e == cudaSuccess) break;
+      if (e != cudaErrorNotReady) return sb_fail(STRICTB200_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+      if (int rc = sb_tp_async_error(ctx)) {
+        sb_tp_abort(ctx);
+        return sb_fail(STRICTB200_ERR_NCCL, std::string(what) + ": NCCL reported an asynchronous error (code " + std::to_string(rc) + "); the communicator was aborted");
+      }
+      if (std::chrono::steady_clock::now() > deadline) {
+        sb_tp_abort(ctx);
+        return sb_fail(STRICTB200_ERR_TIMEOUT, std::string(what) + ": the stream did not finish within " + std::to_string(ctx->opt.host_timeout_ms) +
+                                                   " ms; the NCCL communicator was aborted");
+      }
+      if (polls > 2000) std::this_thread::sleep_for(std::chrono::microseconds(50));  // spin first: a decode step lasts a few ms
+    }
+  }
+  if (int rc = sb_tp_async_error(ctx)) {
+    sb_tp_abort(ctx);
+    return sb_fail(STRICTB200_ERR_NCCL, std::string(what) + ": NCCL reported an asynchronous error (code " + std::to_string(rc) + "); the communicator was aborted");
+  }
+  return STRICTB200_OK;
+}
 
 // Reads and clears the error word the kernels of this context set when a bounded wait expired.
 // The stream must have been synchronised by the caller.
@@ -194,8 +229,7 @@ int strictb200_graph_destroy(strictb200_graph* g) {
 
 int strictb200_synchronize(strictb200_ctx* ctx) {
   SB_ENTER(ctx);
-  SB_CUDA(cudaStreamSynchronize(ctx->stream));
-  return STRICTB200_OK;
+  return sb_sync(ctx, "synchronize");
 }
 
 int strictb200_malloc(strictb200_ctx* ctx, size_t bytes, void** d_out) {
@@ -282,7 +316,7 @@ int strictb200_launch_count(strictb200_ctx* ctx, uint64_t* out) {
 int strictb200_device_status(strictb200_ctx* ctx, int* out) {
   SB_ENTER(ctx);
   SB_REQUIRE(out, "null out pointer");
-  SB_CUDA(cudaStreamSynchronize(ctx->stream));
+  SB_TRY(sb_sync(ctx, "device_status"));
   *out = *(volatile int*)ctx->h_status;
   return sb_check_status(ctx, "device_status");
 }

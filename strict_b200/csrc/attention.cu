@@ -630,7 +630,7 @@ int k_attn_prefill(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf1
 // Keys per block. All blocks of a launch take about the same time, so the grid runs in waves of
 // (blocks resident per SM) x (SM count): the chunk is the multiple of the tile size that
 // minimises waves x (tiles per chunk + per-block overhead) for a full cache, among the chunk
-// sizes that leave at most 8 chunks per sequence. STRICTB200_ATTN_BLOCKS_PER_SM restores the
+// sizes that leave at most 8 (16 for very few pairs) chunks per sequence. The attn_blocks_per_sm option restores the
 // plain "that many blocks per SM" rule.
 static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
   const int per_sm = ctx->opt.attn_blocks_per_sm;
@@ -656,7 +656,10 @@ static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
   const int64_t slots = (int64_t)ctx->sm_count * resident, pairs = (int64_t)B * Hkv;
   int best = tiles;
   double best_cost = 1e30;
-  for (int c = (tiles + 7) / 8; c <= tiles; c++) {
+  // at most 8 chunks per sequence; 16 where 8 per (sequence, head) pair would not even fill one wave
+  // (few KV heads per rank under tensor parallelism), served by the general merge kernel
+  const int max_chunks = pairs * 8 < slots ? 16 : 8;
+  for (int c = (tiles + max_chunks - 1) / max_chunks; c <= tiles; c++) {
     if (c < 4 && c < tiles) continue;  // at least 256 keys per block
     const int64_t blocks = pairs * ((tiles + c - 1) / c), waves = (blocks + slots - 1) / slots;
     const double cost = (double)waves * ((double)c + 1.5);

@@ -57,6 +57,7 @@ struct SbOptions {
   int tp_two_shot = -1;        // fused all-reduce: 0 one shot, 1 two shots
   int wait_limit = 1 << 22;    // polls of a cross-rank wait before the kernel gives up and sets the error word
   int prefill_chunk = 16384;   // token rows per prefill chunk
+  int host_timeout_ms = 0;     // >0: a synchronising call gives up after this long, aborts the NCCL communicator and returns ERR_TIMEOUT
 };
 
 // One-time set-up that belongs to a device (function attributes are set per device): run(device, f)
@@ -106,6 +107,11 @@ struct strictb200_ctx {
 
 void sb_set_error(const std::string& msg);
 int sb_fail(int code, const std::string& msg);
+// Waits for the context's stream. Under tensor parallelism it also polls NCCL's asynchronous error
+// state (a failed peer or link) and, with the host_timeout_ms option, gives up after that long; in
+// both cases the communicator is aborted so that its kernels leave the GPU, and the call returns
+// ERR_NCCL / ERR_TIMEOUT instead of hanging.
+int sb_sync(strictb200_ctx* ctx, const char* what);
 int sb_check_status(strictb200_ctx* ctx, const char* what);  // after a stream synchronise: ERR_TIMEOUT if a kernel's wait expired
 int sb_ws(strictb200_ctx* ctx, size_t bytes, void** out);  // grow-only context scratch
 int sb_ws2(strictb200_ctx* ctx, size_t bytes, void** out);  // a second one, for calls that already hold the first
@@ -276,6 +282,8 @@ int k_tp_publish(strictb200_ctx*, const float* part, int splits, const float* sx
 int sb_tp_allreduce_f32(strictb200_ctx*, float* buf, int64_t count);
 int sb_tp_allgather(strictb200_ctx*, const void* send, void* recv, int64_t bytes_per_rank);
 void sb_tp_destroy(strictb200_ctx*);
+int sb_tp_async_error(strictb200_ctx*);  // 0 = none; else the NCCL result code of the communicator's asynchronous error
+void sb_tp_abort(strictb200_ctx*);       // ncclCommAbort: stops the communicator's kernels; the communicator is unusable afterwards
 
 // ------------------------------------------------------------------ device helpers
 #ifdef __CUDACC__

@@ -1062,7 +1062,7 @@ int strictb200_prefill(strictb200_model* m, strictb200_kv* kv, const int32_t* h_
   }
   SB_CUDA(cudaMemcpyAsync(kv->d_lens, kv->h_lens.data(), (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
   SB_CUDA(cudaMemcpyAsync(h_next, d_next, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
-  SB_CUDA(cudaStreamSynchronize(ctx->stream));
+  SB_TRY(sb_sync(ctx, "prefill"));
   return sb_check_status(ctx, "prefill");
 }
 
@@ -1090,7 +1090,7 @@ int strictb200_decode_step(strictb200_model* m, strictb200_kv* kv, const int32_t
       SB_CUDA(cudaMemcpyAsync(h_logits, tmp, (size_t)m->world * kv->B * m->V_l * 4, cudaMemcpyDeviceToHost, ctx->stream));
     }
   }
-  SB_CUDA(cudaStreamSynchronize(ctx->stream));
+  SB_TRY(sb_sync(ctx, "decode_step"));
   return sb_check_status(ctx, "decode_step");
 }
 
@@ -1133,7 +1133,7 @@ int strictb200_generate(strictb200_model* m, strictb200_kv* kv, const int32_t* h
   SB_CUDA(cudaMemcpyAsync(kv->d_ids, h_ids, (size_t)kv->B * 4, cudaMemcpyHostToDevice, ctx->stream));
   SB_TRY(strictb200_decode_steps_device(m, kv, nullptr, n_steps));
   SB_CUDA(cudaMemcpyAsync(h_out, kv->d_hist, (size_t)n_steps * kv->B * 4, cudaMemcpyDeviceToHost, ctx->stream));
-  SB_CUDA(cudaStreamSynchronize(ctx->stream));
+  SB_TRY(sb_sync(ctx, "generate"));
   return sb_check_status(ctx, "generate");
 }
 

@@ -3,6 +3,7 @@
 // NCCL already loaded by the host process when there is one.
 #include <dlfcn.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -18,13 +19,18 @@ struct Nccl {
   int (*AllReduce)(const void*, void*, size_t, int, int, nccl_comm, cudaStream_t) = nullptr;
   int (*AllGather)(const void*, void*, size_t, int, nccl_comm, cudaStream_t) = nullptr;
   int (*CommDestroy)(nccl_comm) = nullptr;
+  int (*CommAbort)(nccl_comm) = nullptr;
+  int (*CommGetAsyncError)(nccl_comm, int*) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
 };
 Nccl g_nccl;
 
 int load_nccl() {
   if (g_nccl.lib) return STRICTB200_OK;
-  void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
+  // STRICTB200_NCCL_LIB names another library with NCCL's entry points (failure-injection tests load a stand-in)
+  void* h = nullptr;
+  if (const char* other = getenv("STRICTB200_NCCL_LIB")) h = dlopen(other, RTLD_NOW | RTLD_LOCAL);
+  if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
   if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
   if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
   if (!h) return sb_fail(STRICTB200_ERR_NCCL, std::string("cannot load libnccl.so.2: ") + dlerror());
@@ -37,6 +43,8 @@ int load_nccl() {
   SYM(AllGather, "ncclAllGather")
   SYM(CommDestroy, "ncclCommDestroy")
   SYM(GetErrorString, "ncclGetErrorString")
+  SYM(CommAbort, "ncclCommAbort")
+  SYM(CommGetAsyncError, "ncclCommGetAsyncError")
 #undef SYM
   g_nccl.lib = h;
   return STRICTB200_OK;
@@ -109,6 +117,7 @@ __global__ void tp_publish_kernel(const float* __restrict__ part, int splits, co
 
 int sb_tp_allreduce_f32(strictb200_ctx* ctx, float* buf, int64_t count) {
   if (ctx->tp_world == 1) return STRICTB200_OK;
+  if (!ctx->tp || !ctx->tp->comm) return sb_fail(STRICTB200_ERR_NCCL, "this context has no NCCL communicator (never initialised, or aborted after an error)");
   int rc = g_nccl.AllReduce(buf, buf, (size_t)count, NCCL_FLOAT32, NCCL_SUM, ctx->tp->comm, ctx->stream);
   if (rc) return nccl_fail("ncclAllReduce", rc);
   return STRICTB200_OK;
@@ -118,6 +127,7 @@ int sb_tp_allgather(strictb200_ctx* ctx, const void* send, void* recv, int64_t b
     if (send != recv) SB_CUDA(cudaMemcpyAsync(recv, send, (size_t)bytes_per_rank, cudaMemcpyDeviceToDevice, ctx->stream));
     return STRICTB200_OK;
   }
+  if (!ctx->tp || !ctx->tp->comm) return sb_fail(STRICTB200_ERR_NCCL, "this context has no NCCL communicator (never initialised, or aborted after an error)");
   int rc = g_nccl.AllGather(send, recv, (size_t)bytes_per_rank, NCCL_INT8, ctx->tp->comm, ctx->stream);
   if (rc) return nccl_fail("ncclAllGather", rc);
   return STRICTB200_OK;
@@ -143,6 +153,18 @@ int k_tp_publish(strictb200_ctx* ctx, const float* part, int splits, const float
   SB_CUDA(sb_launch(ctx, tp_publish_kernel, dim3(grid), dim3(256), 0, part, splits, sx, sw, M, N, ctx->tp->dev));
   ctx->launches++;
   return STRICTB200_OK;
+}
+
+int sb_tp_async_error(strictb200_ctx* ctx) {
+  if (!ctx->tp || !ctx->tp->comm || !g_nccl.CommGetAsyncError) return 0;
+  int async = 0;
+  int rc = g_nccl.CommGetAsyncError(ctx->tp->comm, &async);
+  return rc ? rc : async;
+}
+void sb_tp_abort(strictb200_ctx* ctx) {
+  if (!ctx->tp || !ctx->tp->comm || !g_nccl.CommAbort) return;
+  g_nccl.CommAbort(ctx->tp->comm);
+  ctx->tp->comm = nullptr;  // aborted communicators are freed by ncclCommAbort; collectives on this context now fail
 }
 
 void sb_tp_destroy(strictb200_ctx* ctx) {

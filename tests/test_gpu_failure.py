@@ -50,3 +50,82 @@ def test_options_are_per_context_and_checked(ctx):
     assert ctx.get_option("attn_tc") == -1
     with pytest.raises(ValueError):
         ctx.set_option("no_such_switch", 1)
+
+
+_FAKE_NCCL_CHILD = r"""
+import ctypes, os, sys
+import numpy as np
+sys.path.insert(0, os.environ["REPO_ROOT"])
+import strict_b200 as sb
+from strict_b200 import native as N
+from strict_b200.kernel import DeviceVariable as DV
+fake = ctypes.CDLL(os.environ["STRICTB200_NCCL_LIB"])  # the same object the library dlopens
+
+def tp_context():
+    ctx = sb.Context(0)
+    uid = np.zeros(128, np.uint8)
+    N.check(N.lib().strictb200_tp_unique_id(N.ptr(uid)))
+    assert uid[0] == 7                                   # it is the stand-in that answered
+    ctx.tp_init(2, 0, N.ptr(uid))
+    return ctx
+
+# 1. an asynchronous NCCL error (a peer or a link failed) surfaces at the next synchronise and aborts the communicator
+ctx = tp_context()
+buf = DV.of(ctx, np.ones(16, np.float32))
+N.check(N.lib().strictb200_tp_allreduce_f32(ctx.h, buf.p, 16))
+ctx.synchronize()
+assert fake.fake_nccl_allreduces() == 1 and fake.fake_nccl_aborts() == 0
+fake.fake_nccl_set_async_error(3)
+try:
+    ctx.synchronize()
+    raise SystemExit("the asynchronous error was not reported")
+except N.KernelException as e:
+    assert e.status == N.ERR_NCCL and "aborted" in str(e), e
+assert fake.fake_nccl_aborts() == 1
+fake.fake_nccl_set_async_error(0)
+try:
+    N.check(N.lib().strictb200_tp_allreduce_f32(ctx.h, buf.p, 16))
+    raise SystemExit("a collective ran on an aborted communicator")
+except N.KernelException as e:
+    assert e.status == N.ERR_NCCL
+ctx.synchronize()                                        # the context itself still works
+ctx.dispose()
+assert fake.fake_nccl_destroys() == 0                    # an aborted communicator is not destroyed a second time
+
+# 2. a stream that does not finish within host_timeout_ms: ERR_TIMEOUT and an abort, no endless wait.
+#    The slow work is an element-wise program bounded by its step budget; it ends by itself.
+ctx = tp_context()
+slow = sb.InstructionsToCuda().compile(sb.Method("Slow(a Number) Number", ["\tmutable t = 0", "\tfor 8000", "\t\tt = t + a", "\tt"]))
+n = 1 << 21
+a, out = DV(ctx, n), DV(ctx, n)
+a.zero()
+ctx.set_option("host_timeout_ms", 20)
+slow.launch(ctx, a, out, n)
+try:
+    ctx.synchronize()
+    timed_out = False
+except N.KernelException as e:
+    assert e.status == N.ERR_TIMEOUT and "aborted" in str(e), e
+    timed_out = True
+ctx.set_option("host_timeout_ms", 0)
+ctx.synchronize()                                        # without a limit the call waits for the kernel, which ends by itself
+assert ctx.device_status() == 0
+assert timed_out and fake.fake_nccl_aborts() == 2, (timed_out, fake.fake_nccl_aborts())
+ctx.dispose()
+print("fake-nccl-ok")
+"""
+
+
+def test_nccl_async_error_and_host_timeout_abort_the_communicator(tmp_path):
+    """NCCL is bound with dlopen; a stand-in (tests/fake_nccl.c) injects the failures on the host:
+    an asynchronous error code, and a stream that outlasts host_timeout_ms. Both must end the
+    synchronising call with an error status and one ncclCommAbort, never with an endless wait."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    so = str(tmp_path / "libfakenccl.so")
+    subprocess.check_call(["gcc", "-shared", "-fPIC", "-O1", "-o", so, os.path.join(here, "fake_nccl.c")])
+    env = dict(os.environ, STRICTB200_NCCL_LIB=so, REPO_ROOT=os.path.dirname(here))
+    r = subprocess.run([sys.executable, "-c", _FAKE_NCCL_CHILD], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "fake-nccl-ok" in r.stdout, r.stdout + r.stderr
