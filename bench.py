@@ -194,6 +194,7 @@ def run_ours(args, rank, world, local_rank):
                 prefill_clocks["device_s_x_sm_mhz"] = prefill_dev_s * prefill_clocks["sm_mhz"]
     ctx.synchronize()
     prefill_s = time.perf_counter() - t0
+    barrier()  # the ranks leave the set-up together: a rank's first decode step waits for its peers inside a kernel, with a bounded wait
 
     # ---- value: device-resident ids, graph replay
     ids_dev = first.copy()

@@ -195,7 +195,10 @@ int strictb200_gemm_f32(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, co
 /* ---- norms / activations ---- */
 /* y = (x * rsqrt(mean(x^2)+eps)) * gain, bf16 in/out, fp32 statistics. If d_residual is not
  * NULL it is first updated in place: residual = bf16(residual + x), and the norm is taken
- * of the updated residual. */
+ * of the updated residual. This is the stand-alone operator with a bf16 residual; the model's
+ * own path keeps its residual stream in fp32 and fuses the split-K sum, the residual update, the
+ * norm and the activation split in one row kernel (the fp32-residual form of the same kernel is
+ * reachable through strictb200_tp_allreduce_rownorm under tensor parallelism). */
 int strictb200_rmsnorm(strictb200_ctx* ctx, const uint16_t* d_x, uint16_t* d_residual, const float* d_gain, float eps, int64_t M,
                        int64_t d, uint16_t* d_y);
 int strictb200_layernorm(strictb200_ctx* ctx, const float* d_x, const float* d_gain, const float* d_bias, float eps, int64_t M,

@@ -225,6 +225,10 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
     if (lane == 0) {
       // instruction descriptor: D = F32 (bits 4-5 = 1), A = B = E4M3 (0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
       constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BT >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
+      // The operand tiles cannot arrive before the producer's dependency wait has returned; waiting for the same
+      // dependency here keeps the bounded waits below for progress inside this kernel (a predecessor that itself
+      // waits for another rank may take longer than any of them).
+      pdl_wait();
       int seg = -1;  // segment = run of K blocks of one tile inside this block's range
       for (int it = 0; it < n_my; it++) {
         const int kb = (int)((my_begin + it) % nkb);

@@ -193,6 +193,10 @@ __global__ void __launch_bounds__(192) gemm_pair_kernel(const __grid_constant__ 
     if (leader && lane == 0) {
       // instruction descriptor: D = F32, A = B = E4M3, both K-major, N = 256 (>> 3 at bit 17), M = 256 (>> 4 at bit 24)
       constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+      // The operand tiles cannot arrive before the producer's dependency wait has returned; waiting for the same
+      // dependency here keeps the bounded waits below for progress inside this kernel (a predecessor that itself
+      // waits for another rank may take longer than any of them).
+      pdl_wait();
       for (int it = 0; it < n_my; it++) {
         const int kb = it % nkb, seg = it / nkb;
         if (kb == 0) {

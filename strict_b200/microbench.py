@@ -1,7 +1,7 @@
 """Kernel microbenchmarks at the shapes of BASELINE.json configs[1] (GEMM/GEMV) and configs[2]
 (GQA attention), through the C ABI, timed with CUDA events on the library's stream.
 
-    python -m strict_b200.microbench [gemm] [attn] [ew] [--iters N] [--shape M,N,K]
+    python -m strict_b200.microbench [gemm] [attn] [ew] [image] [--iters N] [--shape M,N,K]
 
 Every timed call reads buffers that were not touched by the previous call (weights rotate
 through enough distinct copies to exceed the 126 MB L2; the attention caches are GBs), so the
@@ -202,6 +202,61 @@ def ew_cases(ctx, count=1 << 24, chunk=100):
     pool.shutdown()
 
 
+def image_cases(ctx, iters):
+    """The image workloads: the 5x5 box blur over RGB bytes on an image larger than L2 (one byte
+    read and one written per byte of image) and at the reference harness's size and iteration
+    count (2048x1024, 200 passes, Strict.Compiler.Cuda.Tests/BlurPerformanceTests.cs:20-26, with
+    the copies to and from the device, as its RunGpu has); AdjustBrightness over 2^26 colours."""
+    import time
+    hbm, _, kind = _peaks()
+    w, h = 8192, 8192
+    n = w * h * 3
+    a, b = DV(ctx, n, np.uint8), DV(ctx, n, np.uint8)
+    N.check(L().strictb200_gen_tokens(ctx.h, 42, 11, n // 4, 1 << 31, a.p))
+
+    def run_blur(reps):
+        for _ in range(reps):
+            N.check(L().strictb200_blur5x5_rgb8(ctx.h, a.p, b.p, w, h))
+    ms, clocks = timed(ctx, run_blur, max(4, iters // 4))
+    print(json.dumps({"case": "blur5x5_rgb8", "width": w, "height": h, "us": ms * 1e3, "GBps": 2.0 * n / ms / 1e6, "hbm_frac": 2.0 * n / ms / 1e6 / hbm,
+                      "bytes_per_pixel_byte": 2, "peaks": kind, "clocks": clocks, "note": "201 MB read + 201 MB written per pass, larger than L2"}), flush=True)
+    for v in (a, b):
+        v.free()
+    w, h, passes = 2048, 1024, 200
+    n = w * h * 3
+    host = np.random.default_rng(42).integers(0, 256, n, dtype=np.uint8)
+    a, b = DV(ctx, n, np.uint8), DV(ctx, n, np.uint8)
+    out = np.empty(n, np.uint8)
+
+    def harness():
+        N.check(L().strictb200_upload(ctx.h, a.p, N.ptr(host), n))
+        x, y = a, b
+        for _ in range(passes):
+            N.check(L().strictb200_blur5x5_rgb8(ctx.h, x.p, y.p, w, h))
+            x, y = y, x
+        N.check(L().strictb200_download(ctx.h, N.ptr(out), x.p, n))
+    harness()
+    t0 = time.perf_counter()
+    harness()
+    dt = time.perf_counter() - t0
+    print(json.dumps({"case": "blur5x5_rgb8", "variant": "CudaGpu (reference harness: 2048x1024, 200 passes, copies included)", "ms": dt * 1e3,
+                      "pixel_passes_per_s": w * h * passes / dt, "note": "6.3 MB image: resident in L2 between passes"}), flush=True)
+    for v in (a, b):
+        v.free()
+    count = 1 << 26
+    flat = DV(ctx, count * 4)
+    N.check(L().strictb200_gen_normal_f32(ctx.h, 6, 1, 0, count * 4, 0.1, flat.p))
+
+    def run_brightness(reps):
+        for _ in range(reps):
+            N.check(L().strictb200_adjust_brightness(ctx.h, flat.p, 0, count, 4, 3, 1e-6, 0))
+    ms, clocks = timed(ctx, run_brightness, max(4, iters // 4))
+    print(json.dumps({"case": "adjust_brightness", "colors": count, "flat_width": 4, "us": ms * 1e3, "GBps": 32.0 * count / ms / 1e6,
+                      "hbm_frac": 32.0 * count / ms / 1e6 / hbm, "peaks": kind, "clocks": clocks,
+                      "note": "16 bytes read and written per colour (the 128-bit access also carries Alpha)"}), flush=True)
+    flat.free()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="*", default=["gemm", "attn"])
@@ -215,6 +270,8 @@ def main():
         attn_cases(ctx, args.iters)
     if "ew" in args.what:
         ew_cases(ctx)
+    if "image" in args.what:
+        image_cases(ctx, args.iters)
     ctx.dispose()
 
 
