@@ -30,6 +30,7 @@ const OptionName kOptions[] = {
     {"wait_limit", &SbOptions::wait_limit},
     {"prefill_chunk", &SbOptions::prefill_chunk},
     {"host_timeout_ms", &SbOptions::host_timeout_ms},
+    {"fuse_rope", &SbOptions::fuse_rope},
 };
 // STRICTB200_<NAME> of every option, read once, here
 void options_from_environment(SbOptions* o) {
@@ -544,7 +545,7 @@ int strictb200_attn_decode(strictb200_ctx* ctx, const uint16_t* q, const uint16_
   void* ws;
   SB_TRY(sb_ws(ctx, sb_attn_decode_scratch(B, Hq, D, nsplit), &ws));
   return k_attn_decode(ctx, (const bf16*)q, (const bf16*)kc, (const bf16*)vc, lens, 0, B, Hq, Hkv, D, maxlen, scale, nsplit, (float*)ws,
-                       (bf16*)out, nullptr, nullptr);
+                       (bf16*)out, nullptr, nullptr, nullptr);
 }
 
 // ---------------------------------------------------------------- embedding / sampling

@@ -227,13 +227,76 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const bf16* __restric
 }
 
 // ------------------------------------------------------------------ decode (split-KV)
+// What the decode step's RoPE kernel does for one head (rope.cu, operation for operation): sum of
+// the qkv projection's split-K partials, the two scales, per-head RMS norm, rotary embedding at
+// position p, rounded to bf16. One warp per head, four dimensions per lane. is_v: the value head is
+// only summed, scaled and rounded.
+struct RopeFuseArgs {
+  const float* part;   // [splits][B][nqkv] raw accumulators of the qkv projection (null: q is read from memory)
+  int splits;
+  const float* sx;     // [B]
+  const float* sw;     // [nqkv]
+  const float* cos_t;  // [max_pos][64]
+  const float* sin_t;
+  const float* qgain;
+  const float* kgain;
+  float eps;
+  int max_pos;
+  bf16* kcache;        // the caches again, writable: the new token's key and value rows are appended here
+  bf16* vcache;
+};
+__device__ __forceinline__ uint2 rope_head_bf16(const RopeFuseArgs& r, int B, int b, int64_t nqkv, int64_t col0, const float* gain, int p, bool is_v,
+                                                int lane) {
+  const int64_t col = col0 + lane * 4;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float4 v[8];
+#pragma unroll
+  for (int s = 0; s < 8; s++)
+    if (s < r.splits) v[s] = *(const float4*)(r.part + ((int64_t)s * B + b) * nqkv + col);
+  const float4 w = *(const float4*)(r.sw + col);
+  const float sxr = r.sx[b];
+#pragma unroll
+  for (int s = 0; s < 8; s++)
+    if (s < r.splits) { acc[0] += v[s].x; acc[1] += v[s].y; acc[2] += v[s].z; acc[3] += v[s].w; }
+  float x[4] = {__fmul_rn(__fmul_rn(acc[0], sxr), w.x), __fmul_rn(__fmul_rn(acc[1], sxr), w.y), __fmul_rn(__fmul_rn(acc[2], sxr), w.z),
+                __fmul_rn(__fmul_rn(acc[3], sxr), w.w)};
+  float o[4];
+  if (!is_v) {
+    const float4 gv = *(const float4*)(gain + lane * 4);
+    const int i0 = (lane & 15) * 4;
+    const float4 c = *(const float4*)(r.cos_t + (int64_t)p * (D / 2) + i0), sn4 = *(const float4*)(r.sin_t + (int64_t)p * (D / 2) + i0);
+    const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+    const float rr = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)D), r.eps)));
+    const float n[4] = {__fmul_rn(__fmul_rn(x[0], rr), gv.x), __fmul_rn(__fmul_rn(x[1], rr), gv.y), __fmul_rn(__fmul_rn(x[2], rr), gv.z),
+                        __fmul_rn(__fmul_rn(x[3], rr), gv.w)};
+    const float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {sn4.x, sn4.y, sn4.z, sn4.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float other = __shfl_xor_sync(0xffffffffu, n[j], 16);
+      o[j] = lane < 16 ? __fsub_rn(__fmul_rn(n[j], cs[j]), __fmul_rn(other, sn[j])) : __fadd_rn(__fmul_rn(n[j], cs[j]), __fmul_rn(other, sn[j]));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; j++) o[j] = x[j];
+  }
+  return make_uint2(f32_to_bf16_bits(o[0]) | (f32_to_bf16_bits(o[1]) << 16), f32_to_bf16_bits(o[2]) | (f32_to_bf16_bits(o[3]) << 16));
+}
+
 // grid (nsplit, Hkv, B), 128 threads. Warp w owns keys [16w,16w+16) of every 64-key tile.
 // scratch: o_part [B][Hq][nsplit][128] then ml_part [B][Hq][nsplit][2].
+// FUSED: the queries do not come from memory; every block computes the (at most 16) query heads of
+// its KV head from the qkv projection's partial results (sum, scales, QK-norm, RoPE), and the block
+// whose key chunk holds the new token's position also computes that token's key and value rows,
+// appends them to the cache and patches them into its own shared-memory tile (its tile load may
+// have read that row before the append). One kernel less per layer of the decode step.
+template <bool FUSED>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                                                           const int32_t* __restrict__ lens, int len_add, int B, int Hq, int Hkv, int maxlen,
                                                           int chunk, int nsplit, float scale_log2, float* __restrict__ o_part,
-                                                          float* __restrict__ ml_part) {
+                                                          float* __restrict__ ml_part, RopeFuseArgs rf) {
   extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(16) bf16 q_s[FUSED ? 16 * D : 8];    // the query heads of this KV head
+  __shared__ __align__(16) bf16 kv_new[FUSED ? 2 * D : 8];  // the new token's key row, then its value row
   pdl_trigger();
   pdl_wait();
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -243,6 +306,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
   const int k_end = min(len, k_begin + chunk);
   const int G = Hq / Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  // FUSED: position of the new token = the sequence's length before this step; its row is the last key
+  const int p_new = FUSED ? len - 1 : -1;
+  const bool owns_new = FUSED && p_new >= k_begin && p_new < k_end && p_new < rf.max_pos;
   const uint32_t sK = smem_u32(smem), sV = sK + DEC_STAGES * KT * 256;
   const bf16* kbase = kc + ((int64_t)b * Hkv + hk) * maxlen * D;
   const bf16* vbase = vc + ((int64_t)b * Hkv + hk) * maxlen * D;
@@ -260,10 +326,28 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
     cp_async_commit();
   }
 
-  // Q fragments straight from global: rows = the G query heads of this KV head (zero beyond)
+  if (FUSED) {
+    const int64_t nqkv = (int64_t)(Hq + 2 * Hkv) * D;
+    const int pos = min(p_new, rf.max_pos - 1);
+    // items 0..G-1: the query heads; for the owner of the new position also G: the key head, G+1: the value head
+    for (int i = warp; i < G + (owns_new ? 2 : 0); i += 4) {
+      if (i < G) {
+        const uint2 w = rope_head_bf16(rf, B, b, nqkv, (int64_t)(hk * G + i) * D, rf.qgain, pos, false, lane);
+        *(uint2*)(q_s + i * D + lane * 4) = w;
+      } else {
+        const bool is_v = i == G + 1;
+        const uint2 w = rope_head_bf16(rf, B, b, nqkv, (int64_t)(Hq + (is_v ? Hkv : 0) + hk) * D, rf.kgain, pos, is_v, lane);
+        *(uint2*)(kv_new + (is_v ? D : 0) + lane * 4) = w;
+        bf16* cache = is_v ? rf.vcache : rf.kcache;
+        *(uint2*)(cache + (((int64_t)b * Hkv + hk) * maxlen + p_new) * D + lane * 4) = w;
+      }
+    }
+    __syncthreads();
+  }
+  // Q fragments: rows = the G query heads of this KV head (zero beyond), from memory or from the prologue above
   uint32_t qf[8][4];
   {
-    const bf16* q0 = q + ((int64_t)b * Hq + hk * G) * D;
+    const bf16* q0 = FUSED ? q_s : q + ((int64_t)b * Hq + hk * G) * D;
 #pragma unroll
     for (int ks = 0; ks < 8; ks++) {
       int d0 = ks * 16 + 2 * tig;
@@ -294,6 +378,15 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
     }
     __syncthreads();
     const uint32_t tK = sK + (t % DEC_STAGES) * KT * 256, tV = sV + (t % DEC_STAGES) * KT * 256;
+    if (FUSED && owns_new && p_new >= k_begin + t * KT && p_new < k_begin + (t + 1) * KT) {
+      // the tile copy may have read the new token's row before it was appended: put the rows computed above in its place
+      if (warp == 0) {
+        const int row = p_new - (k_begin + t * KT), cc = lane & 15;
+        const uint4 w = *(const uint4*)(kv_new + (lane < 16 ? 0 : D) + cc * 8);
+        *(uint4*)(smem + ((lane < 16 ? tK : tV) - sK) + tile_off(row, cc)) = w;
+      }
+      __syncthreads();
+    }
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
     for (int ks = 0; ks < 8; ks++) {
@@ -630,7 +723,7 @@ int k_attn_prefill(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf1
 // Keys per block. All blocks of a launch take about the same time, so the grid runs in waves of
 // (blocks resident per SM) x (SM count): the chunk is the multiple of the tile size that
 // minimises waves x (tiles per chunk + per-block overhead) for a full cache, among the chunk
-// sizes that leave at most 8 (16 for very few pairs) chunks per sequence. The attn_blocks_per_sm option restores the
+// sizes that leave at most 8 chunks per sequence. The attn_blocks_per_sm option restores the
 // plain "that many blocks per SM" rule.
 static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
   const int per_sm = ctx->opt.attn_blocks_per_sm;
@@ -646,9 +739,10 @@ static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
   static int resident_of[64] = {};  // blocks of the kernel an SM holds, per device
   const size_t smem_dec = 2 * DEC_STAGES * KT * 256;
   once.run(ctx->device, [&] {
-    cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dec);
+    cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dec);
+    cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dec);
     int r = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, attn_decode_kernel, 128, smem_dec) != cudaSuccess || r < 1) r = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, attn_decode_kernel<true>, 128, smem_dec) != cudaSuccess || r < 1) r = 1;
     resident_of[ctx->device & 63] = r;
     return cudaSuccess;
   });
@@ -656,10 +750,10 @@ static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
   const int64_t slots = (int64_t)ctx->sm_count * resident, pairs = (int64_t)B * Hkv;
   int best = tiles;
   double best_cost = 1e30;
-  // at most 8 chunks per sequence; 16 where 8 per (sequence, head) pair would not even fill one wave
-  // (few KV heads per rank under tensor parallelism), served by the general merge kernel
-  const int max_chunks = pairs * 8 < slots ? 16 : 8;
-  for (int c = (tiles + max_chunks - 1) / max_chunks; c <= tiles; c++) {
+  // At most 8 chunks per sequence: that is what the fast merge kernel takes. 16 chunks for the few
+  // (sequence, head) pairs of TP=8 shortened the attention kernel but the general merge kernel they
+  // need cost more than that (21.9 against 17.0 us per layer for the pair, measured on eight GPUs).
+  for (int c = (tiles + 7) / 8; c <= tiles; c++) {
     if (c < 4 && c < tiles) continue;  // at least 256 keys per block
     const int64_t blocks = pairs * ((tiles + c - 1) / c), waves = (blocks + slots - 1) / slots;
     const double cost = (double)waves * ((double)c + 1.5);
@@ -674,7 +768,7 @@ int sb_attn_decode_splits(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
 size_t sb_attn_decode_scratch(int B, int Hq, int Dh, int nsplit) { return (size_t)B * Hq * nsplit * (Dh + 2) * sizeof(float); }
 
 int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16* vc, const int32_t* lens, int len_add, int B, int Hq, int Hkv,
-                  int Dh, int maxlen, float scale, int nsplit, float* scratch, bf16* out, uint8_t* q_out, float* qscale_out) {
+                  int Dh, int maxlen, float scale, int nsplit, float* scratch, bf16* out, uint8_t* q_out, float* qscale_out, const RopeArgs* rope) {
   if (Dh != D) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: head_dim must be 128");
   if (Hq / Hkv > 16) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: at most 16 query heads per KV head");
   if (Hq * (D / 8) > CB_THREADS * CB_ITEMS) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: at most 64 query heads per rank");
@@ -685,7 +779,19 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
   float* ml_part = scratch + (size_t)B * Hq * nsplit * D;
   if (Hkv > 65535 || B > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: too many heads or sequences");
   dim3 grid(nsplit, Hkv, B);
-  SB_CUDA(sb_launch(ctx, attn_decode_kernel, grid, dim3(128), smem, q, kc, vc, lens, len_add, B, Hq, Hkv, maxlen, chunk, nsplit, scale * LOG2E, o_part, ml_part));
+  if (rope) {
+    // queries, key and value of the new token come from the qkv projection's partial results (see the kernel)
+    if (!rope->part || rope->splits < 1 || rope->splits > 8 || len_add != 1 || Hq / Hkv > 16 || rope->Hq != Hq || rope->Hkv != Hkv ||
+        rope->kcache != kc || rope->vcache != vc || rope->lens != lens)
+      return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: the fused RoPE prologue needs split-K partials (at most 8), one new token and the same caches");
+    RopeFuseArgs rf{rope->part, rope->splits, rope->sx, rope->sw, rope->cos_t, rope->sin_t, rope->qgain, rope->kgain, rope->eps, rope->max_pos,
+                    rope->kcache, rope->vcache};
+    SB_CUDA(sb_launch(ctx, attn_decode_kernel<true>, grid, dim3(128), smem, (const bf16*)nullptr, kc, vc, lens, len_add, B, Hq, Hkv, maxlen, chunk, nsplit,
+                      scale * LOG2E, o_part, ml_part, rf));
+  } else {
+    SB_CUDA(sb_launch(ctx, attn_decode_kernel<false>, grid, dim3(128), smem, q, kc, vc, lens, len_add, B, Hq, Hkv, maxlen, chunk, nsplit, scale * LOG2E,
+                      o_part, ml_part, RopeFuseArgs{}));
+  }
   ctx->launches++;
   if (nsplit <= 8 && Hq <= 32) {
     SB_CUDA(sb_launch(ctx, attn_combine_decode_kernel, dim3(B), dim3((unsigned)(Hq * 32)), 0, (const float*)o_part, (const float*)ml_part, lens, len_add, Hq,
@@ -782,5 +888,5 @@ extern "C" int strictb200_attn_decode_noalloc(strictb200_ctx* ctx, const uint16_
   // Nothing in the scratch has to start at zero: each key chunk a sequence owns is written in full
   // by its block before the combine kernel reads it, and chunks beyond a sequence's length are never read.
   return k_attn_decode(ctx, (const bf16*)q, (const bf16*)kc, (const bf16*)vc, lens, 0, B, Hq, Hkv, Dh, maxlen, scale, nsplit, scratch,
-                       (bf16*)out, nullptr, nullptr);
+                       (bf16*)out, nullptr, nullptr, nullptr);
 }

@@ -315,17 +315,18 @@ int qwen_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
     // qkv projection -> raw split-K partials, consumed by the rope kernel
     int s1 = plan_splits(m, B, nqkv, d);
     PROF(STRICTB200_K_GEMM_QKV, run_gemm(m, B, w.wqkv, b.aq, b.sa, nullptr, 0, b.part, s1, 1));
-    {
-      RopeArgs r;
-      r.part = b.part; r.splits = s1; r.sx = b.sa; r.sw = w.wqkv.s; r.lens = kv->d_lens;
-      r.cos_t = m->rope_cos; r.sin_t = m->rope_sin; r.qgain = w.qn_g; r.kgain = w.kn_g; r.eps = c.eps;
-      r.Hq = m->Hq_l; r.Hkv = m->Hkv_l; r.D = (int)D; r.maxlen = kv->maxlen; r.max_pos = c.max_pos;
-      r.q_out = b.qb; r.kcache = kv_k(kv, l); r.vcache = kv_v(kv, l);
-      PROF(STRICTB200_K_ROPE, k_rope_qknorm_kvappend(ctx, r, B));
-    }
+    RopeArgs r;
+    r.part = b.part; r.splits = s1; r.sx = b.sa; r.sw = w.wqkv.s; r.lens = kv->d_lens;
+    r.cos_t = m->rope_cos; r.sin_t = m->rope_sin; r.qgain = w.qn_g; r.kgain = w.kn_g; r.eps = c.eps;
+    r.Hq = m->Hq_l; r.Hkv = m->Hkv_l; r.D = (int)D; r.maxlen = kv->maxlen; r.max_pos = c.max_pos;
+    r.q_out = b.qb; r.kcache = kv_k(kv, l); r.vcache = kv_v(kv, l);
+    // QK-norm, RoPE and the cache append inside the attention kernel (one kernel less per layer), or as a kernel of their own.
+    // The merge kernel overwrites b.sa (the o_proj operand's scales) only after every attention block has read it.
+    const bool fuse_rope = ctx->opt.fuse_rope && s1 <= 8 && m->Hq_l / m->Hkv_l <= 16;
+    if (!fuse_rope) PROF(STRICTB200_K_ROPE, k_rope_qknorm_kvappend(ctx, r, B));
     // split-KV attention over len+1 keys; the combine emits the quantised o_proj input
     PROF(STRICTB200_K_ATTN, k_attn_decode(ctx, b.qb, kv_k(kv, l), kv_v(kv, l), kv->d_lens, 1, (int)B, m->Hq_l, m->Hkv_l, (int)D, kv->maxlen,
-                                          scale, kv->nsplit, b.attn_ws, b.att, b.aq, b.sa));
+                                          scale, kv->nsplit, b.attn_ws, b.att, b.aq, b.sa, fuse_rope ? &r : nullptr));
     // o_proj -> partials -> (all-reduce) -> residual + norm2 + quantise
     int s2 = plan_splits(m, B, d, nq);
     PROF(STRICTB200_K_GEMM_O, run_gemm(m, B, w.wo, b.aq, b.sa, nullptr, 0, b.part, s2, 1));

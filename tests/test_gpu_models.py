@@ -334,3 +334,28 @@ def test_qwen3_8b_decode_properties_full_size(ctx, oracle):
     assert runs[0].min() >= 0 and runs[0].max() < cfg["vocab"]
     assert kv.decode_bytes() > 17_000_000_000  # 7.57 GB of weights + ~9.7 GB of KV at this context
     kv.dispose(), m.dispose()
+
+
+@pytest.mark.parametrize("cfg,B,S,lens", [(TINY_QWEN_TIED, 5, 70, [70, 1, 33, 64, 65]), (Q8_SHAPED, 3, 100, [100, 63, 64])], ids=["tied-ragged", "q8-shaped"])
+def test_rope_inside_attention_equals_rope_kernel(ctx, oracle, cfg, B, S, lens):
+    """The decode step computes QK-norm, RoPE and the cache append inside the attention kernel
+    (option fuse_rope, the default) with the arithmetic of the RoPE kernel, operation for
+    operation: tokens, logits and the appended cache rows' effect on later steps are identical
+    bit for bit to the step that runs the RoPE kernel by itself. Sequence lengths cross the 64-key
+    tile and the key-chunk boundaries during the steps (63, 64, 65 -> ...)."""
+    m = sb.Model(ctx, cfg).init_random(3)
+    toks = oracle.gen_tokens(8, 1, B * S, cfg["vocab"]).reshape(B, S)
+    runs = []
+    for fused in (1, 0):
+        for graph in (True, False):
+            with ctx.option("fuse_rope", fused):
+                m.set_graph(graph)
+                kv = m.new_cache(B, S + 80)
+                first, _ = kv.prefill(toks, np.array(lens, np.int32))
+                ids = kv.generate(first, 70)
+                last, logits = kv.decode_step(ids[-1], want_logits=True)
+                runs.append((ids, last, logits))
+                kv.dispose()
+    for ids, last, logits in runs[1:]:
+        assert np.array_equal(ids, runs[0][0]) and np.array_equal(last, runs[0][1]) and np.array_equal(logits, runs[0][2])
+    m.dispose()
