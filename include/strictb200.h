@@ -89,7 +89,9 @@ int strictb200_flush_l2(strictb200_ctx* ctx);
  * "gemm_pair" (many-token GEMM on SM pairs, 1), "prefetch" (1), "deep_ring" (1),
  * "attn_blocks_per_sm" (0), "split_target" (0), "tp_two_shot" (fused all-reduce in two shots,
  * -1: from four ranks on), "wait_limit" (polls of a cross-rank wait before it gives up,
- * 4194304), "prefill_chunk" (token rows per prefill chunk, 16384), "host_timeout_ms" (under tensor
+ * 4194304), "prefill_chunk" (token rows per prefill chunk, 16384), "fuse_rope" (decode attention applies
+ * QK-norm and RoPE and appends to the cache itself, 0), "blur_rows" (image rows per block of the
+ * blur kernel, 0 = 8), "host_timeout_ms" (under tensor
  * parallelism: a synchronising call polls the stream and NCCL's asynchronous error state and, after
  * this many milliseconds, aborts the communicator and returns ERR_TIMEOUT instead of waiting for
  * ever; 0 = wait without limit). Unknown name -> ERR_INVALID_ARG.

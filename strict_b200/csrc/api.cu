@@ -29,6 +29,7 @@ const OptionName kOptions[] = {
     {"tp_two_shot", &SbOptions::tp_two_shot},
     {"wait_limit", &SbOptions::wait_limit},
     {"prefill_chunk", &SbOptions::prefill_chunk},
+    {"blur_rows", &SbOptions::blur_rows},
     {"host_timeout_ms", &SbOptions::host_timeout_ms},
     {"fuse_rope", &SbOptions::fuse_rope},
 };

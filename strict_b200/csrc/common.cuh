@@ -57,7 +57,8 @@ struct SbOptions {
   int tp_two_shot = -1;        // fused all-reduce: 0 one shot, 1 two shots
   int wait_limit = 1 << 22;    // polls of a cross-rank wait before the kernel gives up and sets the error word
   int prefill_chunk = 16384;   // token rows per prefill chunk
-  int fuse_rope = 1;           // decode step: QK-norm, RoPE and the cache append run inside the attention kernel
+  int fuse_rope = 0;           // decode step: QK-norm, RoPE and the cache append inside the attention kernel (bit-identical; measured no faster)
+  int blur_rows = 0;           // rows of the image per block of the blur kernel; 0 = chosen from the image and the grid
   int host_timeout_ms = 0;     // >0: a synchronising call gives up after this long, aborts the NCCL communicator and returns ERR_TIMEOUT
 };
 

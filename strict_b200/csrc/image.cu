@@ -13,13 +13,13 @@
 // written per colour member). The blur is also close to the integer-issue limit, so the fast
 // kernel keeps two 16-bit sums per 32-bit register (25 x 255 fits 16 bits, so packed adds never
 // carry between the lanes), is separable (horizontal 5-sums per row, a sliding window of five
-// rows down a column strip), and divides by 25 with one multiply and shift.
+// rows down a column strip), shares the sums of neighbouring taps between outputs, and divides by
+// 25 on the floating-point pipe, which the integer-bound kernel leaves idle.
 #include "common.cuh"
 
 namespace {
 
-constexpr int BLUR_ROWS = 32;     // output rows per block (plus 4 rows of halo read again)
-constexpr int BLUR_THREADS = 128; // threads per block, 16 output bytes each
+constexpr int BLUR_THREADS = 128; // threads per block, one 16-byte chunk of a row each
 
 // Bytes i and i+1 of a window of 32-bit words as two 16-bit lanes (i is a compile-time constant
 // after unrolling). Inside one word the zero bytes come from a zero second operand of the byte
@@ -30,44 +30,63 @@ __device__ __forceinline__ uint32_t pair_at(const uint32_t* w, int i) {
   return __byte_perm(w[word], w[word + 1], 3u | (4u << 8)) & 0x00FF00FFu;
 }
 
-// sum / 25 for sum <= 6375, exactly: 5243 / 2^17 is 1/25 from above by less than 1/(25 * 6376).
-__device__ __forceinline__ uint32_t div25(uint32_t s) { return (s * 5243u) >> 17; }
+// sum / 25 for sum <= 6375, exactly, in one fused multiply-add on the floating-point pipe (the
+// kernel is bound by the integer pipe). The sum enters a float through its mantissa:
+// f = 2^23 + 22 * 2^16 + s (bit pattern BLUR_MAGIC | s). With m = 0.04 rounded up to the next float,
+// m * (2^23 + 22 * 2^16) = 393216.0278..., so m * f - 393216 = s / 25 + d with 0.0278 <= d < 0.0279
+// for every s <= 6375: always inside [s/25, s/25 + 1/25), hence its floor is the quotient. Adding
+// 1.5 * 2^23 - 393216 (an integer, exact as a float) with round-toward-zero leaves that floor in
+// the low mantissa bits. Checked against integer division for all 6376 sums (tests).
+constexpr uint32_t BLUR_MAGIC = 0x4B160000u;
+__device__ __forceinline__ uint32_t div25_bits(uint32_t magic_bits) {
+  return __float_as_uint(__fmaf_rz(__uint_as_float(magic_bits), __uint_as_float(0x3D23D70Bu), 12189696.0f));
+}
 
-// Interior of the image: rows [2, H-2), bytes [x0, x1) of every such row with x0 >= 6,
-// x1 <= stride - 6, both multiples of 16. A thread owns 16 consecutive bytes of a row strip and
-// walks BLUR_ROWS output rows down, keeping the horizontal sums of the last five input rows.
-__global__ void __launch_bounds__(BLUR_THREADS) blur5x5_rgb8_interior_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
-                                                                             int64_t stride, int height, int64_t x0, int64_t x1) {
+// Interior of the image: rows [2, H-2), bytes [x0, x1) of every such row with x0 >= 16,
+// x1 <= stride - 16, both multiples of 16. A thread owns 16 consecutive bytes of a row strip and
+// walks `rows_per_block` output rows down, keeping the horizontal sums of the last five input
+// rows; the loads of the next input row are issued before the current one is worked on. 72
+// registers: seven blocks of 128 threads per SM.
+__global__ void __launch_bounds__(BLUR_THREADS, 7) blur5x5_rgb8_interior_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                                             int64_t stride, int height, int64_t x0, int64_t x1, int rows_per_block) {
   const int64_t x = x0 + ((int64_t)blockIdx.x * BLUR_THREADS + threadIdx.x) * 16;
   if (x >= x1) return;
-  const int row_begin = 2 + blockIdx.y * BLUR_ROWS;
-  int row_end = row_begin + BLUR_ROWS;
+  const int row_begin = 2 + blockIdx.y * rows_per_block;
+  int row_end = row_begin + rows_per_block;
   if (row_end > height - 2) row_end = height - 2;
   // h[r % 5][p]: horizontal 5-sums of input row r for output byte pairs p (bytes 2p, 2p+1 of the 16)
   uint32_t h[5][8];
   uint32_t v[8];
 #pragma unroll
   for (int p = 0; p < 8; p++) v[p] = 0;
-  auto hsum_row = [&](int r, uint32_t* out) {
-    // bytes x-16 .. x+31 of row r as twelve words (three aligned 16-byte loads; the neighbours'
-    // loads of the same lines hit in L1)
+  // bytes x-16 .. x+31 of a row as three aligned 16-byte loads (the neighbours' loads of the same lines hit in L1)
+  struct Row { uint4 a, b, c; };
+  auto load_row = [&](int r) {
     const uint4* p = (const uint4*)(src + (int64_t)r * stride + x);
-    const uint4 a = __ldg(p - 1), b = __ldg(p), c = __ldg(p + 1);
-    const uint32_t w[12] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w, c.x, c.y, c.z, c.w};
+    return Row{__ldg(p - 1), __ldg(p), __ldg(p + 1)};
+  };
+  auto hsum_row = [&](const Row& in, uint32_t* out) {
+    const uint32_t w[12] = {in.a.x, in.a.y, in.a.z, in.a.w, in.b.x, in.b.y, in.b.z, in.b.w, in.c.x, in.c.y, in.c.z, in.c.w};
     // Byte 0 of the window is x-16, so output byte j is window byte 16+j and its five taps are
-    // window bytes 10+j, 13+j, 16+j, 19+j, 22+j; output pair q covers j = 2q, 2q+1.
+    // window bytes 10+j, 13+j, 16+j, 19+j, 22+j; output pair q covers j = 2q, 2q+1. The sum of
+    // two neighbouring taps, t(i) = pair(i) + pair(i+3), serves two outputs: out(q) = t(10+2q) + t(16+2q) + pair(22+2q),
+    // and t(16+2q) is t(10+2(q+3)).
+    uint32_t t[11];
 #pragma unroll
-    for (int q = 0; q < 8; q++)
-      out[q] = pair_at(w, 10 + 2 * q) + pair_at(w, 13 + 2 * q) + pair_at(w, 16 + 2 * q) + pair_at(w, 19 + 2 * q) + pair_at(w, 22 + 2 * q);
+    for (int i = 0; i < 11; i++) t[i] = pair_at(w, 10 + 2 * i) + pair_at(w, 13 + 2 * i);
+#pragma unroll
+    for (int q = 0; q < 8; q++) out[q] = t[q] + t[q + 3] + pair_at(w, 22 + 2 * q);
   };
   // prime the window with input rows row_begin-2 .. row_begin+1
+  {
+    Row r0 = load_row(row_begin - 2), r1 = load_row(row_begin - 1), r2 = load_row(row_begin), r3 = load_row(row_begin + 1);
+    hsum_row(r0, h[0]); hsum_row(r1, h[1]); hsum_row(r2, h[2]); hsum_row(r3, h[3]);
 #pragma unroll
-  for (int i = 0; i < 4; i++) {
-    const int r = row_begin - 2 + i;
-    hsum_row(r, h[i]);
+    for (int i = 0; i < 4; i++)
 #pragma unroll
-    for (int p = 0; p < 8; p++) v[p] += h[i][p];
+      for (int p = 0; p < 8; p++) v[p] += h[i][p];
   }
+  Row next = load_row(row_begin + 2);  // row_begin + 2 <= height - 1
   // five output rows per turn, so that every index into the ring of row sums is a constant
   for (int base = row_begin; base < row_end; base += 5) {
 #pragma unroll
@@ -75,15 +94,20 @@ __global__ void __launch_bounds__(BLUR_THREADS) blur5x5_rgb8_interior_kernel(con
       const int r = base + i;
       if (r < row_end) {
         const int slot = (i + 4) % 5;  // holds input row r+2 from now on; it held row r-3, already taken out of v
-        hsum_row(r + 2, h[slot]);
+        const Row cur = next;
+        if (r + 1 < row_end) next = load_row(r + 3);  // in flight while row r+2 is summed and row r is written
+        hsum_row(cur, h[slot]);
         uint32_t q[4];
 #pragma unroll
-        for (int p = 0; p < 8; p++) {
+        for (int p = 0; p < 8; p += 2) {
           v[p] += h[slot][p];
-          const uint32_t two = div25(v[p] & 0xFFFFu) | (div25(v[p] >> 16) << 8);
-          if (p & 1) q[p >> 1] |= two << 16; else q[p >> 1] = two;
+          v[p + 1] += h[slot][p + 1];
+          // the four sums of an output word as floats 2^23 + s: low lanes by mask, high lanes by byte permute
+          const uint32_t b0 = div25_bits((v[p] & 0xFFFFu) | BLUR_MAGIC), b1 = div25_bits(__byte_perm(v[p], BLUR_MAGIC, 0x7632));
+          const uint32_t b2 = div25_bits((v[p + 1] & 0xFFFFu) | BLUR_MAGIC), b3 = div25_bits(__byte_perm(v[p + 1], BLUR_MAGIC, 0x7632));
+          q[p >> 1] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
         }
-        *(uint4*)(dst + (int64_t)r * stride + x) = make_uint4(q[0], q[1], q[2], q[3]);
+        __stcs((uint4*)(dst + (int64_t)r * stride + x), make_uint4(q[0], q[1], q[2], q[3]));  // written once, not read again by this kernel
 #pragma unroll
         for (int p = 0; p < 8; p++) v[p] -= h[i][p];  // input row r-2 leaves the window
       }
@@ -165,10 +189,16 @@ int k_blur5x5_rgb8(strictb200_ctx* ctx, const uint8_t* src, uint8_t* dst, int wi
   const bool fast = height > 4 && stride % 16 == 0 && xb > xa && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0;
   if (!fast) xa = xb = stride;  // everything through the generic kernel (xa bytes on the left, none on the right)
   if (fast) {
-    const int64_t chunks = (xb - xa) / 16;
-    dim3 grid((unsigned)((chunks + BLUR_THREADS - 1) / BLUR_THREADS), (unsigned)((height - 4 + BLUR_ROWS - 1) / BLUR_ROWS));
-    if (grid.y > 65535) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "blur: image taller than 2 million rows");
-    blur5x5_rgb8_interior_kernel<<<grid, BLUR_THREADS, 0, ctx->stream>>>(src, dst, stride, height, xa, xb);
+    const int64_t chunks = (xb - xa) / 16, strips = (chunks + BLUR_THREADS - 1) / BLUR_THREADS;
+    // Rows per block. A block reads four rows of halo again and sums them again, so taller blocks
+    // do less work in total; measured on 8192 x 8192 they are slower all the same (111 us at 8 rows,
+    // 113 at 16, 119 at 32, 134 at 64, 138 at 128): with short blocks the blocks that run at one
+    // time cover a narrow band of the image that moves down it, the halo rows are found in L2, and
+    // small images still give every SM several blocks. The option blur_rows overrides the choice.
+    const int rows = ctx->opt.blur_rows > 0 ? ctx->opt.blur_rows : 8;
+    dim3 grid((unsigned)strips, (unsigned)((height - 4 + rows - 1) / rows));
+    if (grid.y > 65535) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "blur: too many blocks of rows for one launch (raise the option blur_rows)");
+    blur5x5_rgb8_interior_kernel<<<grid, BLUR_THREADS, 0, ctx->stream>>>(src, dst, stride, height, xa, xb, rows);
     SB_LAUNCHED(ctx);
   }
   const int border_rows = height < 4 ? height : 4;

@@ -109,3 +109,23 @@ def test_blur_larger_than_l2_properties(ctx, oracle):
     top = oracle.blur5x5_rgb8(host.reshape(h, w * 3)[:40].reshape(-1), w, 40).reshape(40, w * 3)
     assert np.array_equal(got[:38], top[:38])
     a.free(), b.free()
+
+
+def test_blur_division_covers_every_sum(ctx, oracle):
+    """The strip kernel divides by 25 with one floating-point multiply-add; its exactness argument
+    holds for every window sum 0..6375, so an image is built whose interior windows take every one
+    of those sums (a brightness ramp across the columns, with seeded noise), the coverage is
+    checked on the host, and the result is compared with the oracle's integer division."""
+    w, h = 2048, 96
+    rng = np.random.default_rng(25)
+    level = np.repeat(np.linspace(-20.0, 275.0, w), 3)[None, :]
+    px = np.clip(np.rint(level + rng.normal(0.0, 12.0, (h, w * 3))), 0, 255).astype(np.uint8)
+    img = px.reshape(h, w, 3).astype(np.int64)
+    sums = sum(img[2 + dy:h - 2 + dy, 2 + dx:w - 2 + dx] for dy in range(-2, 3) for dx in range(-2, 3))
+    assert np.array_equal(np.unique(sums), np.arange(6376)), np.setdiff1d(np.arange(6376), sums)[:10]
+    want = oracle.blur5x5_rgb8(px.reshape(-1), w, h)
+    assert np.array_equal(want.reshape(h, w, 3)[2:-2, 2:-2], sums // 25)  # the oracle divides as integers
+    for rows in (0, 8, 64):
+        with ctx.option("blur_rows", rows):
+            got = sb.blur5x5_rgb8(ctx, px.reshape(-1), w, h)
+        assert np.array_equal(got, want), np.flatnonzero(got != want)[:10]

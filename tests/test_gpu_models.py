@@ -343,6 +343,7 @@ def test_rope_inside_attention_equals_rope_kernel(ctx, oracle, cfg, B, S, lens):
     operation: tokens, logits and the appended cache rows' effect on later steps are identical
     bit for bit to the step that runs the RoPE kernel by itself. Sequence lengths cross the 64-key
     tile and the key-chunk boundaries during the steps (63, 64, 65 -> ...)."""
+    cfg = dict(cfg, max_pos=256)
     m = sb.Model(ctx, cfg).init_random(3)
     toks = oracle.gen_tokens(8, 1, B * S, cfg["vocab"]).reshape(B, S)
     runs = []
