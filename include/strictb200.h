@@ -190,6 +190,22 @@ int strictb200_gemm_fp8(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, co
 /* bf16 activations in (split inside, using context scratch); bf16 out. */
 int strictb200_gemm_fp8w(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const uint16_t* d_x_bf16, const uint8_t* d_wq,
                          const float* d_sw, uint16_t* d_y_bf16, int kernel);
+/* ---- int8-weight linear layer (no reference counterpart; new surface) ----
+ * y = (x . Wq^T) * sw with bf16 x, signed 8-bit Wq and one fp32 scale per output channel
+ * (absmax / 127). The integer tensor cores take the activations as two int8 terms per element,
+ * x ~ s * (128 * hi + lo) with s a power of two per token (|x| / s <= 16256, hi in [-127, 127],
+ * lo in [-64, 63]; exact for every element within a factor 63 of the row's largest); the sums are exact 32-bit integers joined in 64 bits, so the result does
+ * not depend on how K is split and equals the CPU restatement bit for bit. The split buffer has
+ * the layout of strictb200_quantize_rows (groups of 8 tokens: 8 hi rows, 8 lo rows).
+ * K % 128 == 0, K <= 131072, N % 16 == 0. */
+int strictb200_quantize_weights_int8(strictb200_ctx* ctx, const float* d_w, int64_t N, int64_t K, int8_t* d_wq, float* d_sw);
+int strictb200_quantize_rows_int8(strictb200_ctx* ctx, const uint16_t* d_x_bf16, int64_t M, int64_t K, int8_t* d_split, float* d_scale);
+/* Y[M,N] bf16 from the split of M rows (above). */
+int strictb200_gemm_int8(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const int8_t* d_split, const float* d_sx, const int8_t* d_wq,
+                         const float* d_sw, uint16_t* d_y_bf16);
+/* bf16 activations in (split inside, using context scratch); bf16 out. */
+int strictb200_gemm_int8w(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const uint16_t* d_x_bf16, const int8_t* d_wq, const float* d_sw,
+                          uint16_t* d_y_bf16);
 /* fp32 Y[M,N] = X[M,K] . W[N,K]^T + bias[N] (bias may be NULL). */
 int strictb200_gemm_f32(strictb200_ctx* ctx, int64_t M, int64_t N, int64_t K, const float* d_x, const float* d_w,
                         const float* d_bias, float* d_y);

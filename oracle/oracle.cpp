@@ -833,6 +833,67 @@ void or_adjust_brightness(float* flat, int64_t offset, int64_t count, int flat_w
     }
 }
 
+// int8-weight linear layer (numerics contract of the integer path; no reference counterpart, so
+// unpinned like the FP8 path, but every intermediate is an exact integer and the device result
+// must equal this one bit for bit):
+//  * weights: one fp32 scale per output channel, sw = absmax / 127 (1 for a row of zeros),
+//    q = round-to-nearest-even(w / sw) clamped to [-127, 127];
+//  * activations: per token, s = the smallest power of two with absmax / s <= 16256 (1 for a row of
+//    zeros), v = round-to-nearest-even(x / s) (exact scaling), carried as v = 128 * hi + lo with
+//    hi = floor((v + 64) / 128) in [-127, 127] and lo in [-64, 63];
+//  * y = bf16(((float)(128 * sum_k hi*q + sum_k lo*q) * s) * sw): integer sums, one conversion to
+//    fp32 (round to nearest even), two fp32 products, one rounding to bf16.
+void or_quantize_weights_int8(const float* w, int64_t N, int64_t K, int8_t* q, float* sw) {
+#pragma omp parallel for schedule(static)
+  for (int64_t n = 0; n < N; n++) {
+    float amax = 0.f;
+    for (int64_t k = 0; k < K; k++) amax = std::max(amax, std::fabs(w[n * K + k]));
+    const float s = amax > 0.f ? amax / 127.f : 1.f;
+    sw[n] = s;
+    for (int64_t k = 0; k < K; k++) {
+      int v = (int)std::nearbyint(w[n * K + k] / s);
+      q[n * K + k] = (int8_t)std::min(127, std::max(-127, v));
+    }
+  }
+}
+// x: bf16-valued fp32 rows. hi, lo: [M, K]; scale: [M].
+void or_quantize_rows_int8(const float* x, int64_t M, int64_t K, int8_t* hi, int8_t* lo, float* scale) {
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; m++) {
+    float amax = 0.f;
+    for (int64_t k = 0; k < K; k++) amax = std::max(amax, std::fabs(x[m * K + k]));
+    float s = 1.f;
+    if (amax > 0.f) {
+      int e;
+      const float mant = std::frexp(amax, &e);
+      s = std::ldexp(1.f, mant <= 0.9921875f ? e - 14 : e - 13);
+    }
+    scale[m] = s;
+    const float inv = 1.f / s;
+    for (int64_t k = 0; k < K; k++) {
+      const int v = (int)std::nearbyint(x[m * K + k] * inv);
+      const int h = (v + 64) >> 7;
+      hi[m * K + k] = (int8_t)h;
+      lo[m * K + k] = (int8_t)(v - h * 128);
+    }
+  }
+}
+// out: bf16 bit patterns [M, N].
+void or_gemm_int8w(const float* x, const int8_t* wq, const float* sw, int64_t M, int64_t N, int64_t K, uint16_t* out) {
+  std::vector<int8_t> hi((size_t)M * K), lo((size_t)M * K);
+  std::vector<float> sx((size_t)M);
+  or_quantize_rows_int8(x, M, K, hi.data(), lo.data(), sx.data());
+#pragma omp parallel for schedule(static)
+  for (int64_t n = 0; n < N; n++)
+    for (int64_t m = 0; m < M; m++) {
+      int64_t sh = 0, sl = 0;
+      const int8_t *h = &hi[(size_t)m * K], *l = &lo[(size_t)m * K], *w = wq + n * K;
+      for (int64_t k = 0; k < K; k++) { sh += (int)h[k] * (int)w[k]; sl += (int)l[k] * (int)w[k]; }
+      const float v = (float)(sh * 128 + sl);
+      out[m * N + n] = f32_to_bf16((v * sx[m]) * sw[n]);
+    }
+}
+
 // Benchmark set-up only: positions [0,len) of every sequence get cheap pseudo-random values in
 // [-1,1) (a multiplicative hash of the element index; the values do not matter for timing) and
 // the lengths are set to len, so that a decode step at a long context can be timed without the

@@ -209,6 +209,38 @@ def linear_fp8w(x, wq, sw):
     return out
 
 
+def quantize_weights_int8(w):
+    """int8 weights with one fp32 scale per output channel (absmax / 127)."""
+    w = _f32(w)
+    N, K = w.shape
+    q = np.empty((N, K), np.int8)
+    s = np.empty(N, np.float32)
+    lib().or_quantize_weights_int8(_p(w), C.c_int64(N), C.c_int64(K), _p(q), _p(s))
+    return q, s
+
+
+def quantize_rows_int8(x):
+    """Two int8 terms per element of bf16-valued rows, x ~ s * (128 * hi + lo): (hi, lo, s)."""
+    x = _f32(x)
+    M, K = x.shape
+    hi = np.empty((M, K), np.int8)
+    lo = np.empty((M, K), np.int8)
+    s = np.empty(M, np.float32)
+    lib().or_quantize_rows_int8(_p(x), C.c_int64(M), C.c_int64(K), _p(hi), _p(lo), _p(s))
+    return hi, lo, s
+
+
+def gemm_int8w(x, wq, sw):
+    """bf16 bit patterns of ((x . Wq^T) * sx) * sw with bf16-valued x and int8 weights."""
+    x = _f32(x)
+    M, K = x.shape
+    wq = np.ascontiguousarray(wq, dtype=np.int8)
+    N = wq.shape[0]
+    out = np.empty((M, N), np.uint16)
+    lib().or_gemm_int8w(_p(x), _p(wq), _p(_f32(sw)), C.c_int64(M), C.c_int64(N), C.c_int64(K), _p(out))
+    return out
+
+
 def gemm_f32(x, w, b=None):
     x, w = _f32(x), _f32(w)
     M, K = x.shape

@@ -249,6 +249,7 @@ struct GemmArgs {
   int splits = 1;
   int raw = 0;                  // 1: always write raw accumulators to part, even for splits == 1
   int kernel = 0;               // 0 auto, 1 skinny, 2 mma.sync tiles, 3 tcgen05
+  int i8 = 0;                   // 1: int8 weights and two int8 activation terms (gemm_int8.cu); part then holds int32 sums [splits][2][M,N]
 };
 int k_gemm_fp8(strictb200_ctx*, const GemmArgs& a);
 int sb_gemm_pick_splits(strictb200_ctx*, int64_t M, int64_t N, int64_t K);

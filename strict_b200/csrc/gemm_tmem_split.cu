@@ -74,6 +74,16 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t tmem_d, uint64_t desc_a, uint
       : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+// Signed 8-bit integer operands, 32-bit integer accumulator (same operand layout and K = 32 per instruction).
+__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -104,7 +114,10 @@ struct TmemArgs {
   int prefetch;  // issue the first ring of weight loads before the dependency wait
 };
 
-template <int BT, int STAGES>
+// I8: both operands are signed 8-bit integers (weights int8, activations as two int8 terms
+// x = s * (128 * hi + lo), gemm_int8.cu) and the accumulators 32-bit integers; the epilogue joins
+// the two terms in 64-bit integers, so the result does not depend on the K split or on any order.
+template <int BT, int STAGES, bool I8>
 __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                                                         TmemArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -168,8 +181,9 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // instruction descriptor: D = F32 (bits 4-5 = 1), A = B = E4M3 (0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
-      constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BT >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
+      // instruction descriptor: D = F32 (bits 4-5 = 1), A = B = E4M3 (0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24;
+      // integers: D = S32 (bits 4-5 = 2), A (bits 7-9) = B (bits 10-12) = signed 8 bit (1)
+      constexpr uint32_t idesc = (I8 ? (2u << 4) | (1u << 7) | (1u << 10) : (1u << 4)) | ((uint32_t)(BT >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
       // The operand tiles cannot arrive before the producer's dependency wait has returned; waiting for the same
       // dependency here keeps the bounded waits below for progress inside this kernel (a predecessor that itself
       // waits for another rank may take longer than any of them).
@@ -184,7 +198,8 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; k++) {
           // +32 bytes of K inside the swizzle atom = +2 in the (address >> 4) field
-          tc_mma_f8(tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc, (kb | k) ? 1u : 0u);
+          if (I8) tc_mma_i8(tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc, (kb | k) ? 1u : 0u);
+          else tc_mma_f8(tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc, (kb | k) ? 1u : 0u);
         }
         tc_commit(smem_u32(&bar_empty[s]));  // stage is free once these MMAs have read it
       }
@@ -211,7 +226,20 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < 8; j++) {
           int tok = tok0 + j;
-          if (tok < a.M && n < a.N) {
+          if (I8) {
+            if (tok < a.M && n < a.N) {
+              if (raw) {  // the two integer sums of this K range, [split][hi, lo][token][channel]
+                int32_t* part = (int32_t*)a.part;
+                part[(((int64_t)blockIdx.z * 2 + 0) * a.M + tok) * a.N + n] = (int32_t)r[j];
+                part[(((int64_t)blockIdx.z * 2 + 1) * a.M + tok) * a.N + n] = (int32_t)r[8 + j];
+              } else {
+                const float v = __ll2float_rn((int64_t)(int32_t)r[j] * 128 + (int64_t)(int32_t)r[8 + j]);
+                const float y = __fmul_rn(__fmul_rn(v, a.sx[tok]), swn);
+                if (a.out_f32) ((float*)a.out)[(int64_t)tok * a.N + n] = y;
+                else ((bf16*)a.out)[(int64_t)tok * a.N + n] = __float2bfloat16_rn(y);
+              }
+            }
+          } else if (tok < a.M && n < a.N) {
             float v = __fadd_rn(__uint_as_float(r[j]), __fmul_rn(0.0625f, __uint_as_float(r[8 + j])));
             if (raw) {
               a.part[((int64_t)blockIdx.z * a.M + tok) * a.N + n] = v;
@@ -259,18 +287,18 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_
   return STRICTB200_OK;
 }
 
-template <int BT, int STAGES>
+template <int BT, int STAGES, bool I8 = false>
 int launch(strictb200_ctx* ctx, const GemmArgs& g, const TmemArgs& ta) {
   constexpr int STAGE_BYTES = BN * BK + BT * BK;
   size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;  // + slack for the 1024-byte round-up
   static SbDeviceOnce once;  // one per instantiation
-  SB_CUDA(once.run(ctx->device, [&] { return cudaFuncSetAttribute(gemm_tmem_kernel<BT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); }));
+  SB_CUDA(once.run(ctx->device, [&] { return cudaFuncSetAttribute(gemm_tmem_kernel<BT, STAGES, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); }));
   CUtensorMap mw, mx;
   SB_TRY(make_map(&mw, g.wq, g.N, g.K, g.ldw, BN));
   SB_TRY(make_map(&mx, g.xq, ta.Mq, g.K, g.ldx, BT));
   dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((ta.Mq + BT - 1) / BT), (unsigned)g.splits);
   if (grid.y > 65535) return sb_fail(STRICTB200_ERR_INVALID_ARG, "gemm_fp8: M too large for one launch");
-  SB_CUDA(sb_launch(ctx, gemm_tmem_kernel<BT, STAGES>, grid, dim3(192), smem, mw, mx, ta));
+  SB_CUDA(sb_launch(ctx, gemm_tmem_kernel<BT, STAGES, I8>, grid, dim3(192), smem, mw, mx, ta));
   ctx->launches++;
   return STRICTB200_OK;
 }
@@ -291,6 +319,12 @@ int k_gemm_fp8_tmem_split(strictb200_ctx* ctx, const GemmArgs& g) {
   // per SM resident.
   const int64_t blocks = ((g.N + BN - 1) / BN) * g.splits;
   const int deep = ctx->opt.deep_ring;
+  if (g.i8) {  // integer operands: the same tiles; token tiles beyond the first go to grid.y
+    if (ta.Mq <= 32) return launch<32, 5, true>(ctx, g, ta);
+    if (ta.Mq <= 64) return launch<64, 4, true>(ctx, g, ta);
+    if (ta.Mq <= 128) return launch<128, 4, true>(ctx, g, ta);
+    return launch<256, 4, true>(ctx, g, ta);
+  }
   if (ta.Mq <= 32) return deep && blocks <= ctx->sm_count ? launch<32, 10>(ctx, g, ta) : launch<32, 5>(ctx, g, ta);
   if (ta.Mq <= 64) return deep && blocks <= ctx->sm_count ? launch<64, 9>(ctx, g, ta) : launch<64, 4>(ctx, g, ta);
   if (ta.Mq <= 128) return launch<128, 4>(ctx, g, ta);

@@ -89,6 +89,49 @@ def gemm_cases(ctx, iters, shape=None):
         sw.free()
 
 
+def gemm_int8_cases(ctx, iters):
+    """The int8-weight linear layer (tcgen05 kind::i8) on the two microbenchmark shapes; weights
+    N(0, 0.02) from the seeded generator quantised on the device, activations split beforehand."""
+    hbm, bf16_tf, kind = _peaks()
+    for N_, K in ((4096, 4096), (14336, 4096)):
+        copies = max(2, int(np.ceil(300e6 / (N_ * K))))
+        wf = DV(ctx, N_ * K)
+        wq = [DV(ctx, N_ * K, np.int8) for _ in range(copies)]
+        sw = DV(ctx, N_)
+        for i, w in enumerate(wq):
+            N.check(L().strictb200_gen_normal_f32(ctx.h, 2, 10 + i, 0, N_ * K, 0.02, wf.p))
+            N.check(L().strictb200_quantize_weights_int8(ctx.h, wf.p, N_, K, w.p, sw.p))
+        wf.free()
+        for M in (1, 8, 32, 128, 2048):
+            x = DV(ctx, M * K, np.uint16)
+            N.check(L().strictb200_gen_normal_bf16(ctx.h, 2, 99, 0, M * K, 1.0, x.p))
+            y = DV(ctx, M * N_, np.uint16)
+            rows = 16 * ((M + 7) // 8)
+            xq, sx = DV(ctx, rows * K, np.int8), DV(ctx, M)
+            N.check(L().strictb200_quantize_rows_int8(ctx.h, x.p, M, K, xq.p, sx.p))
+            for it in range(copies):
+                N.check(L().strictb200_gemm_int8(ctx.h, M, N_, K, xq.p, sx.p, wq[it].p, sw.p, y.p))
+            ctx.synchronize()
+            with ctx.record():
+                for it in range(copies):
+                    N.check(L().strictb200_gemm_int8(ctx.h, M, N_, K, xq.p, sx.p, wq[it].p, sw.p, y.p))
+            graph = ctx.last_graph
+            ms, clocks = timed(ctx, lambda reps: ctx.replay(graph, reps), max(1, iters // copies))
+            ms /= copies
+            ctx.free_graph(graph)
+            byts = N_ * K + 4 * N_ + 2 * M * K + 2 * M * N_
+            flops = 2.0 * M * N_ * K
+            print(json.dumps({"case": "gemm_int8w", "M": M, "N": N_, "K": K, "us": ms * 1e3, "GBps": byts / ms / 1e6, "hbm_frac": byts / ms / 1e6 / hbm,
+                              "useful_TOPs": flops / ms / 1e9, "executed_int8_TOPs": 2 * flops / ms / 1e9, "peaks": kind, "clocks": clocks,
+                              "note": "split of the activations not included; weights rotate over %d copies; the K-split sum is a second kernel" % copies}),
+                  flush=True)
+            for v in (x, y, xq, sx):
+                v.free()
+        for w in wq:
+            w.free()
+        sw.free()
+
+
 def attn_cases(ctx, iters):
     hbm, bf16_tf, kind = _peaks()
     Hq, Hkv, D = 32, 8, 128
@@ -266,6 +309,8 @@ def main():
     ctx = Context(0)
     if "gemm" in args.what:
         gemm_cases(ctx, args.iters, tuple(int(v) for v in args.shape.split(",")) if args.shape else None)
+    if "int8" in args.what:
+        gemm_int8_cases(ctx, args.iters)
     if "attn" in args.what:
         attn_cases(ctx, args.iters)
     if "ew" in args.what:

@@ -70,6 +70,10 @@ SIGNATURES = {
     "strictb200_quantize_rows": [vp, vp, i64, i64, vp, vp],
     "strictb200_gemm_fp8": [vp, i64, i64, i64, vp, vp, vp, vp, vp, i32, i32],
     "strictb200_gemm_fp8w": [vp, i64, i64, i64, vp, vp, vp, vp, i32],
+    "strictb200_quantize_weights_int8": [vp, vp, i64, i64, vp, vp],
+    "strictb200_quantize_rows_int8": [vp, vp, i64, i64, vp, vp],
+    "strictb200_gemm_int8": [vp, i64, i64, i64, vp, vp, vp, vp, vp],
+    "strictb200_gemm_int8w": [vp, i64, i64, i64, vp, vp, vp, vp],
     "strictb200_gemm_f32": [vp, i64, i64, i64, vp, vp, vp, vp],
     "strictb200_rmsnorm": [vp, vp, vp, vp, f32, i64, i64, vp],
     "strictb200_layernorm": [vp, vp, vp, vp, f32, i64, i64, vp],

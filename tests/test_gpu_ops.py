@@ -287,6 +287,64 @@ def test_gemm_fp8w_entry(ctx, oracle, rng):
     assert np.abs(got - want).max() <= np.abs(want).max() * 2 ** -7 and (got != want).mean() < 1e-3
 
 
+@pytest.mark.parametrize("M,N_,K", [(1, 512, 1024), (8, 4096, 4096), (32, 1536, 4096), (33, 144, 256), (128, 4096, 12288), (200, 1024, 1024),
+                                    (300, 256, 128), (2048, 512, 512)])
+def test_gemm_int8w_bit_exact(ctx, oracle, rng, M, N_, K):
+    """int8 weights on the integer tensor cores (tcgen05 kind::i8): quantisers and linear layer
+    equal the CPU restatement bit for bit, for one and several K splits, one and several token
+    tiles, token counts that are not multiples of 8 and channel counts that are not multiples of
+    the 128-channel tile."""
+    x = oracle.round_bf16(rng.standard_normal((M, K)).astype(np.float32) * rng.choice([1e-2, 1.0, 50.0], (M, 1)).astype(np.float32))
+    if M > 2:
+        x[2] = 0.0
+    w = (rng.standard_normal((N_, K)) * 0.02).astype(np.float32)
+    w[min(5, N_ - 1)] = 0.0
+    wq, sw = oracle.quantize_weights_int8(w)
+    dw, dwq, dsw = DV.of(ctx, w), DV(ctx, N_ * K, np.int8), DV(ctx, N_)
+    N.check(L().strictb200_quantize_weights_int8(ctx.h, dw.p, N_, K, dwq.p, dsw.p))
+    assert np.array_equal(dwq.to_host().reshape(N_, K), wq) and np.array_equal(dsw.to_host(), sw)
+    hi, lo, s = oracle.quantize_rows_int8(x)
+    rows = 16 * ((M + 7) // 8)
+    dx, dsplit, dsx = bf16_dev(ctx, oracle, x), DV(ctx, rows * K, np.int8), DV(ctx, M)
+    N.check(L().strictb200_memset(ctx.h, dsplit.p, 0x55, rows * K))  # the padding rows must be written too
+    N.check(L().strictb200_quantize_rows_int8(ctx.h, dx.p, M, K, dsplit.p, dsx.p))
+    split = dsplit.to_host().reshape(rows // 16, 2, 8, K)
+    want_split = np.zeros((rows // 16 * 8, 2, K), np.int8)
+    want_split[:M, 0], want_split[:M, 1] = hi, lo
+    assert np.array_equal(split, want_split.reshape(rows // 16, 8, 2, K).transpose(0, 2, 1, 3)) and np.array_equal(dsx.to_host(), s)
+    want = oracle.gemm_int8w(x, wq, sw)
+    dy = DV(ctx, M * N_, np.uint16)
+    N.check(L().strictb200_gemm_int8w(ctx.h, M, N_, K, dx.p, dwq.p, dsw.p, dy.p))
+    got = dy.to_host().reshape(M, N_)
+    assert np.array_equal(got, want), (np.argwhere(got != want)[:5], (got != want).sum())
+    N.check(L().strictb200_memset(ctx.h, dy.p, 0, M * N_ * 2))
+    N.check(L().strictb200_gemm_int8(ctx.h, M, N_, K, dsplit.p, dsx.p, dwq.p, dsw.p, dy.p))
+    assert np.array_equal(dy.to_host().reshape(M, N_), want)
+    for v in (dw, dwq, dsw, dx, dsplit, dsx, dy):
+        v.free()
+
+
+def test_gemm_int8w_extreme_sums(ctx, oracle):
+    """Every product at its largest magnitude over the longest K of the configurations: the hi and
+    lo sums stay inside 32 bits and the joined 64-bit value is converted once."""
+    M, N_, K = 8, 256, 12288
+    x = np.full((M, K), 16256.0, np.float32)
+    x[1] = -x[1]
+    x[2, ::2] = 63.0 * 2.0 ** -7 * 128  # lo at its largest with hi zero
+    w = np.ones((N_, K), np.float32)
+    w[1::2] = -1.0
+    wq, sw = oracle.quantize_weights_int8(w)
+    assert np.abs(wq).min() == 127
+    want = oracle.gemm_int8w(x, wq, sw)
+    dx, dwq, dsw, dy = bf16_dev(ctx, oracle, x), DV.of(ctx, wq), DV.of(ctx, sw), DV(ctx, M * N_, np.uint16)
+    N.check(L().strictb200_gemm_int8w(ctx.h, M, N_, K, dx.p, dwq.p, dsw.p, dy.p))
+    got = dy.to_host().reshape(M, N_)
+    assert np.array_equal(got, want)
+    assert oracle.bf16_to_f32(got)[0, 0] == oracle.round_bf16(np.float32(16256.0 * K))
+    for v in (dx, dwq, dsw, dy):
+        v.free()
+
+
 @pytest.mark.parametrize("M,N_,K", [(1, 2304, 768), (3, 50257, 768), (128, 768, 3072), (9, 10, 4), (5, 7, 1500), (2, 13, 8200)])
 def test_gemm_f32_vs_oracle(ctx, oracle, rng, M, N_, K):
     x = rng.standard_normal((M, K)).astype(np.float32)

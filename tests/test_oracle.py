@@ -418,3 +418,35 @@ def test_noise_floor_of_the_numerics_contract_at_qwen3_8b_width(oracle):
     mean_rel = err.mean() / np.abs(logits[0]).mean()
     assert 3e-3 < mean_rel < 2e-2, mean_rel   # at or above the 5e-3 bar's order of magnitude, far above fp32 noise (1e-6)
     assert err.max() < 5e-2                    # the max-abs bar of the FP8 path still holds
+
+
+def test_int8_weight_linear_contract(oracle, rng):
+    """The integer path's restatement against plain numpy integer arithmetic: ranges of the two
+    activation terms, exactness of the split for elements within a factor 63 of the row's largest, the
+    weight quantiser, and the linear layer as exact integer sums (float64 holds them exactly)."""
+    M, N, K = 5, 48, 256
+    x = oracle.round_bf16(rng.standard_normal((M, K)).astype(np.float32) * np.array([[1e-3], [1.0], [300.0], [0.0], [7.0]], np.float32))
+    x[4, 3] = 16256.0 * 2.0 ** -6  # a row maximum whose mantissa is the largest that keeps the smaller scale
+    hi, lo, s = oracle.quantize_rows_int8(x)
+    assert hi.min() >= -127 and hi.max() <= 127 and lo.min() >= -64 and lo.max() <= 63
+    assert s[3] == 1.0 and not hi[3].any() and not lo[3].any()
+    v = 128 * hi.astype(np.int64) + lo
+    assert np.abs(v).max() <= 16256 and (np.log2(s) % 1 == 0).all()
+    amax = np.abs(x).max(axis=1, keepdims=True)
+    assert (np.abs(v).max(axis=1)[[0, 1, 2, 4]] > 8128).all()  # the smallest power of two that fits
+    rec = v * s[:, None].astype(np.float64)
+    big = np.abs(x) >= amax / 63  # |x| / s >= 128: the eight significant bits of a bf16 value are all kept
+    assert np.array_equal(rec[big], x.astype(np.float64)[big])
+    assert (np.abs(rec - x) <= s[:, None] / 2).all()
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    w[7] = 0.0
+    wq, sw = oracle.quantize_weights_int8(w)
+    assert np.array_equal(sw, np.where(np.abs(w).max(axis=1) > 0, np.abs(w).max(axis=1) / np.float32(127), np.float32(1)).astype(np.float32))
+    assert np.array_equal(wq, np.clip(np.rint(w / sw[:, None]), -127, 127).astype(np.int8)) and np.abs(wq).max() == 127 and not wq[7].any()
+    got = oracle.gemm_int8w(x, wq, sw)
+    t = (v @ wq.astype(np.int64).T).astype(np.float32)  # exact integers, one rounding to fp32
+    want = oracle.f32_to_bf16((t * s[:, None]) * sw[None, :])
+    assert np.array_equal(got, want)
+    # and the quantised layer stays close to the unquantised one
+    ref = x.astype(np.float64) @ w.astype(np.float64).T
+    assert np.abs(oracle.bf16_to_f32(got) - ref).max() <= 0.02 * np.abs(ref).max()
