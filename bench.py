@@ -253,6 +253,22 @@ def run_ours(args, rank, world, local_rank):
     e2e = {"value": BATCH * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": BATCH * 4, "d2h_bytes_per_step": BATCH * 4,
            "ms_per_step": e2e_s / args.steps * 1e3}
 
+    # ---- optional: where one graph-replayed step's time goes, from per-block time stamps (outside every timed region)
+    timeline = None
+    if args.timeline:
+        from strict_b200 import timeline as TL
+        with ctx.trace(1 << 18) as tr:
+            kv.decode_steps_device(1)
+        Hkv_t, D_t = cfg["n_kv_heads"] // world, cfg["head_dim"]
+        d_t, I_t, nq_t = cfg["d_model"], cfg["d_ff"] // world, cfg["n_q_heads"] // world * D_t
+        names = {(nq_t + 2 * Hkv_t * D_t, d_t): "gemm_qkv", (d_t, nq_t): "gemm_o", (2 * I_t, d_t): "gemm_gate_up", (d_t, I_t): "gemm_down",
+                 (cfg["vocab"] // world, d_t): "head"}
+        ll = TL.launches(tr.records, names)
+        timeline = {"blocks_reported": tr.reported, "launches": len(ll), "span_us": (ll[-1]["end"] / 1e3) if ll else 0.0,
+                    "exposed_us": {k: [v[0] / 1e3, v[1]] for k, v in TL.per_kernel(ll).items()}}
+        with open(args.timeline + f".rank{rank}" if world > 1 else args.timeline, "w") as f:
+            json.dump({"summary": timeline, "launches": ll}, f)
+
     # ---- per-kernel-class device times of the same step (plain launches, CUDA events on the launch stream)
     prof = kv.profile_decode(4)
     lens_now = kv.lens()
@@ -298,6 +314,8 @@ def run_ours(args, rank, world, local_rank):
                       "cuda_graph": not args.no_graph, "kv": "synthetic" if args.synthetic_kv else "prefill of the seeded prompts"},
             "roofline": roofline, "kernels": kernels, "e2e": e2e, "sustained": sustained, "gpu_launches": int(launches), "clocks": clocks,
             "device_status": status}
+    if timeline:
+        line["timeline"] = timeline
     if base:
         line["cpu_baseline"] = base
     sys.stdout.flush()
@@ -323,6 +341,7 @@ def main():
     ap.add_argument("--no-sustained", action="store_true", help="skip the 256-step sustained leg")
     ap.add_argument("--nccl-allreduce", action="store_true", help="decode all-reduces through NCCL instead of the fused peer-memory exchange")
     ap.add_argument("--two-shot", type=int, default=-1, help="fused all-reduce: 0 one shot, 1 two shots (default: two from four ranks on)")
+    ap.add_argument("--timeline", default=None, help="write the per-launch timeline of one graph-replayed decode step (per-block time stamps) to this file")
     ap.add_argument("--no-graph", action="store_true", help="plain launches instead of CUDA-graph replay of the decode step")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

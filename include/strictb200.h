@@ -82,6 +82,18 @@ int strictb200_launch_count(strictb200_ctx* ctx, uint64_t* out);
 int strictb200_device_status(strictb200_ctx* ctx, int* out);
 /* Writes `bytes` to a private buffer (> L2) so the next kernel starts with a cold L2. */
 int strictb200_flush_l2(strictb200_ctx* ctx);
+/* Diagnostics: time stamps of the decode step's kernels, per block. Between _trace_begin and
+ * _trace_end thread 0 of every block of the instrumented kernels (decode GEMM, row kernels, RoPE,
+ * decode attention and its merge, SwiGLU) stores eight 64-bit words: the global timer in ns at block
+ * start, after the block's dependency wait, at block end, (kernel id | tag << 8 | SM << 48), up to
+ * three optional marks inside the kernel (0 when unused) and a zero,
+ * with ids 1 GEMM, 2 row kernel, 3 RoPE, 4 attention, 5 merge, 6 SwiGLU, 7 row kernel with the
+ * fused all-reduce; the tag tells launches of one kernel apart (GEMM: N ^ K << 12). A recorded
+ * graph can be replayed under a trace as it is. _trace_end copies at most max_records records
+ * (8 words each) and returns in *out_count how many blocks reported. One trace per process at a
+ * time (the switch is a device variable). The reference has no counterpart. */
+int strictb200_trace_begin(strictb200_ctx* ctx, int capacity);
+int strictb200_trace_end(strictb200_ctx* ctx, uint64_t* out_records, int max_records, int* out_count);
 /* Switches of a context. Each is read ONCE from the environment variable STRICTB200_<NAME IN
  * CAPITALS> when the context is created; no launch path reads the environment. -1 = the
  * library's own choice. Names: "pdl" (programmatic dependent launch, 1), "attn_tc" (prefill
@@ -90,7 +102,9 @@ int strictb200_flush_l2(strictb200_ctx* ctx);
  * "attn_blocks_per_sm" (0), "split_target" (0), "tp_two_shot" (fused all-reduce in two shots,
  * -1: from four ranks on), "wait_limit" (polls of a cross-rank wait before it gives up,
  * 4194304), "prefill_chunk" (token rows per prefill chunk, 16384), "fuse_rope" (decode attention applies
- * QK-norm and RoPE and appends to the cache itself, 0), "blur_rows" (image rows per block of the
+ * QK-norm and RoPE and appends to the cache itself, 0), "row_cluster" (blocks of one cluster that share a row in the decode row
+ * kernels, 4), "attn_prefetch" (decode attention loads its first key/value
+ * tiles before the dependency wait, 1), "blur_rows" (image rows per block of the
  * blur kernel, 0 = 8), "host_timeout_ms" (under tensor
  * parallelism: a synchronising call polls the stream and NCCL's asynchronous error state and, after
  * this many milliseconds, aborts the communicator and returns ERR_TIMEOUT instead of waiting for

@@ -29,6 +29,8 @@ const OptionName kOptions[] = {
     {"tp_two_shot", &SbOptions::tp_two_shot},
     {"wait_limit", &SbOptions::wait_limit},
     {"prefill_chunk", &SbOptions::prefill_chunk},
+    {"row_cluster", &SbOptions::row_cluster},
+    {"attn_prefetch", &SbOptions::attn_prefetch},
     {"blur_rows", &SbOptions::blur_rows},
     {"host_timeout_ms", &SbOptions::host_timeout_ms},
     {"fuse_rope", &SbOptions::fuse_rope},
@@ -122,7 +124,46 @@ __global__ void flush_kernel(uint4* p, size_t n) {
   for (; i < n; i += stride) p[i] = make_uint4((uint32_t)i, 0u, 0u, 0u);
 }
 
+int sb_trace_set_gemm_split(const SbTraceDev&);  // one per instrumented translation unit
+int sb_trace_set_norm(const SbTraceDev&);
+int sb_trace_set_rope(const SbTraceDev&);
+int sb_trace_set_attention(const SbTraceDev&);
+static int trace_set_all(const SbTraceDev& t) {
+  return sb_trace_set_gemm_split(t) | sb_trace_set_norm(t) | sb_trace_set_rope(t) | sb_trace_set_attention(t);
+}
+
 extern "C" {
+
+int strictb200_trace_begin(strictb200_ctx* ctx, int capacity) {
+  SB_ENTER(ctx);
+  SB_REQUIRE(capacity > 0 && capacity <= (1 << 24), "capacity must be between 1 and 2^24 records");
+  SB_REQUIRE(!ctx->trace_rec, "a trace is already armed on this context");
+  SB_TRY(sb_sync(ctx, "trace_begin"));
+  SB_CUDA(cudaMalloc(&ctx->trace_rec, (size_t)capacity * 64));
+  SB_CUDA(cudaMalloc(&ctx->trace_count, 256));
+  SB_CUDA(cudaMemset(ctx->trace_count, 0, 256));
+  ctx->trace_capacity = (unsigned)capacity;
+  if (trace_set_all(SbTraceDev{ctx->trace_rec, ctx->trace_count, ctx->trace_capacity})) return sb_fail(STRICTB200_ERR_CUDA, "trace: cannot set the device variables");
+  return STRICTB200_OK;
+}
+
+int strictb200_trace_end(strictb200_ctx* ctx, uint64_t* out_records, int max_records, int* out_count) {
+  SB_ENTER(ctx);
+  SB_REQUIRE(ctx->trace_rec, "no trace is armed on this context");
+  SB_REQUIRE(out_count && (out_records || max_records == 0), "null pointer");
+  int st = sb_sync(ctx, "trace_end");
+  trace_set_all(SbTraceDev{nullptr, nullptr, 0});
+  unsigned n = 0;
+  cudaMemcpy(&n, ctx->trace_count, 4, cudaMemcpyDeviceToHost);
+  *out_count = (int)n;  // blocks that reported, also beyond the capacity
+  unsigned take = n < ctx->trace_capacity ? n : ctx->trace_capacity;
+  if ((int)take > max_records) take = (unsigned)max_records;
+  if (take) cudaMemcpy(out_records, ctx->trace_rec, (size_t)take * 64, cudaMemcpyDeviceToHost);
+  cudaFree(ctx->trace_rec);
+  cudaFree(ctx->trace_count);
+  ctx->trace_rec = nullptr; ctx->trace_count = nullptr; ctx->trace_capacity = 0;
+  return st;
+}
 
 int strictb200_version(void) { return STRICTB200_VERSION; }
 const char* strictb200_last_error(void) { return g_last_error.c_str(); }

@@ -282,6 +282,13 @@ __device__ __forceinline__ uint2 rope_head_bf16(const RopeFuseArgs& r, int B, in
   return make_uint2(f32_to_bf16_bits(o[0]) | (f32_to_bf16_bits(o[1]) << 16), f32_to_bf16_bits(o[2]) | (f32_to_bf16_bits(o[3]) << 16));
 }
 
+// A length that the previous step's last kernel writes: read around every cache, before and after the dependency wait.
+__device__ __forceinline__ int ld_volatile_i32(const int32_t* p) {
+  int v;
+  asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // grid (nsplit, Hkv, B), 128 threads. Warp w owns keys [16w,16w+16) of every 64-key tile.
 // scratch: o_part [B][Hq][nsplit][128] then ml_part [B][Hq][nsplit][2].
 // FUSED: the queries do not come from memory; every block computes the (at most 16) query heads of
@@ -293,15 +300,43 @@ template <bool FUSED>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                                                           const int32_t* __restrict__ lens, int len_add, int B, int Hq, int Hkv, int maxlen,
                                                           int chunk, int nsplit, float scale_log2, float* __restrict__ o_part,
-                                                          float* __restrict__ ml_part, RopeFuseArgs rf) {
+                                                          float* __restrict__ ml_part, RopeFuseArgs rf, int prefetch) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(16) bf16 q_s[FUSED ? 16 * D : 8];    // the query heads of this KV head
   __shared__ __align__(16) bf16 kv_new[FUSED ? 2 * D : 8];  // the new token's key row, then its value row
+  SB_TRACE_BEGIN();
   pdl_trigger();
-  pdl_wait();
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
-  const int len = min(lens[b] + len_add, maxlen);
   const int k_begin = split * chunk;
+  const uint32_t sK = smem_u32(smem), sV = sK + DEC_STAGES * KT * 256;
+  const bf16* kbase = kc + ((int64_t)b * Hkv + hk) * maxlen * D;
+  const bf16* vbase = vc + ((int64_t)b * Hkv + hk) * maxlen * D;
+  const uint64_t kv_policy = l2_evict_first_policy();
+  // Before the dependency wait: the first tiles of this block's keys and values start to stream
+  // while the preceding kernels (the qkv projection's tail, RoPE) still run. Only rows that were
+  // written in earlier steps are touched, never the block's last tile (it may hold the row the
+  // preceding kernel appends), and the length they are derived from is read again after the wait:
+  // if it changed, the tiles are loaded again from scratch.
+  const int len_early = min(ld_volatile_i32(lens + b) + len_add, maxlen);
+  int npre = 0;
+  if (prefetch && k_begin < len_early) {
+    const int nt = (min(len_early, k_begin + chunk) - k_begin + KT - 1) / KT;
+    npre = min(DEC_STAGES - 1, nt - 1);
+    for (int t = 0; t < npre; t++) {
+      const int k0 = k_begin + t * KT;
+      load_tile_hint(sK + t * KT * 256, kbase + (int64_t)k0 * D, KT, KT, 128, kv_policy);
+      load_tile_hint(sV + t * KT * 256, vbase + (int64_t)k0 * D, KT, KT, 128, kv_policy);
+      cp_async_commit();
+    }
+  }
+  pdl_wait();
+  SB_TRACE_WAITED();
+  const int len = min(ld_volatile_i32(lens + b) + len_add, maxlen);
+  if (len != len_early && npre) {  // not expected: the length belongs to the previous step
+    cp_async_wait<0>();
+    __syncthreads();
+    npre = 0;
+  }
   if (k_begin >= len) return;
   const int k_end = min(len, k_begin + chunk);
   const int G = Hq / Hkv;
@@ -309,15 +344,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
   // FUSED: position of the new token = the sequence's length before this step; its row is the last key
   const int p_new = FUSED ? len - 1 : -1;
   const bool owns_new = FUSED && p_new >= k_begin && p_new < k_end && p_new < rf.max_pos;
-  const uint32_t sK = smem_u32(smem), sV = sK + DEC_STAGES * KT * 256;
-  const bf16* kbase = kc + ((int64_t)b * Hkv + hk) * maxlen * D;
-  const bf16* vbase = vc + ((int64_t)b * Hkv + hk) * maxlen * D;
   const int ntiles = (k_end - k_begin + KT - 1) / KT;
 
-  const uint64_t kv_policy = l2_evict_first_policy();
   // prologue: the first DEC_STAGES-1 tiles are in flight before any is consumed (one group per tile)
-#pragma unroll
-  for (int t = 0; t < DEC_STAGES - 1; t++) {
+  for (int t = npre; t < DEC_STAGES - 1; t++) {
     if (t < ntiles) {
       int k0 = k_begin + t * KT;
       load_tile_hint(sK + t * KT * 256, kbase + (int64_t)k0 * D, KT, min(KT, k_end - k0), 128, kv_policy);
@@ -483,6 +513,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
     o_part[idx * D + d] = O;
     if (d == 0) { ml_part[idx * 2] = M; ml_part[idx * 2 + 1] = L; }
   }
+  SB_TRACE_END(SB_K_ATTN, 0);
 }
 
 // grid B, 512 threads: merge the key chunks of every head of one token. A thread owns 8
@@ -549,12 +580,16 @@ __global__ void __launch_bounds__(CB_THREADS) attn_combine_kernel(const float* _
 __global__ void __launch_bounds__(1024) attn_combine_decode_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                                                                    const int32_t* __restrict__ lens, int len_add, int Hq, int maxlen, int chunk,
                                                                    int nsplit, bf16* __restrict__ out, uint8_t* __restrict__ q_out,
-                                                                   float* __restrict__ qscale) {
+                                                                   float* __restrict__ qscale, int* __restrict__ status) {
   __shared__ float red[32];
+  __shared__ __align__(8) ClusterExchange xch;
+  SB_TRACE_BEGIN();
+  if (gridDim.y > 1) cluster_exchange_init(&xch);  // the blocks of one cluster share a token (some of its heads each)
   pdl_trigger();
   pdl_wait();
+  SB_TRACE_WAITED();
   const int b = blockIdx.x;
-  const int e4 = threadIdx.x, h = e4 >> 5, d = (e4 & 31) * 4;
+  const int e4 = blockIdx.y * blockDim.x + threadIdx.x, h = e4 >> 5, d = (e4 & 31) * 4;
   const int64_t base = ((int64_t)b * Hq + h) * nsplit;
   const int len_raw = lens[b];
   float2 ml[8];
@@ -586,11 +621,17 @@ __global__ void __launch_bounds__(1024) attn_combine_decode_kernel(const float* 
     amax = fmaxf(amax, fabsf(v[i]));
   }
   *(uint2*)(out + ((int64_t)b * Hq + h) * D + d) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
-  if (!q_out) return;
-  amax = block_max(amax, red);
-  const int ex = sb_scale_exponent(amax);
-  if (threadIdx.x == 0) qscale[b] = sb_pow2(ex);
-  sb_store_split4(q_out, (int64_t)Hq * D, b, (int64_t)e4 * 4, v, sb_pow2(-ex));
+  if (q_out) {
+    amax = block_max(amax, red);
+    if (gridDim.y > 1) {
+      if (!cluster_exchange(&xch, amax, gridDim.y, blockIdx.y, 0) && threadIdx.x == 0) { *(volatile int*)status = 6; __threadfence_system(); }
+      for (uint32_t r = 0; r < gridDim.y; r++) amax = fmaxf(amax, ((volatile float*)xch.slot[0])[r]);
+    }
+    const int ex = sb_scale_exponent(amax);
+    if (blockIdx.y == 0 && threadIdx.x == 0) qscale[b] = sb_pow2(ex);
+    sb_store_split4(q_out, (int64_t)Hq * D, b, (int64_t)e4 * 4, v, sb_pow2(-ex));
+  }
+  SB_TRACE_END(SB_K_COMBINE, 0);
 }
 
 // ------------------------------------------------------------------ fp32 attention (GPT-2 path)
@@ -720,6 +761,8 @@ int k_attn_prefill(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf1
   return STRICTB200_OK;
 }
 
+SB_TRACE_TU(attention)
+
 // Keys per block. All blocks of a launch take about the same time, so the grid runs in waves of
 // (blocks resident per SM) x (SM count): the chunk is the multiple of the tile size that
 // minimises waves x (tiles per chunk + per-block overhead) for a full cache, among the chunk
@@ -787,15 +830,21 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
     RopeFuseArgs rf{rope->part, rope->splits, rope->sx, rope->sw, rope->cos_t, rope->sin_t, rope->qgain, rope->kgain, rope->eps, rope->max_pos,
                     rope->kcache, rope->vcache};
     SB_CUDA(sb_launch(ctx, attn_decode_kernel<true>, grid, dim3(128), smem, (const bf16*)nullptr, kc, vc, lens, len_add, B, Hq, Hkv, maxlen, chunk, nsplit,
-                      scale * LOG2E, o_part, ml_part, rf));
+                      scale * LOG2E, o_part, ml_part, rf, ctx->opt.attn_prefetch));
   } else {
     SB_CUDA(sb_launch(ctx, attn_decode_kernel<false>, grid, dim3(128), smem, q, kc, vc, lens, len_add, B, Hq, Hkv, maxlen, chunk, nsplit, scale * LOG2E,
-                      o_part, ml_part, RopeFuseArgs{}));
+                      o_part, ml_part, RopeFuseArgs{}, ctx->opt.attn_prefetch));
   }
   ctx->launches++;
   if (nsplit <= 8 && Hq <= 32) {
-    SB_CUDA(sb_launch(ctx, attn_combine_decode_kernel, dim3(B), dim3((unsigned)(Hq * 32)), 0, (const float*)o_part, (const float*)ml_part, lens, len_add, Hq,
-                      maxlen, chunk, nsplit, out, q_out, qscale_out));
+    // blocks per token (one cluster): 8 heads = 256 threads each
+    const unsigned per_tok = q_out && ctx->opt.row_cluster > 1 && Hq % 8 == 0 ? (unsigned)std::min(ctx->opt.row_cluster, Hq / 8) : 1u;
+    if (per_tok > 1 && Hq % per_tok == 0)
+      SB_CUDA(sb_launch_cluster(ctx, attn_combine_decode_kernel, dim3(B, per_tok), dim3((unsigned)(Hq * 32 / per_tok)), 0, dim3(1, per_tok, 1), (const float*)o_part,
+                                (const float*)ml_part, lens, len_add, Hq, maxlen, chunk, nsplit, out, q_out, qscale_out, ctx->d_status));
+    else
+      SB_CUDA(sb_launch(ctx, attn_combine_decode_kernel, dim3(B), dim3((unsigned)(Hq * 32)), 0, (const float*)o_part, (const float*)ml_part, lens, len_add, Hq,
+                        maxlen, chunk, nsplit, out, q_out, qscale_out, ctx->d_status));
     ctx->launches++;
     return STRICTB200_OK;
   }

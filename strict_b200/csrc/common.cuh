@@ -58,6 +58,8 @@ struct SbOptions {
   int wait_limit = 1 << 22;    // polls of a cross-rank wait before the kernel gives up and sets the error word
   int prefill_chunk = 16384;   // token rows per prefill chunk
   int fuse_rope = 0;           // decode step: QK-norm, RoPE and the cache append inside the attention kernel (bit-identical; measured no faster)
+  int row_cluster = 4;         // blocks (one cluster) per row of the decode row kernels, where the row has 1024 columns per block; 0 or 1 = one block per row
+  int attn_prefetch = 1;       // decode attention starts to load its first key/value tiles before the dependency wait
   int blur_rows = 0;           // rows of the image per block of the blur kernel; 0 = chosen from the image and the grid
   int host_timeout_ms = 0;     // >0: a synchronising call gives up after this long, aborts the NCCL communicator and returns ERR_TIMEOUT
 };
@@ -101,6 +103,9 @@ struct strictb200_ctx {
   void* gemm_ws = nullptr;  // stream-K tile counters + partial tiles of the tensor-memory GEMM
   size_t gemm_count_bytes = 0, gemm_part_bytes = 0;
   SbOptions opt;
+  unsigned long long* trace_rec = nullptr;  // armed trace (strictb200_trace_begin): records, counter, capacity
+  unsigned int* trace_count = nullptr;
+  unsigned int trace_capacity = 0;
   // scratch of the prefill chunks (activations of up to opt.prefill_chunk token rows), grow-only
   void* prefill_ws = nullptr;
   size_t prefill_ws_bytes = 0;
@@ -301,6 +306,53 @@ void sb_tp_abort(strictb200_ctx*);       // ncclCommAbort: stops the communicato
 // Without the launch attribute both are no-ops.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Diagnostics: per-block time stamps of the decode step's kernels. While a trace is armed
+// (strictb200_trace_begin) thread 0 of every block of an instrumented kernel records the global
+// timer at block start, after the dependency wait and at block end, with the SM it ran on; the
+// host reads the records back (strictb200_trace_end). The pointer lives in a device variable of
+// each translation unit (read at run time, so a recorded CUDA graph can be traced as it is); when
+// it is null a block pays one cached load.
+struct SbTraceDev {
+  unsigned long long* rec;  // [capacity][8]: start, after the wait, end, kernel id | tag << 8 | SM << 48, three optional marks inside the kernel, 0
+  unsigned int* count;
+  unsigned int capacity;
+};
+static __device__ SbTraceDev sb_trace_dev;
+#define SB_TRACE_TU(name) \
+  int sb_trace_set_##name(const SbTraceDev& t) { return cudaMemcpyToSymbol(sb_trace_dev, &t, sizeof t) == cudaSuccess ? 0 : 1; }
+enum { SB_K_GEMM = 1, SB_K_ROWNORM = 2, SB_K_ROPE = 3, SB_K_ATTN = 4, SB_K_COMBINE = 5, SB_K_SWIGLU = 6, SB_K_ROWNORM_TP = 7 };
+__device__ __forceinline__ unsigned long long sb_globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void sb_trace_emit(int kid, uint32_t tag, const unsigned long long* marks) {
+  if (!marks[0]) return;
+  const unsigned long long t2 = sb_globaltimer();
+  unsigned int smid;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+  const unsigned int i = atomicAdd(sb_trace_dev.count, 1u);
+  if (i < sb_trace_dev.capacity) {
+    unsigned long long* r = sb_trace_dev.rec + (size_t)i * 8;
+    r[0] = marks[0]; r[1] = marks[1]; r[2] = t2;
+    r[3] = (unsigned long long)kid | ((unsigned long long)tag << 8) | ((unsigned long long)smid << 48);
+    r[4] = marks[2]; r[5] = marks[3]; r[6] = marks[4]; r[7] = 0;
+  }
+}
+// In a kernel: SB_TRACE_BEGIN() first, SB_TRACE_WAITED() by thread 0 right after its pdl_wait(), SB_TRACE_END(id, tag) last;
+// SB_TRACE_MARK(0..2) stamps a point in between (as thread 0 reaches it).
+#define SB_TRACE_BEGIN()                                 \
+  __shared__ unsigned long long sb_tr_[5];               \
+  if (threadIdx.x == 0) {                                \
+    sb_tr_[0] = sb_trace_dev.rec ? sb_globaltimer() : 0; \
+    sb_tr_[1] = sb_tr_[2] = sb_tr_[3] = sb_tr_[4] = 0;   \
+  }
+#define SB_TRACE_WAITED() \
+  if (threadIdx.x == 0 && sb_tr_[0]) sb_tr_[1] = sb_globaltimer();
+#define SB_TRACE_MARK(i) \
+  if (threadIdx.x == 0 && sb_tr_[0]) sb_tr_[2 + (i)] = sb_globaltimer();
+#define SB_TRACE_END(kid, tag) \
+  if (threadIdx.x == 0) sb_trace_emit(kid, (uint32_t)(tag), sb_tr_);
 // L2 eviction policy for data that is read exactly once per step (weights, the KV cache): such
 // lines are the first to be replaced, so the 126 MB L2 keeps the small tensors the kernels hand
 // to each other, the scale/gain vectors and the kernels' own instructions resident.
@@ -348,29 +400,31 @@ inline cudaError_t sb_launch_cluster(strictb200_ctx* ctx, void (*kernel)(KArgs..
 // block that may already have left (measured about 0.4 us, against 0.9 us for a cluster
 // barrier plus remote reads plus a second barrier before exit).
 struct ClusterExchange {
-  float slot[8];
-  unsigned long long bar;
+  float slot[2][8];
+  unsigned long long bar[2];  // one barrier per exchange: a fast block's second value must not count for a slow block's first wait
 };
 // All threads of all blocks call this once at kernel start (before any long wait).
 __device__ __forceinline__ void cluster_exchange_init(ClusterExchange* x) {
   if (threadIdx.x == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&x->bar)));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&x->bar[0])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&x->bar[1])));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
-// All threads of all blocks call this once with a block-uniform value; returns false if the
-// other blocks' values did not arrive within the spin limit (slot[] is then incomplete).
-__device__ __forceinline__ bool cluster_exchange(ClusterExchange* x, float v, uint32_t nblocks, uint32_t rank) {
-  const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&x->bar);
+// All threads of all blocks call this with a block-uniform value, at most once per `which` (0,
+// then 1); returns false if the other blocks' values did not arrive within the spin limit
+// (slot[which][] is then incomplete). Afterwards slot[which][r] holds block r's value in every block.
+__device__ __forceinline__ bool cluster_exchange(ClusterExchange* x, float v, uint32_t nblocks, uint32_t rank, int which = 0) {
+  const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&x->bar[which]);
   if (threadIdx.x == 0) {
-    x->slot[rank] = v;
+    x->slot[which][rank] = v;
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(4u * (nblocks - 1)) : "memory");
   }
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every block's barrier is initialised
+  if (which == 0) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every block's barriers are initialised
   if (threadIdx.x < nblocks && threadIdx.x != rank) {
     uint32_t rslot, rbar;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rslot) : "r"((uint32_t)__cvta_generic_to_shared(&x->slot[rank])), "r"(threadIdx.x));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rslot) : "r"((uint32_t)__cvta_generic_to_shared(&x->slot[which][rank])), "r"(threadIdx.x));
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(bar), "r"(threadIdx.x));
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(rslot), "r"(__float_as_uint(v)), "r"(rbar) : "memory");
   }

@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
+  SB_TRACE_BEGIN();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, t0 = blockIdx.y * BT;
   // split z owns the k-blocks [z * nkb_all / splits, (z + 1) * nkb_all / splits): sizes differ by at most one
@@ -166,6 +167,7 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
         tma_load_2d_hint(smem_u32(smem + (size_t)kb * STAGE_BYTES), &map_w, k_begin + kb * BK, n0, full, w_policy);
       }
       pdl_wait();
+      SB_TRACE_WAITED();
       for (int kb = 0; kb < npre; kb++)
         tma_load_2d(smem_u32(smem + (size_t)kb * STAGE_BYTES) + BN * BK, &map_x, k_begin + kb * BK, t0, smem_u32(&bar_full[kb]));
       for (int kb = npre; kb < nkb; kb++) {
@@ -259,6 +261,7 @@ __global__ void __launch_bounds__(192) gemm_tmem_kernel(const __grid_constant__ 
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
   }
+  SB_TRACE_END(SB_K_GEMM, (uint32_t)a.N ^ ((uint32_t)a.K << 12));
 }
 
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -304,6 +307,8 @@ int launch(strictb200_ctx* ctx, const GemmArgs& g, const TmemArgs& ta) {
 }
 
 }  // namespace
+
+SB_TRACE_TU(gemm_split)
 
 int k_gemm_fp8_tmem_split(strictb200_ctx* ctx, const GemmArgs& g) {
   if (g.K % BK || g.splits < 1 || g.splits > g.K / BK)

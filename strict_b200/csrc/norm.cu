@@ -106,6 +106,7 @@ struct RowNormDev {
   uint8_t* q;
   float* qscale;
   int two_shot;  // fused all-reduce: owner-reduces-and-returns instead of everyone-sends-to-everyone
+  int* status;   // host-visible error word of the context
 };
 
 __global__ void __launch_bounds__(512) rownorm_kernel(RowNormDev a, int64_t M, int64_t d) {
@@ -235,12 +236,19 @@ __global__ void __launch_bounds__(512) rownorm_kernel(RowNormDev a, int64_t M, i
 template <int MODE>
 __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int64_t M, int64_t d) {
   __shared__ float red[32];
-  const int64_t row = blockIdx.x, k = (int64_t)threadIdx.x * 4;
+  __shared__ __align__(8) ClusterExchange xch;
+  SB_TRACE_BEGIN();
+  // gridDim.y blocks of one cluster share a row (a quarter of its columns each at d = 4096): the row's
+  // partial results then arrive through four SMs' paths to L2 instead of one, and four SMs issue the
+  // arithmetic; the sum of squares and the absolute maximum are exchanged through the cluster.
+  if (gridDim.y > 1) cluster_exchange_init(&xch);
+  const int64_t row = blockIdx.x, k = ((int64_t)blockIdx.y * blockDim.x + threadIdx.x) * 4;
   pdl_trigger();
   float4 sw = make_float4(0.f, 0.f, 0.f, 0.f);
   if (MODE == 0 || MODE == 3) sw = *(const float4*)(a.sw + k);
   const float4 g = *(const float4*)(a.gain + k);
   pdl_wait();
+  SB_TRACE_WAITED();
   float t[4] = {0.f, 0.f, 0.f, 0.f};
   float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
   if (MODE == 0) {
@@ -258,6 +266,7 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
     t[1] += __fmul_rn(__fmul_rn(acc[1], sxr), sw.y);
     t[2] += __fmul_rn(__fmul_rn(acc[2], sxr), sw.z);
     t[3] += __fmul_rn(__fmul_rn(acc[3], sxr), sw.w);
+    SB_TRACE_MARK(0);
   } else if (MODE == 3) {
     // Fused all-reduce, row-granular: this block sums the rank's own split-K partials of its row
     // and exchanges them with the peers as 8-byte packets {value, epoch} pushed into their
@@ -370,6 +379,12 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
   }
   float ss = t[0] * t[0] + t[1] * t[1] + t[2] * t[2] + t[3] * t[3];
   ss = block_sum(ss, red);
+  if (gridDim.y > 1) {
+    if (!cluster_exchange(&xch, ss, gridDim.y, blockIdx.y, 0) && threadIdx.x == 0) { *(volatile int*)a.status = 6; __threadfence_system(); }
+    ss = 0.f;
+    for (uint32_t r = 0; r < gridDim.y; r++) ss += ((volatile float*)xch.slot[0])[r];  // in block order, the same in every block
+  }
+  SB_TRACE_MARK(1);
   const float ms = __fdiv_rn(ss, (float)d);
   const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, a.eps)));
   const float gg[4] = {g.x, g.y, g.z, g.w};
@@ -385,11 +400,18 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
     w.y = f32_to_bf16_bits(t[2]) | (f32_to_bf16_bits(t[3]) << 16);
     *(uint2*)(a.y + row * d + k) = w;
   }
-  if (!a.q) return;
-  amax = block_max(amax, red);
-  const int e = sb_scale_exponent(amax);
-  if (threadIdx.x == 0) a.qscale[row] = sb_pow2(e);
-  sb_store_split4(a.q, d, row, k, t, sb_pow2(-e));
+  if (a.q) {
+    amax = block_max(amax, red);
+    if (gridDim.y > 1) {
+      if (!cluster_exchange(&xch, amax, gridDim.y, blockIdx.y, 1) && threadIdx.x == 0) { *(volatile int*)a.status = 6; __threadfence_system(); }
+      for (uint32_t r = 0; r < gridDim.y; r++) amax = fmaxf(amax, ((volatile float*)xch.slot[1])[r]);
+    }
+    SB_TRACE_MARK(2);
+    const int e = sb_scale_exponent(amax);
+    if (blockIdx.y == 0 && threadIdx.x == 0) a.qscale[row] = sb_pow2(e);
+    sb_store_split4(a.q, d, row, k, t, sb_pow2(-e));
+  }
+  SB_TRACE_END(MODE == 3 ? SB_K_ROWNORM_TP : SB_K_ROWNORM, (uint32_t)((uintptr_t)a.gain >> 4));
 }
 
 
@@ -518,8 +540,10 @@ __global__ void __launch_bounds__(512) swiglu_decode_kernel(const float* __restr
   __shared__ float red[32];
   __shared__ __align__(8) ClusterExchange xch;
   if (gridDim.y > 1) cluster_exchange_init(&xch);
+  SB_TRACE_BEGIN();
   pdl_trigger();
   pdl_wait();
+  SB_TRACE_WAITED();
   const int64_t row = blockIdx.x, k = ((int64_t)blockIdx.y * blockDim.x + threadIdx.x) * 8;
   float g[8], u[8], h[8];
   load8_f32(gu32 + row * 2 * I + k, g);
@@ -534,11 +558,12 @@ __global__ void __launch_bounds__(512) swiglu_decode_kernel(const float* __restr
   amax = block_max(amax, red);
   if (gridDim.y > 1) {
     if (!cluster_exchange(&xch, amax, gridDim.y, blockIdx.y) && threadIdx.x == 0) { *(volatile int*)status = 6; __threadfence_system(); }
-    for (uint32_t r = 0; r < gridDim.y; r++) amax = fmaxf(amax, ((volatile float*)xch.slot)[r]);
+    for (uint32_t r = 0; r < gridDim.y; r++) amax = fmaxf(amax, ((volatile float*)xch.slot[0])[r]);
   }
   const int e = sb_scale_exponent(amax);
   if (blockIdx.y == 0 && threadIdx.x == 0) qscale[row] = sb_pow2(e);
   sb_store_split8(q, I, row, k, h, sb_pow2(-e));
+  SB_TRACE_END(SB_K_SWIGLU, 0);
 }
 
 // The same for a gate/up projection that arrives as at most 4 raw split-K partials
@@ -550,10 +575,12 @@ __global__ void __launch_bounds__(512) swiglu_decode_part_kernel(const float* __
   __shared__ float red[32];
   __shared__ __align__(8) ClusterExchange xch;
   if (gridDim.y > 1) cluster_exchange_init(&xch);
+  SB_TRACE_BEGIN();
   pdl_trigger();
   const int64_t row = blockIdx.x, k = ((int64_t)blockIdx.y * blockDim.x + threadIdx.x) * 4;
   const float4 wg = *(const float4*)(sw + k), wu = *(const float4*)(sw + I + k);
   pdl_wait();
+  SB_TRACE_WAITED();
   float4 pg[4], pu[4];
 #pragma unroll
   for (int s = 0; s < 4; s++)
@@ -580,11 +607,12 @@ __global__ void __launch_bounds__(512) swiglu_decode_part_kernel(const float* __
   amax = block_max(amax, red);
   if (gridDim.y > 1) {
     if (!cluster_exchange(&xch, amax, gridDim.y, blockIdx.y) && threadIdx.x == 0) { *(volatile int*)status = 6; __threadfence_system(); }
-    for (uint32_t r = 0; r < gridDim.y; r++) amax = fmaxf(amax, ((volatile float*)xch.slot)[r]);
+    for (uint32_t r = 0; r < gridDim.y; r++) amax = fmaxf(amax, ((volatile float*)xch.slot[0])[r]);
   }
   const int e = sb_scale_exponent(amax);
   if (blockIdx.y == 0 && threadIdx.x == 0) qscale[row] = sb_pow2(e);
   sb_store_split4(q, I, row, k, h, sb_pow2(-e));
+  SB_TRACE_END(SB_K_SWIGLU, 0);
 }
 
 __global__ void gelu_tanh_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ y) {
@@ -602,6 +630,8 @@ int stream_grid(strictb200_ctx* ctx, int64_t n, int threads) {
 }
 
 }  // namespace
+
+SB_TRACE_TU(norm)
 
 int k_quantize_rows(strictb200_ctx* ctx, const bf16* x, int64_t M, int64_t K, int64_t ldx, uint8_t* q, float* scale) {
   if (K % 8 || ldx % 8) return sb_fail(STRICTB200_ERR_INVALID_ARG, "quantize_rows: K and the row stride must be multiples of 8");
@@ -624,7 +654,7 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   // many rows (prefill): narrower blocks, two chunks per thread and more blocks per SM keep more bytes in flight
   if (M > 1024 && threads > 256) threads = 256;
   while ((int64_t)threads * 8 * MAX_CHUNKS < d) threads += 32;
-  RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale, 0};
+  RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale, 0, ctx->d_status};
   // decode-step shapes: 4 columns per thread, at most 8 partials, no bf16 residual
   const bool narrow = d % 128 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
   // Four or more ranks exchange in two shots (one shot sends world-1 copies of every row);
@@ -650,13 +680,17 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
     ctx->launches++;
     return STRICTB200_OK;
   }
+  // blocks per row (one cluster): 256 threads each where the row is wide enough
+  const unsigned per_row = ctx->opt.row_cluster > 0 && d % 1024 == 0 ? (unsigned)std::min<int64_t>(ctx->opt.row_cluster, d / 1024) : 1u;
   if (narrow && !a.comm && !a.part && a.x_f32) {
-    SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<2>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
+    if (per_row > 1) SB_CUDA(sb_launch_cluster(ctx, rownorm_decode_kernel<2>, dim3((unsigned)M, per_row), dim3((unsigned)(d / 4 / per_row)), 0, dim3(1, per_row, 1), v, M, d));
+    else SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<2>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
     ctx->launches++;
     return STRICTB200_OK;
   }
   if (narrow && !a.comm && a.part && a.groups == 1 && a.splits <= 8) {
-    SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<0>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
+    if (per_row > 1) SB_CUDA(sb_launch_cluster(ctx, rownorm_decode_kernel<0>, dim3((unsigned)M, per_row), dim3((unsigned)(d / 4 / per_row)), 0, dim3(1, per_row, 1), v, M, d));
+    else SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<0>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
     ctx->launches++;
     return STRICTB200_OK;
   }

@@ -107,6 +107,7 @@ __global__ void __launch_bounds__(256) rope_kernel(RopeDev a, int64_t T) {
 // it; the arithmetic is that of the kernel above, operation for operation.
 __global__ void __launch_bounds__(256) rope_decode_kernel(RopeDev a, int64_t T) {
   constexpr int D = 128;
+  SB_TRACE_BEGIN();
   pdl_trigger();
   const int64_t t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -119,6 +120,7 @@ __global__ void __launch_bounds__(256) rope_decode_kernel(RopeDev a, int64_t T) 
   float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
   if (!is_v) gv = *(const float4*)((h < a.Hq ? a.qgain : a.kgain) + lane * 4);
   pdl_wait();
+  SB_TRACE_WAITED();
   const int p = a.lens[t];
   float4 v[8];
   float sxr = 1.f;
@@ -175,9 +177,12 @@ __global__ void __launch_bounds__(256) rope_decode_kernel(RopeDev a, int64_t T) 
     bf16* cache = is_v ? a.vcache : a.kcache;
     *(uint2*)(cache + ((t * a.Hkv + hk) * a.maxlen + p) * D + lane * 4) = wv;
   }
+  SB_TRACE_END(SB_K_ROPE, 0);
 }
 
 }  // namespace
+
+SB_TRACE_TU(rope)
 
 int k_rope_qknorm_kvappend(strictb200_ctx* ctx, const RopeArgs& a, int64_t T) {
   if (a.D != 128) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "rope: head_dim must be 128");

@@ -78,6 +78,33 @@ class Context:
         N.check(N.lib().strictb200_get_option(self.h, name.encode(), C.byref(v)))
         return v.value
 
+    def trace(self, capacity=1 << 18):
+        """Context manager: per-block time stamps of the instrumented decode kernels launched inside
+        (strictb200_trace_begin/_end). The object's ``records`` is an (n, 8) uint64 array afterwards:
+        start, after the dependency wait, end (ns of the GPU's global timer),
+        kernel id | tag << 8 | SM << 48, three optional marks inside the kernel, 0; ``reported`` counts the blocks, also beyond the capacity."""
+        ctx = self
+
+        class _Trace:
+            records = None
+            reported = 0
+
+            def __enter__(self):
+                N.check(N.lib().strictb200_trace_begin(ctx.h, capacity))
+                return self
+
+            def __exit__(self, et, ev, tb):
+                buf = np.empty((capacity, 8), np.uint64)
+                n = C.c_int()
+                st = N.lib().strictb200_trace_end(ctx.h, N.ptr(buf), capacity, C.byref(n))
+                self.reported = n.value
+                self.records = buf[:min(n.value, capacity)].copy()
+                if et is None:
+                    N.check(st)
+                return False
+
+        return _Trace()
+
     def option(self, name, value):
         """Context manager: the option holds `value` inside the block and its old value after it."""
         ctx = self

@@ -70,6 +70,8 @@ SIGNATURES = {
     "strictb200_quantize_rows": [vp, vp, i64, i64, vp, vp],
     "strictb200_gemm_fp8": [vp, i64, i64, i64, vp, vp, vp, vp, vp, i32, i32],
     "strictb200_gemm_fp8w": [vp, i64, i64, i64, vp, vp, vp, vp, i32],
+    "strictb200_trace_begin": [vp, i32],
+    "strictb200_trace_end": [vp, vp, i32, vp],
     "strictb200_quantize_weights_int8": [vp, vp, i64, i64, vp, vp],
     "strictb200_quantize_rows_int8": [vp, vp, i64, i64, vp, vp],
     "strictb200_gemm_int8": [vp, i64, i64, i64, vp, vp, vp, vp, vp],
