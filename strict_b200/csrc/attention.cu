@@ -781,15 +781,19 @@ static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
   static SbDeviceOnce once;
   static int resident_of[64] = {};  // blocks of the kernel an SM holds, per device
   const size_t smem_dec = 2 * DEC_STAGES * KT * 256;
+  static int resident_fused_of[64] = {};
   once.run(ctx->device, [&] {
     cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dec);
     cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dec);
     int r = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, attn_decode_kernel<true>, 128, smem_dec) != cudaSuccess || r < 1) r = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, attn_decode_kernel<false>, 128, smem_dec) != cudaSuccess || r < 1) r = 1;
     resident_of[ctx->device & 63] = r;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, attn_decode_kernel<true>, 128, smem_dec) != cudaSuccess || r < 1) r = 1;
+    resident_fused_of[ctx->device & 63] = r;
     return cudaSuccess;
   });
-  const int resident = resident_of[ctx->device & 63] > 0 ? resident_of[ctx->device & 63] : 1;
+  const int res0 = (ctx->opt.fuse_rope ? resident_fused_of : resident_of)[ctx->device & 63];
+  const int resident = res0 > 0 ? res0 : 1;
   const int64_t slots = (int64_t)ctx->sm_count * resident, pairs = (int64_t)B * Hkv;
   int best = tiles;
   double best_cost = 1e30;
@@ -836,6 +840,8 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
                       o_part, ml_part, RopeFuseArgs{}, ctx->opt.attn_prefetch));
   }
   ctx->launches++;
+  // The merge stays a kernel of its own: done inside the attention kernel by the last block of every (sequence, head) and
+  // of every sequence to finish (fence, counters), it cost 3 us per layer more than this launch (55.0 against 46.8 + 5.1 us).
   if (nsplit <= 8 && Hq <= 32) {
     // blocks per token (one cluster): 8 heads = 256 threads each
     const unsigned per_tok = q_out && ctx->opt.row_cluster > 1 && Hq % 8 == 0 ? (unsigned)std::min(ctx->opt.row_cluster, Hq / 8) : 1u;
