@@ -340,7 +340,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-sustained", action="store_true", help="skip the 256-step sustained leg")
     ap.add_argument("--nccl-allreduce", action="store_true", help="decode all-reduces through NCCL instead of the fused peer-memory exchange")
-    ap.add_argument("--two-shot", type=int, default=-1, help="fused all-reduce: 0 one shot, 1 two shots (default: two from four ranks on)")
+    ap.add_argument("--two-shot", type=int, default=-1, help="fused all-reduce: 0 one shot, 1 two shots (default: two with more than four ranks)")
     ap.add_argument("--timeline", default=None, help="write the per-launch timeline of one graph-replayed decode step (per-block time stamps) to this file")
     ap.add_argument("--no-graph", action="store_true", help="plain launches instead of CUDA-graph replay of the decode step")
     args = ap.parse_args()

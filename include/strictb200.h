@@ -100,7 +100,7 @@ int strictb200_trace_end(strictb200_ctx* ctx, uint64_t* out_records, int max_rec
  * attention kernel: 0 mma.sync, 1 tcgen05 one query tile per block, 2 two tiles per block, -1),
  * "gemm_pair" (many-token GEMM on SM pairs, 1), "prefetch" (1), "deep_ring" (1),
  * "attn_blocks_per_sm" (0), "split_target" (0), "tp_two_shot" (fused all-reduce in two shots,
- * -1: from four ranks on), "wait_limit" (polls of a cross-rank wait before it gives up,
+ * -1: with more than four ranks), "wait_limit" (polls of a cross-rank wait before it gives up,
  * 4194304), "prefill_chunk" (token rows per prefill chunk, 16384), "fuse_rope" (decode attention applies
  * QK-norm and RoPE and appends to the cache itself, 0), "row_cluster" (blocks of one cluster that share a row in the decode row
  * kernels, 4), "attn_prefetch" (decode attention loads its first key/value
@@ -358,10 +358,12 @@ int strictb200_tp_info(strictb200_ctx* ctx, int* world, int* rank);
  * of its exchange buffer, the host gathers the handles of all ranks (rank order, world x 64 bytes)
  * and hands them to every rank. From then on the all-reduce after o_proj and down_proj happens
  * inside the residual/RMSNorm kernel that consumes the sum: the block of a token row adds the
- * rank's own split-K partials, pushes every value into the peers' buffers over NVLink as an
- * 8-byte packet {value, epoch} (plain stores; no multicast), polls its own buffer until the same
- * row's packets of every peer carry the current epoch, and adds the ranks' values in rank order,
- * so every rank computes bit-identical sums. With four or more ranks the exchange takes two
+ * rank's own split-K partials, pushes every value into the peers' buffers over NVLink as one
+ * 32-bit word whose two lowest mantissa bits carry the row's call count modulo 4 (plain stores;
+ * no multicast), polls its own buffer until the same row's words of every peer carry the
+ * current tag, and adds the ranks' values, those two bits cleared in every one of them, in rank
+ * order, so every rank computes bit-identical sums (a partial sum loses at most 3 units of its
+ * last place, 3.6e-7 relative; the NCCL path adds the unmodified values). With more than four ranks the exchange takes two
  * shots: each column slice goes to the rank that owns it, which returns the finished sums.
  * Every poll is bounded ("wait_limit"); if a rank never shows up the kernel sets the error word
  * and the call that synchronises next returns ERR_TIMEOUT. All ranks must be processes on one

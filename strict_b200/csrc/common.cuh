@@ -17,8 +17,9 @@ struct TpState;     // tp.cpp
 // All-reduce over peer memory (tp.cpp): every rank owns a buffer that all ranks of the box map
 // (CUDA IPC). Passed to kernels by value. Two exchanges use it:
 //   row-granular (the decode step's default): the row kernel that consumes the sum pushes each of
-//     its values into the peers' buffers as an 8-byte packet {value, epoch} and polls its own
-//     buffer until the packets of every peer carry the row's current epoch (row_data, row_epoch);
+//     its values into the peers' buffers as one word whose two lowest mantissa bits carry the row's
+//     epoch modulo 4, and polls its own buffer until the words of every peer carry the current tag
+//     (row_data, row_epoch); sums are taken over the values with those two bits cleared;
 //   whole-result (shapes the row exchange does not take): a publish kernel writes the rank's fp32
 //     partial result into its own buffer and raises an epoch flag in every peer's buffer; the
 //     consumer waits for all flags and adds the ranks' data in rank order with plain peer loads
@@ -33,9 +34,9 @@ struct TpCommDev {
   int world, rank;
   long long max_elems;
   // Row-granular variant (the row kernel itself exchanges the sums): every value is pushed into
-  // the peers' buffers as an 8-byte packet {value, epoch}, so a packet validates itself and
+  // the peers' buffers as a word that carries its epoch tag, so a word validates itself and
   // neither fences nor separate flags are needed.
-  float* row_data[8];   // rank r's packet area: [parity][source rank][row_elems][2] words
+  float* row_data[8];   // rank r's packet area: [parity][source rank] areas of 2 * row_elems words (the first row_elems in use)
   int* row_epoch;       // this rank's per-row epoch counters (device memory, one writer per row)
   long long row_elems;  // values per (parity, source rank)
   int max_rows;
@@ -287,7 +288,7 @@ int k_bf16_to_f32(strictb200_ctx*, const bf16* x, int64_t n, float* y);
 // tp.cpp
 const TpCommDev* sb_tp_comm(strictb200_ctx*);  // null unless the peer buffers were opened
 bool sb_tp_comm_fits(strictb200_ctx*, int64_t M, int64_t d);  // the peer-memory all-reduce takes an [M,d] result
-bool sb_tp_row_exchange_ok(strictb200_ctx*, int64_t M, int64_t d);  // ... with the row-granular exchange (one row width per context)
+bool sb_tp_row_exchange_ok(strictb200_ctx*, int64_t M, int64_t d, int two_shot);  // ... with the row-granular exchange (one row width per context)
 // out[m,n] = (sum_s part[s][m,n]) * sx[m] * sw[n] written to this rank's peer buffer, then published
 int k_tp_publish(strictb200_ctx*, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N);
 int sb_tp_allreduce_f32(strictb200_ctx*, float* buf, int64_t count);

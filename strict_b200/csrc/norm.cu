@@ -269,9 +269,8 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
     SB_TRACE_MARK(0);
   } else if (MODE == 3) {
     // Fused all-reduce, row-granular: this block sums the rank's own split-K partials of its row
-    // and exchanges them with the peers as 8-byte packets {value, epoch} pushed into their
-    // buffers (two 16-byte stores of two packets each); a receiver polls its own buffer until
-    // the packets carry the row's current epoch. No fence, no other kernel, no grid-wide step.
+    // and pushes the sums into the peers' buffers as tagged words (below); a receiver polls its own
+    // buffer until the words carry the row's current tag. No fence, no other kernel, no grid-wide step.
     float4 p[8];
 #pragma unroll
     for (int s = 0; s < 8; s++)
@@ -283,30 +282,35 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
 #pragma unroll
     for (int s = 0; s < 8; s++)
       if (s < a.splits) { acc[0] += p[s].x; acc[1] += p[s].y; acc[2] += p[s].z; acc[3] += p[s].w; }
-    const float own[4] = {__fmul_rn(__fmul_rn(acc[0], sxr), sw.x), __fmul_rn(__fmul_rn(acc[1], sxr), sw.y),
-                          __fmul_rn(__fmul_rn(acc[2], sxr), sw.z), __fmul_rn(__fmul_rn(acc[3], sxr), sw.w)};
-    const float ef = __int_as_float(e);
-    // Word offsets of this thread's two 16-byte stores inside a packet area: the warp's 128 columns
-    // are 256 words; the lanes' first stores are contiguous, then the second ones, so that each
-    // store instruction of a warp writes four whole 128-byte lines (NVLink carries whole lines
-    // far better than half-written sectors).
-    const size_t off0 = (size_t)(row * d + (k & ~(int64_t)127)) * 2 + (size_t)(threadIdx.x & 31) * 4, off1 = off0 + 128;
+    auto clear2f = [](float x) { return __uint_as_float(__float_as_uint(x) & ~3u); };
+    const float own[4] = {clear2f(__fmul_rn(__fmul_rn(acc[0], sxr), sw.x)), clear2f(__fmul_rn(__fmul_rn(acc[1], sxr), sw.y)),
+                          clear2f(__fmul_rn(__fmul_rn(acc[2], sxr), sw.z)), clear2f(__fmul_rn(__fmul_rn(acc[3], sxr), sw.w))};
+    // A value travels as one 32-bit word: its two lowest mantissa bits are replaced by the row's
+    // epoch modulo 4 (the two parities of the packet area alternate, so the word that a slot held
+    // before always carries epoch - 2, whose tag differs). Every rank adds the values with those
+    // two bits cleared, its own included, so all ranks get the same sum. 16 bytes per thread and
+    // peer, one store instruction; a warp's store covers four whole 128-byte lines.
+    const uint32_t tag = (uint32_t)e & 3u;
+    const size_t off = (size_t)(row * d + k);
     const size_t area = (size_t)a.comm.row_elems * 2;
+    auto clear2 = [](float x) { return __uint_as_float(__float_as_uint(x) & ~3u); };
     auto push = [&](float* dst, const float* v4) {  // dst: start of a packet area
-      asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + off0), "f"(v4[0]), "f"(ef), "f"(v4[1]), "f"(ef) : "memory");
-      asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + off1), "f"(v4[2]), "f"(ef), "f"(v4[3]), "f"(ef) : "memory");
+      asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(dst + off), "r"((__float_as_uint(v4[0]) & ~3u) | tag),
+                   "r"((__float_as_uint(v4[1]) & ~3u) | tag), "r"((__float_as_uint(v4[2]) & ~3u) | tag), "r"((__float_as_uint(v4[3]) & ~3u) | tag)
+                   : "memory");
     };
     auto poll = [&](const float* src, float* v4) {  // bounded: on expiry the error word is set and the (wrong) values are used
-      float4 q0, q1;
+      float4 q0;
       uint32_t spins = 0;
       while (true) {
-        q0 = ld_peer4(src + off0);
-        q1 = ld_peer4(src + off1);
-        if (__float_as_int(q0.y) == e && __float_as_int(q0.w) == e && __float_as_int(q1.y) == e && __float_as_int(q1.w) == e) break;
+        q0 = ld_peer4(src + off);
+        if (((__float_as_uint(q0.x) ^ tag) & 3u) == 0 && ((__float_as_uint(q0.y) ^ tag) & 3u) == 0 && ((__float_as_uint(q0.z) ^ tag) & 3u) == 0 &&
+            ((__float_as_uint(q0.w) ^ tag) & 3u) == 0)
+          break;
         if (++spins > a.comm.wait_limit) { *(volatile int*)a.comm.status = 5; __threadfence_system(); break; }
         if ((spins & 4095u) == 0 && *(volatile int*)a.comm.status) break;  // another wait already expired: do not wait it out again
       }
-      v4[0] = q0.x; v4[1] = q0.z; v4[2] = q1.x; v4[3] = q1.z;
+      v4[0] = clear2(q0.x); v4[1] = clear2(q0.y); v4[2] = clear2(q0.z); v4[3] = clear2(q0.w);
     };
     float* mine = a.comm.row_data[a.comm.rank];
     if (!a.two_shot) {
@@ -314,13 +318,16 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
 #pragma unroll
       for (int r = 0; r < 8; r++)
         if (r < a.comm.world && r != a.comm.rank) push(a.comm.row_data[r] + ((size_t)(e & 1) * 8 + a.comm.rank) * area, own);
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int r = 0; r < 8; r++)
         if (r < a.comm.world) {
           float v[4] = {own[0], own[1], own[2], own[3]};
           if (r != a.comm.rank) poll(mine + ((size_t)(e & 1) * 8 + r) * area, v);
-          t[0] += v[0]; t[1] += v[1]; t[2] += v[2]; t[3] += v[3];
+          sum[0] += v[0]; sum[1] += v[1]; sum[2] += v[2]; sum[3] += v[3];
         }
+      // the same value as two shots deliver (there the sum itself travels as a tagged word)
+      t[0] += clear2(sum[0]); t[1] += clear2(sum[1]); t[2] += clear2(sum[2]); t[3] += clear2(sum[3]);
     } else {
       // two shots (the one-shot push sends world-1 copies of the row from every rank, 7 MB per
       // rank and sum at 8 ranks): rank j owns the columns [j*d/world, (j+1)*d/world) of every
@@ -342,6 +349,7 @@ __global__ void __launch_bounds__(1024) rownorm_decode_kernel(RowNormDev a, int6
 #pragma unroll
         for (int r = 0; r < 8; r++)
           if (r < a.comm.world && r != a.comm.rank) push(a.comm.row_data[r] + (16 + (size_t)(e & 1)) * area, sum);
+        sum[0] = clear2(sum[0]); sum[1] = clear2(sum[1]); sum[2] = clear2(sum[2]); sum[3] = clear2(sum[3]);  // what the peers received
       }
       t[0] += sum[0]; t[1] += sum[1]; t[2] += sum[2]; t[3] += sum[3];
     }
@@ -657,14 +665,15 @@ int k_rownorm(strictb200_ctx* ctx, const RowNormArgs& a, int64_t M, int64_t d) {
   RowNormDev v{a.comm ? *a.comm : TpCommDev{}, a.comm ? 1 : 0, a.x_f32, a.x_in, a.part, a.groups, a.splits, a.sx, a.sw, a.residual_f32, a.residual, a.gain, a.eps, a.y, a.q, a.qscale, 0, ctx->d_status};
   // decode-step shapes: 4 columns per thread, at most 8 partials, no bf16 residual
   const bool narrow = d % 128 == 0 && d <= 4096 && a.gain && !a.residual && M <= 1024;
-  // Four or more ranks exchange in two shots (one shot sends world-1 copies of every row);
+  // More than four ranks exchange in two shots (one shot sends world-1 copies of every row: at four
+  // ranks one shot measured 14730 tokens/s against 14470 for two, at eight 11800 against 14470);
   // the tp_two_shot option (0 / 1) forces either.
   if (a.comm) {
     v.comm.wait_limit = ctx->opt.wait_limit > 0 ? (unsigned)ctx->opt.wait_limit : 1u;
     const int ts = ctx->opt.tp_two_shot;
-    v.two_shot = (ts >= 0 ? ts != 0 : a.comm->world >= 4) && d % (a.comm->world * 128) == 0;
+    v.two_shot = (ts >= 0 ? ts != 0 : a.comm->world > 4) && d % (a.comm->world * 128) == 0;
   }
-  if (narrow && a.comm && a.part && a.groups == 1 && a.splits <= 8 && a.comm->world <= 8 && sb_tp_row_exchange_ok(ctx, M, d)) {
+  if (narrow && a.comm && a.part && a.groups == 1 && a.splits <= 8 && a.comm->world <= 8 && sb_tp_row_exchange_ok(ctx, M, d, v.two_shot)) {
     SB_CUDA(sb_launch(ctx, rownorm_decode_kernel<3>, dim3((unsigned)M), dim3((unsigned)(d / 4)), 0, v, M, d));
     ctx->launches++;
     return STRICTB200_OK;

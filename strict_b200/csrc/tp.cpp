@@ -58,7 +58,8 @@ constexpr long long COMM_MAX_ELEMS = 1 << 20;  // floats per epoch parity (4 MiB
 constexpr size_t COMM_FLAG_BYTES = 256;        // 2 parities x 8 source ranks, padded
 constexpr int COMM_ROWS = 64;                  // rows of the row-granular exchange
 constexpr long long COMM_ROW_ELEMS = (long long)COMM_ROWS * 4096;  // values per (parity, source rank) of the row area
-// row area: [parity][source rank][value][2] words, every value travelling with its epoch (8-byte packets)
+// row area: [parity][source rank] areas of 2 x COMM_ROW_ELEMS words; a value travels as one word that carries the row's epoch modulo 4 in
+// its two lowest mantissa bits (the first half of an area is used)
 constexpr size_t COMM_ROW_OFFSET = COMM_FLAG_BYTES + 2 * COMM_MAX_ELEMS * sizeof(float);
 // [2 parities][8 source ranks] areas of partial sums, then [2 parities] areas of finished sums (two-shot exchange)
 constexpr size_t COMM_BYTES = COMM_ROW_OFFSET + (size_t)(2 * 8 + 2) * COMM_ROW_ELEMS * 2 * sizeof(float);
@@ -72,6 +73,7 @@ struct TpState {
   bool opened = false;
   bool absent_peers = false;      // failure-injection set-up: the "peers" are local areas nobody writes
   long long row_d = 0;            // row width the row-granular exchange is tied to (0: not used yet)
+  int row_two_shot = -1;          // and its one- or two-shot form (-1: not used yet)
   TpCommDev dev{};
 };
 
@@ -136,13 +138,15 @@ const TpCommDev* sb_tp_comm(strictb200_ctx* ctx) { return ctx->tp && ctx->tp->op
 bool sb_tp_comm_fits(strictb200_ctx* ctx, int64_t M, int64_t d) {
   return ctx->tp && ctx->tp->opened && d % 4 == 0 && M * d <= COMM_MAX_ELEMS;
 }
-// The packet area is addressed by row * d + column and validated by per-row epochs, so two row
-// widths on one context could take each other's stale packets for fresh ones: the first width
-// that uses the exchange owns it, other widths go through the publish kernel and its flags.
-bool sb_tp_row_exchange_ok(strictb200_ctx* ctx, int64_t M, int64_t d) {
+// The packet area is addressed by row * d + column and validated by a two-bit tag of the row's
+// epoch, which tells a fresh word from the one its slot held before (epoch - 2) as long as every
+// call writes the same slots: two row widths, or the one- and the two-shot form, on one context
+// could take each other's stale words for fresh ones. The first width and form that use the
+// exchange own it; others go through the publish kernel and its flags.
+bool sb_tp_row_exchange_ok(strictb200_ctx* ctx, int64_t M, int64_t d, int two_shot) {
   if (!ctx->tp || !ctx->tp->opened || M > COMM_ROWS || M * d > COMM_ROW_ELEMS) return false;
-  if (!ctx->tp->row_d) ctx->tp->row_d = d;
-  return ctx->tp->row_d == d;
+  if (!ctx->tp->row_d) { ctx->tp->row_d = d; ctx->tp->row_two_shot = two_shot; }
+  return ctx->tp->row_d == d && ctx->tp->row_two_shot == two_shot;
 }
 
 int k_tp_publish(strictb200_ctx* ctx, const float* part, int splits, const float* sx, const float* sw, int64_t M, int64_t N) {

@@ -67,11 +67,16 @@ def _row_inputs(world, M, d, splits, call):
     return parts, sxs, sw, resid, gain
 
 
+def _clear2(x):
+    return (np.ascontiguousarray(x, dtype=np.float32).view(np.uint32) & np.uint32(0xFFFFFFFC)).view(np.float32)
+
+
 def _fused_op_check(ctx, world, rank, O):
     """strictb200_tp_allreduce_rownorm at the decode step's shape and a narrow one, three calls in a
     row (both epoch parities, then a second row count): the updated residual must equal the fp32
-    restatement bit for bit (own partials summed split by split, scaled, ranks added in rank
-    order), the normalised output the oracle's RMSNorm of it."""
+    restatement bit for bit (own partials summed split by split, scaled, the two lowest mantissa
+    bits cleared because they carry the epoch tag in transit, ranks added in rank order, the sum
+    cleared the same way), the normalised output the oracle's RMSNorm of it."""
     from strict_b200 import native as N
     from strict_b200.kernel import DeviceVariable as DV
     d = CFG["d_model"]
@@ -82,8 +87,8 @@ def _fused_op_check(ctx, world, rank, O):
             acc = np.zeros((M, d), np.float32)
             for s_ in range(splits):
                 acc = acc + parts[r][s_]
-            total = total + (acc * sxs[r][:, None]) * sw[None, :]
-        want_res = resid + total
+            total = total + _clear2((acc * sxs[r][:, None]) * sw[None, :])
+        want_res = resid + _clear2(total)
         dp, dsx, dsw = DV.of(ctx, parts[rank]), DV.of(ctx, sxs[rank]), DV.of(ctx, sw)
         dres, dg, dy = DV.of(ctx, resid), DV.of(ctx, gain), DV(ctx, M * d, np.uint16)
         N.check(N.lib().strictb200_tp_allreduce_rownorm(ctx.h, dp.p, splits, dsx.p, dsw.p, dres.p, dg.p, 1e-6, M, d, dy.p, None, None))
