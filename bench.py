@@ -316,6 +316,9 @@ def run_ours(args, rank, world, local_rank):
             "device_status": status}
     if timeline:
         line["timeline"] = timeline
+    from strict_b200 import build as _build
+    stamp = N.lib().strictb200_build_id().decode()
+    line["build"] = {"library": stamp, "sources_beside_it": _build.source_id(), "match": stamp.split()[0] == _build.source_id()}
     if base:
         line["cpu_baseline"] = base
     sys.stdout.flush()

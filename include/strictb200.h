@@ -40,6 +40,10 @@ typedef struct strictb200_kv strictb200_kv;
 /* ---- library ---- */
 int strictb200_version(void);
 const char* strictb200_last_error(void);
+/* "<16 hex digits> <date> <time>": a hash of the sources this binary was built from (every file
+ * under csrc/ and this header; python -m strict_b200.build computes and stamps it) and when it was
+ * compiled. bench.py prints it beside the hash of the sources it finds next to the library. */
+const char* strictb200_build_id(void);
 
 /* Compiles CUDA C text to PTX with NVRTC, as the reference does through ManagedCuda's
  * CudaRuntimeCompiler(code, name).Compile(options) / GetPTXAsString / GetLogAsString

@@ -21,6 +21,21 @@ def sources():
     return sorted(f for f in os.listdir(CSRC) if f.endswith((".cu", ".cpp")))
 
 
+def source_id():
+    """sha256 over the library's sources and its header (file names and contents, sorted): the build
+    stamps it into the library (strictb200_build_id) so that a run can say which sources its binary
+    was made from."""
+    import hashlib
+    h = hashlib.sha256()
+    files = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".cu", ".cpp", ".cuh", ".h"))]
+    files.append(os.path.join(HERE, "..", "include", "strictb200.h"))
+    for path in files:
+        h.update(os.path.basename(path).encode() + b"\0")
+        with open(path, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:16]
+
+
 def _stale(target, deps):
     if not os.path.exists(target):
         return True
@@ -34,11 +49,16 @@ def build(force=False, verbose=False):
     headers.append(os.path.join(HERE, "..", "include", "strictb200.h"))
     jobs = []
     objs = []
+    sid = source_id()
+    stamp = os.path.join(OBJ, "build_id.txt")
+    stamped = open(stamp).read().strip() if os.path.exists(stamp) else ""
     for src in sources():
         obj = os.path.join(OBJ, src.rsplit(".", 1)[0] + ".o")
         objs.append(obj)
-        if force or _stale(obj, [os.path.join(CSRC, src)] + headers):
-            cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", os.path.join(CSRC, src), "-o", obj]
+        is_id = src == "build_id.cpp"  # the one file that carries the stamp: rebuilt whenever any source changed
+        if force or _stale(obj, [os.path.join(CSRC, src)] + headers) or (is_id and stamped != sid):
+            cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + (['-DSB_BUILD_ID="%s"' % sid] if is_id else []) + \
+                  ["-x", "cu", "-c", os.path.join(CSRC, src), "-o", obj]
             jobs.append(cmd)
 
     def run(cmd):
@@ -51,6 +71,8 @@ def build(force=False, verbose=False):
                 sys.stderr.write(" ".join(cmd[-4:]) + "\n" + r.stdout + r.stderr)
             if r.returncode:
                 raise RuntimeError("nvcc failed for " + cmd[-3])
+    with open(stamp, "w") as f:
+        f.write(sid + "\n")
     if force or jobs or _stale(LIB, objs):
         cmd = [NVCC, "-shared", "-ccbin", HOST_CXX, "-o", LIB] + objs + ["-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)

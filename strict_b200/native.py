@@ -132,6 +132,8 @@ def lib():
         L.strictb200_version.argtypes = []
         L.strictb200_last_error.restype = C.c_char_p
         L.strictb200_last_error.argtypes = []
+        L.strictb200_build_id.restype = C.c_char_p
+        L.strictb200_build_id.argtypes = []
         _lib = L
     return _lib
 

@@ -75,7 +75,10 @@ def test_library_exports_every_declared_symbol():
     missing = [s for s in sorted(declared) if not hasattr(lib, s)]
     assert not missing, missing
     # the ctypes table binds exactly the declared functions
-    assert set(native.SIGNATURES) | {"strictb200_version", "strictb200_last_error"} == declared
+    assert set(native.SIGNATURES) | {"strictb200_version", "strictb200_last_error", "strictb200_build_id"} == declared
+    # the binary says which sources it was built from; after a build they are the ones beside it
+    from strict_b200 import build
+    assert lib.strictb200_build_id().decode().split()[0] == build.source_id()
     assert lib.strictb200_version() == int(re.search(r"#define STRICTB200_VERSION (\d+)", header).group(1))
 
 

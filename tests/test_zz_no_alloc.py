@@ -5,7 +5,8 @@ Some users of the library run it from a serving loop that must never hit cudaMal
 memory for its own pool before the library was loaded, so the driver has nothing left to hand out.
 The entry point keeps its split-KV partial results in a 4 MiB array compiled into the library
 instead. Its output must be the same as strictb200_attn_decode's, call after call, even though
-the array keeps whatever the previous call left in it.
+the array keeps whatever the previous call left in it, and within the attention tests' bars of
+the CPU oracle.
 
 This file sorts last on purpose: a run that stops at the first failure has then already run
 every other test.
@@ -34,6 +35,10 @@ def _case(ctx, oracle, seed, B, Hq, Hkv, maxlen, lens):
     a, b = oracle.bf16_to_f32(want.to_host()), oracle.bf16_to_f32(got.to_host())
     for v in (dq, dk, dv, dl, want, got):
         v.free()
+    # the entry against the CPU oracle as well (not only against the allocating entry): the bars of the attention tests
+    ref = oracle.round_bf16(oracle.attn_decode(oracle.bf16_to_f32(q), oracle.bf16_to_f32(kc), oracle.bf16_to_f32(vc), np.array(lens, np.int32), scale))
+    err = np.abs(b.reshape(ref.shape) - ref)
+    assert err.max() <= 2e-2 and err.mean() / np.abs(ref).mean() <= 5e-3, (err.max(), err.mean())
     return a, b
 
 
