@@ -117,6 +117,11 @@ def _worker(rank, world, port, path, out, mode):
         nxt, logits = kv.prefill(toks, lens, want_logits=True)
         ids = kv.generate(nxt, N_TOKENS)  # returns ERR_TIMEOUT by itself if a cross-rank wait expired
         assert ctx.device_status() == 0
+        if MODES[mode] is not None:
+            # the exchange really ran inside the row kernel: one more step under the block time stamps (all ranks take it)
+            with ctx.trace(1 << 16) as tr:
+                kv.decode_step(ids[-1])
+            assert 7 in set((tr.records[:, 3] & np.uint64(0xFF)).astype(int).tolist())
         if rank == 0:
             np.savez(path, nxt=nxt, logits=logits, ids=ids, toks=toks, lens=lens)
         dist.barrier()
@@ -128,7 +133,7 @@ def _worker(rank, world, port, path, out, mode):
 
 @pytest.mark.parametrize("mode", list(MODES))
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_tp_matches_oracle(oracle, tmp_path, world, mode):
+def test_tp_matches_oracle(oracle, tmp_path, parity_log, world, mode):
     if _gpu_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
@@ -157,6 +162,8 @@ def test_tp_matches_oracle(oracle, tmp_path, world, mode):
                 near_ties += 1
         if s_ < N_TOKENS:
             logits = st.decode(pick)
+    parity_log(dict(test="tensor parallel vs unsharded oracle", world=world, mode=mode, prefill_logits_max_abs=float(err.max()),
+                    prefill_logits_mean_rel=float(err.mean() / np.abs(want).mean()), tokens=N_TOKENS + 1, sequences=3, near_tie_departures=near_ties))
     assert alive.sum() >= 2, f"{near_ties} sequences left the oracle's path"
     st.close(), om.close()
 
