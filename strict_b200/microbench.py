@@ -300,6 +300,42 @@ def image_cases(ctx, iters):
     flat.free()
 
 
+def model_cases(ctx):
+    """Decode throughput of the two single-GPU model configurations as they are specified: GPT-2
+    small (fp32, batch 1, prompt 128, 128 decoded tokens) and Qwen3-0.6B (FP8 weights, batch 8,
+    prompts of 512, 256 decoded tokens); seeded weights and prompts, greedy steps with the ids
+    resident on the device (graph replay), CUDA events around the whole decode loop."""
+    from .model import CONFIGS, Model
+    hbm, _, kind = _peaks()
+    for name, B, prompt, new, seed in (("gpt2-small", 1, 128, 128, 0), ("qwen3-0.6b", 8, 512, 256, 4)):
+        cfg = CONFIGS[name]
+        m = Model(ctx, cfg).init_random(seed)
+        kv = m.new_cache(B, prompt + new + 8)
+        tok = DV(ctx, B * prompt, np.int32)
+        N.check(L().strictb200_gen_tokens(ctx.h, seed + 1, 1, B * prompt, cfg["vocab"], tok.p))
+        first, _ = kv.prefill(tok.to_host().reshape(B, prompt))
+        kv.decode_step(first)            # plain launches once (set-up)
+        kv.decode_steps_device(3)        # includes the graph capture
+        ctx.synchronize()
+        bytes_step = kv.decode_bytes()
+        sampler = ClockSampler(ctx.device)
+        sampler.start()
+        ctx.synchronize()
+        ctx.timer_begin()
+        kv.decode_steps_device(new - 4)
+        ms = ctx.timer_end()
+        clocks = sampler.stop()
+        steps = new - 4
+        print(json.dumps({"case": "model_decode", "model": name, "batch": B, "prompt": prompt, "steps": steps, "ms_per_step": ms / steps,
+                          "tokens_per_s": B * steps / (ms / 1e3), "bytes_per_step": bytes_step, "GBps": bytes_step / (ms / steps) / 1e6,
+                          "hbm_frac": bytes_step / (ms / steps) / 1e6 / hbm, "peaks": kind, "clocks": clocks,
+                          "note": "a step streams %.2f GB (weights + cache); below ~1 GB a step is a chain of launch-bound kernels" % (bytes_step / 1e9)}),
+              flush=True)
+        tok.free()
+        kv.dispose()
+        m.dispose()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="*", default=["gemm", "attn"])
@@ -317,6 +353,8 @@ def main():
         ew_cases(ctx)
     if "image" in args.what:
         image_cases(ctx, args.iters)
+    if "models" in args.what:
+        model_cases(ctx)
     ctx.dispose()
 
 
