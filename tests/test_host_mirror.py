@@ -198,3 +198,35 @@ def test_tensors_beside_the_bytecode(tmp_path, oracle):
         packaging.read_model(str(bad))
     with pytest.raises(ValueError):
         packaging.add_model(path, cfg, {"x": np.zeros(3, np.int64)})
+
+
+def test_timeline_groups_blocks_into_launches_and_exposed_times_add_up():
+    """strict_b200/timeline.py on hand-made records: two launches of one GEMM shape separated by a
+    row kernel, blocks of a launch overlapping in time, marks optional; the exposed times telescope
+    to the end of the last launch."""
+    from strict_b200 import timeline as TL
+    N_, K = 6144, 4096
+    gemm = 1 | (((N_ ^ (K << 12)) & 0xFFFFFFFF) << 8)
+    row = 2 | (77 << 8)
+
+    def rec(t0, tw, t2, word, sm, marks=(0, 0, 0)):
+        return [1000 + t0, 1000 + tw if tw else 0, 1000 + t2, word | (sm << 48), *[1000 + m if m else 0 for m in marks], 0]
+    records = np.array([
+        rec(0, 50, 400, gemm, 0), rec(10, 55, 420, gemm, 1), rec(5, 52, 390, gemm, 2),      # first GEMM launch, three blocks
+        rec(100, 430, 600, row, 3, (450, 500, 0)), rec(110, 431, 610, row, 4, (452, 505, 0)),  # row kernel, resident early
+        rec(500, 620, 900, gemm, 0), rec(505, 622, 950, gemm, 1),                             # second GEMM launch
+    ], dtype=np.uint64)
+    ll = TL.launches(records, {(N_, K): "gemm_qkv"})
+    assert [d["kernel"] for d in ll] == ["gemm_qkv", "rownorm", "gemm_qkv"] and [d["blocks"] for d in ll] == [3, 2, 2]
+    assert ll[0]["first_start"] == 0 and ll[0]["end"] == 420 and ll[0]["waited"] == 52
+    assert ll[1]["marks"] == [451, 502, None] and ll[1]["exposed"] == 610 - 420
+    assert sum(d["exposed"] for d in ll) == ll[-1]["end"] == 950
+    per = TL.per_kernel(ll)
+    assert per["gemm_qkv"] == (420 + (950 - 610), 2) and per["rownorm"] == (190, 1)
+    assert TL.launches(np.zeros((0, 8), np.uint64)) == []
+
+
+def test_build_identity_follows_the_sources(tmp_path):
+    from strict_b200 import build
+    a = build.source_id()
+    assert a == build.source_id() and len(a) == 16 and int(a, 16) >= 0
