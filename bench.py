@@ -255,7 +255,7 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- optional: where one graph-replayed step's time goes, from per-block time stamps (outside every timed region)
     timeline = None
-    if args.timeline:
+    if not args.no_timeline:
         from strict_b200 import timeline as TL
         with ctx.trace(1 << 18) as tr:
             kv.decode_steps_device(1)
@@ -266,8 +266,9 @@ def run_ours(args, rank, world, local_rank):
         ll = TL.launches(tr.records, names)
         timeline = {"blocks_reported": tr.reported, "launches": len(ll), "span_us": (ll[-1]["end"] / 1e3) if ll else 0.0,
                     "exposed_us": {k: [v[0] / 1e3, v[1]] for k, v in TL.per_kernel(ll).items()}}
-        with open(args.timeline + f".rank{rank}" if world > 1 else args.timeline, "w") as f:
-            json.dump({"summary": timeline, "launches": ll}, f)
+        if args.timeline:
+            with open(args.timeline + f".rank{rank}" if world > 1 else args.timeline, "w") as f:
+                json.dump({"summary": timeline, "launches": ll}, f)
 
     # ---- per-kernel-class device times of the same step (plain launches, CUDA events on the launch stream)
     prof = kv.profile_decode(4)
@@ -290,6 +291,19 @@ def run_ours(args, rank, world, local_rank):
     tot_ms = sum(v[0] for v in prof.values())
     for k in kernels:
         kernels[k]["share"] = prof[k][0] / tot_ms
+    if timeline:
+        # the same classes inside the graph-replayed step, from the kernels' own time stamps: how far each launch moved the
+        # end of the chain (the traced replay is about 6 % slower than an untraced one, so these fractions are on the low side)
+        per_call = {}
+        for k, (us, n) in timeline["exposed_us"].items():
+            k = {"rope": "rope_kvappend", "rownorm_allreduce": "rownorm", "attn_combine": "attn_decode"}.get(k, k)  # the merge belongs to the attention class
+            if n:
+                per_call[k] = per_call.get(k, 0.0) + us / n
+        for k, us in per_call.items():
+            if k in kernels:
+                kernels[k]["exposed_us_in_step"] = us
+                if k in alg:
+                    kernels[k]["frac_in_step"] = alg[k] / (us * 1e-6) / 1e9 / hbm
     dom = max((k for k in kernels if k in alg), key=lambda k: prof[k][0])
     roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gbs"], "peak": hbm, "unit": "GB/s", "frac": kernels[dom]["frac"],
                 "traffic": TRAFFIC_RATIO[dom] * alg[dom] if dom in TRAFFIC_RATIO else None,
@@ -344,7 +358,8 @@ def main():
     ap.add_argument("--no-sustained", action="store_true", help="skip the 256-step sustained leg")
     ap.add_argument("--nccl-allreduce", action="store_true", help="decode all-reduces through NCCL instead of the fused peer-memory exchange")
     ap.add_argument("--two-shot", type=int, default=-1, help="fused all-reduce: 0 one shot, 1 two shots (default: two with more than four ranks)")
-    ap.add_argument("--timeline", default=None, help="write the per-launch timeline of one graph-replayed decode step (per-block time stamps) to this file")
+    ap.add_argument("--timeline", default=None, help="also write the per-launch timeline of one graph-replayed decode step (per-block time stamps) to this file")
+    ap.add_argument("--no-timeline", action="store_true", help="skip the traced replay (outside every timed region) that gives the per-kernel exposed times")
     ap.add_argument("--no-graph", action="store_true", help="plain launches instead of CUDA-graph replay of the decode step")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
