@@ -294,13 +294,13 @@ def run_ours(args, rank, world, local_rank):
     if timeline:
         # the same classes inside the graph-replayed step, from the kernels' own time stamps: how far each launch moved the
         # end of the chain (the traced replay is about 6 % slower than an untraced one, so these fractions are on the low side)
-        per_call = {}
+        total_us = {}
         for k, (us, n) in timeline["exposed_us"].items():
             k = {"rope": "rope_kvappend", "rownorm_allreduce": "rownorm", "attn_combine": "attn_decode"}.get(k, k)  # the merge belongs to the attention class
-            if n:
-                per_call[k] = per_call.get(k, 0.0) + us / n
-        for k, us in per_call.items():
-            if k in kernels:
+            total_us[k] = total_us.get(k, 0.0) + us
+        for k, us in total_us.items():
+            if k in kernels and kernels[k]["calls_per_step"]:
+                us = us / kernels[k]["calls_per_step"]  # per call of the class, as ms_per_call is
                 kernels[k]["exposed_us_in_step"] = us
                 if k in alg:
                     kernels[k]["frac_in_step"] = alg[k] / (us * 1e-6) / 1e9 / hbm
