@@ -296,7 +296,7 @@ def run_ours(args, rank, world, local_rank):
         # end of the chain (the traced replay is about 6 % slower than an untraced one, so these fractions are on the low side)
         total_us = {}
         for k, (us, n) in timeline["exposed_us"].items():
-            k = {"rope": "rope_kvappend", "rownorm_allreduce": "rownorm", "attn_combine": "attn_decode"}.get(k, k)  # the merge belongs to the attention class
+            k = {"rope": "rope_kvappend", "rownorm_allreduce": "rownorm", "attn_combine": "attn_merge"}.get(k, k)
             total_us[k] = total_us.get(k, 0.0) + us
         for k, us in total_us.items():
             if k in kernels and kernels[k]["calls_per_step"]:

@@ -334,7 +334,7 @@ enum strictb200_kernel_class {
   STRICTB200_K_EMBED = 0,     /* embedding gather, length update */
   STRICTB200_K_GEMM_QKV = 1,
   STRICTB200_K_ROPE = 2,      /* split-K reduce + QK-norm + RoPE + cache append */
-  STRICTB200_K_ATTN = 3,      /* split-KV attention + combine + quantise */
+  STRICTB200_K_ATTN = 3,      /* split-KV attention (the kernel that streams the cache) */
   STRICTB200_K_GEMM_O = 4,
   STRICTB200_K_ROWNORM = 5,   /* split-K reduce + residual + RMSNorm + quantise */
   STRICTB200_K_GEMM_GU = 6,
@@ -342,7 +342,8 @@ enum strictb200_kernel_class {
   STRICTB200_K_GEMM_DOWN = 8,
   STRICTB200_K_HEAD = 9,      /* LM head GEMM + argmax */
   STRICTB200_K_ALLREDUCE = 10,
-  STRICTB200_K_COUNT = 11
+  STRICTB200_K_ATTN_MERGE = 11, /* merge of the key chunks + quantise */
+  STRICTB200_K_COUNT = 12
 };
 /* Runs n_steps greedy decode steps as plain launches with a pair of CUDA events around every
  * call, and returns the summed device milliseconds and the number of calls per kernel class

@@ -840,6 +840,7 @@ int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16
                       o_part, ml_part, RopeFuseArgs{}, ctx->opt.attn_prefetch));
   }
   ctx->launches++;
+  sb_prof_split(ctx, STRICTB200_K_ATTN_MERGE);
   // The merge stays a kernel of its own: done inside the attention kernel by the last block of every (sequence, head) and
   // of every sequence to finish (fence, counters), it cost 3 us per layer more than this launch (55.0 against 46.8 + 5.1 us).
   if (nsplit <= 8 && Hq <= 32) {

@@ -43,6 +43,7 @@ struct TpCommDev {
   unsigned wait_limit;  // polls before a wait gives up (the context's wait_limit option, copied at launch)
 };
 struct SbProfiler;  // model.cu
+void sb_prof_split(strictb200_ctx*, int cls);  // model.cu: inside a profiled call, the following launches count for class `cls`
 
 // Switches of a context. Each is read once from the environment (STRICTB200_<NAME IN CAPITALS>)
 // when the context is created and can be changed afterwards with strictb200_set_option; no

@@ -275,11 +275,23 @@ struct SbProfiler {
   std::vector<ProfSpan> spans;
   std::vector<cudaEvent_t> pool;
   size_t used = 0;
+  ProfSpan* open = nullptr;  // the span of the call that is being made
   cudaEvent_t get() {
     if (used == pool.size()) { cudaEvent_t e; cudaEventCreate(&e); pool.push_back(e); }
     return pool[used++];
   }
 };
+// Inside a bracketed call: what is launched from here on belongs to class `cls` (a call that
+// launches kernels of two classes, e.g. the attention kernel and the merge of its key chunks).
+void sb_prof_split(strictb200_ctx* ctx, int cls) {
+  SbProfiler* p = ctx->prof;
+  if (!p || !p->open) return;
+  cudaEvent_t e = p->get();
+  cudaEventRecord(e, ctx->stream);
+  p->spans.push_back(ProfSpan{p->open->cls, p->open->a, e});
+  p->open->cls = cls;
+  p->open->a = e;
+}
 namespace {
 template <typename F>
 int prof(strictb200_ctx* ctx, int cls, F&& f) {
@@ -287,7 +299,9 @@ int prof(strictb200_ctx* ctx, int cls, F&& f) {
   if (!p) return f();
   ProfSpan sp{cls, p->get(), p->get()};
   cudaEventRecord(sp.a, ctx->stream);
+  p->open = &sp;
   int st = f();
+  p->open = nullptr;
   cudaEventRecord(sp.b, ctx->stream);
   p->spans.push_back(sp);
   return st;

@@ -118,7 +118,7 @@ class KvCache:
         N.check(N.lib().strictb200_decode_steps_device(self.model.h, self.h, None, n_steps))
 
     KERNEL_CLASSES = ("embed", "gemm_qkv", "rope_kvappend", "attn_decode", "gemm_o", "rownorm", "gemm_gate_up", "swiglu",
-                      "gemm_down", "head", "allreduce")
+                      "gemm_down", "head", "allreduce", "attn_merge")
 
     def profile_decode(self, n_steps):
         """Per-kernel-class device time of n plain-launch decode steps: {class: (total_ms, calls)}."""
