@@ -14,6 +14,8 @@
 #include <cstdlib>
 #include <mutex>
 
+#include <cmath>
+
 #include "common.cuh"
 
 namespace {
@@ -765,12 +767,15 @@ SB_TRACE_TU(attention)
 
 // Keys per block. All blocks of a launch take about the same time, so the grid runs in waves of
 // (blocks resident per SM) x (SM count): the chunk is the multiple of the tile size that
-// minimises waves x (tiles per chunk + per-block overhead) for a full cache, among the chunk
-// sizes that leave at most 8 chunks per sequence. The attn_blocks_per_sm option restores the
-// plain "that many blocks per SM" rule.
-static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
+// minimises waves x (tiles per chunk + per-block overhead) among the chunk sizes that leave at
+// most 8 chunks for a full cache. The waves are counted for sequences of `len_plan` keys (0: a
+// full cache): a cache that holds 2100 of 2432 keys in chunks of 512 runs four full chunks and a
+// stub per sequence, chunks of 448 run five even ones (14 % less attention time, measured). The
+// attn_blocks_per_sm option restores the plain "that many blocks per SM" rule.
+static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen, int len_plan = 0) {
   const int per_sm = ctx->opt.attn_blocks_per_sm;
   const int tiles = (maxlen + KT - 1) / KT;
+  const int tiles_plan = len_plan > 0 && len_plan < maxlen ? (len_plan + KT - 1) / KT : tiles;
   if (per_sm > 0) {
     int64_t c = (int64_t)maxlen * B * Hkv / ((int64_t)ctx->sm_count * per_sm);
     c = (c + KT - 1) / KT * KT;
@@ -802,8 +807,10 @@ static int decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
   // need cost more than that (21.9 against 17.0 us per layer for the pair, measured on eight GPUs).
   for (int c = (tiles + 7) / 8; c <= tiles; c++) {
     if (c < 4 && c < tiles) continue;  // at least 256 keys per block
-    const int64_t blocks = pairs * ((tiles + c - 1) / c), waves = (blocks + slots - 1) / slots;
-    const double cost = (double)waves * ((double)c + 1.5);
+    // (counting a stub as a whole block is deliberate: weighting blocks by their length made the rule pick three long
+    // chunks where five short ones measured 47 us against 66)
+    const int64_t blocks = pairs * ((tiles_plan + c - 1) / c), waves = (blocks + slots - 1) / slots;
+    const double cost = (double)waves * ((double)std::min(c, tiles_plan) + 1.5);
     if (cost < best_cost - 1e-9) { best_cost = cost; best = c; }
   }
   return best * KT;
@@ -812,15 +819,17 @@ int sb_attn_decode_splits(strictb200_ctx* ctx, int B, int Hkv, int maxlen) {
   int c = decode_chunk(ctx, B, Hkv, maxlen);
   return (maxlen + c - 1) / c;
 }
+int sb_attn_decode_chunk(strictb200_ctx* ctx, int B, int Hkv, int maxlen, int len_plan) { return decode_chunk(ctx, B, Hkv, maxlen, len_plan); }
 size_t sb_attn_decode_scratch(int B, int Hq, int Dh, int nsplit) { return (size_t)B * Hq * nsplit * (Dh + 2) * sizeof(float); }
 
 int k_attn_decode(strictb200_ctx* ctx, const bf16* q, const bf16* kc, const bf16* vc, const int32_t* lens, int len_add, int B, int Hq, int Hkv,
-                  int Dh, int maxlen, float scale, int nsplit, float* scratch, bf16* out, uint8_t* q_out, float* qscale_out, const RopeArgs* rope) {
+                  int Dh, int maxlen, float scale, int nsplit, float* scratch, bf16* out, uint8_t* q_out, float* qscale_out, const RopeArgs* rope,
+                  int chunk) {
   if (Dh != D) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: head_dim must be 128");
   if (Hq / Hkv > 16) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: at most 16 query heads per KV head");
   if (Hq * (D / 8) > CB_THREADS * CB_ITEMS) return sb_fail(STRICTB200_ERR_UNSUPPORTED, "attention: at most 64 query heads per rank");
-  int chunk = decode_chunk(ctx, B, Hkv, maxlen);
-  if ((maxlen + chunk - 1) / chunk != nsplit) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: split count does not match the cache size");
+  if (chunk <= 0) chunk = decode_chunk(ctx, B, Hkv, maxlen);  // else the caller's plan (a multiple of the tile; it has run decode_chunk, which sets the kernel up)
+  if (chunk % KT || (maxlen + chunk - 1) / chunk != nsplit) return sb_fail(STRICTB200_ERR_INVALID_ARG, "attention: split count does not match the cache size");
   size_t smem = 2 * DEC_STAGES * KT * 256;  // K and V rings; also covers the 34 KB merge area (the attribute is set by decode_chunk above)
   float* o_part = scratch;
   float* ml_part = scratch + (size_t)B * Hq * nsplit * D;

@@ -268,11 +268,12 @@ int k_attn_prefill(strictb200_ctx*, const bf16* q, const bf16* kc, const bf16* v
                    const int32_t* qstart, int B, int S, int64_t q_rows, int Hq, int Hkv, int D, int maxlen, float scale, bf16* out);
 size_t sb_attn_decode_scratch(int B, int Hq, int D, int nsplit);
 int sb_attn_decode_splits(strictb200_ctx*, int B, int Hkv, int maxlen);
+int sb_attn_decode_chunk(strictb200_ctx*, int B, int Hkv, int maxlen, int len_plan);  // keys per block for sequences of about len_plan keys (at most 8 chunks cover maxlen)
 // rope != null: the queries and the new token's key/value rows are computed inside the attention kernel from the qkv
 // projection's partial results (what k_rope_qknorm_kvappend would do in a kernel of its own); q is then unused
 int k_attn_decode(strictb200_ctx*, const bf16* q, const bf16* kc, const bf16* vc, const int32_t* lens, int len_add, int B, int Hq,
                   int Hkv, int D, int maxlen, float scale, int nsplit, float* scratch, bf16* out, uint8_t* q_out, float* qscale_out,
-                  const RopeArgs* rope = nullptr);
+                  const RopeArgs* rope = nullptr, int chunk = 0);
 int k_attn_f32(strictb200_ctx*, const float* qkv, float* kc, float* vc, const int32_t* seq, const int32_t* pos, const int32_t* lens,
                int64_t T, int H, int D, int maxlen, float scale, float* out);
 // sampling.cu

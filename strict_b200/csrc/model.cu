@@ -75,7 +75,9 @@ struct strictb200_kv {
   cudaGraphExec_t graph = nullptr;
   uint64_t graph_kernels = 0;
   bool warmed = false;
-  int nsplit = 1;
+  int nsplit = 1;        // key chunks per sequence of the decode attention, and
+  int chunk = 0;         // keys per chunk: planned for the lengths the cache holds now (plan_attention), 0 = not planned yet
+  int plan_until = 0;    // the plan is kept until a sequence grows beyond this length
   std::vector<void*> allocs;
 };
 
@@ -179,7 +181,8 @@ void carve_decode(strictb200_kv* kv, char* base, DecBuf* out, size_t* total) {
     b.qb = cv.take<bf16>(B * nq);
     b.att = cv.take<bf16>(B * nq);
     b.gu = cv.take<float>(B * 2 * m->I_l);
-    b.attn_ws = cv.take<float>(sb_attn_decode_scratch((int)B, m->Hq_l, (int)D, kv->nsplit) / sizeof(float));
+    // room for the most chunks any plan uses (8, or one per 64-key tile of a short cache)
+    b.attn_ws = cv.take<float>(sb_attn_decode_scratch((int)B, m->Hq_l, (int)D, std::min(8, (kv->maxlen + 63) / 64)) / sizeof(float));
     b.red = cv.take<float>(B * d);
   } else {
     int64_t w = std::max<int64_t>(3 * d, c.d_ff);
@@ -340,7 +343,7 @@ int qwen_decode_body(strictb200_model* m, strictb200_kv* kv, DecBuf& b) {
     if (!fuse_rope) PROF(STRICTB200_K_ROPE, k_rope_qknorm_kvappend(ctx, r, B));
     // split-KV attention over len+1 keys; the combine emits the quantised o_proj input
     PROF(STRICTB200_K_ATTN, k_attn_decode(ctx, b.qb, kv_k(kv, l), kv_v(kv, l), kv->d_lens, 1, (int)B, m->Hq_l, m->Hkv_l, (int)D, kv->maxlen,
-                                          scale, kv->nsplit, b.attn_ws, b.att, b.aq, b.sa, fuse_rope ? &r : nullptr));
+                                          scale, kv->nsplit, b.attn_ws, b.att, b.aq, b.sa, fuse_rope ? &r : nullptr, kv->chunk));
     // o_proj -> partials -> (all-reduce) -> residual + norm2 + quantise
     int s2 = plan_splits(m, B, d, nq);
     PROF(STRICTB200_K_GEMM_O, run_gemm(m, B, w.wo, b.aq, b.sa, nullptr, 0, b.part, s2, 1));
@@ -444,6 +447,21 @@ int decode_enqueue(strictb200_model* m, strictb200_kv* kv) {
   for (int b = 0; b < kv->B; b++)
     if (kv->h_lens[b] + 1 > kv->maxlen || kv->h_lens[b] + 1 > m->c.max_pos)
       return sb_fail(STRICTB200_ERR_INVALID_ARG, "decode: sequence " + std::to_string(b) + " has no room left in the cache");
+  if (m->c.arch == STRICTB200_QWEN3) {
+    // The key chunks of the decode attention are planned for the lengths the cache holds, not for a full cache, and planned
+    // again when the longest sequence has grown by 256 keys; a new plan needs a new recording of the step.
+    int longest = 0;
+    for (int b = 0; b < kv->B; b++) longest = std::max(longest, kv->h_lens[b] + 1);
+    if (!kv->chunk || longest > kv->plan_until) {
+      const int chunk = sb_attn_decode_chunk(ctx, kv->B, m->Hkv_l, kv->maxlen, std::min(kv->maxlen, longest + 128));
+      if (chunk != kv->chunk) {
+        kv->chunk = chunk;
+        kv->nsplit = (kv->maxlen + chunk - 1) / chunk;
+        if (kv->graph) { cudaGraphExecDestroy(kv->graph); kv->graph = nullptr; }
+      }
+      kv->plan_until = std::min(kv->maxlen, longest + 256);
+    }
+  }
   if (!m->use_graph || !kv->warmed) {
     // the first step runs as plain launches: it also performs the one-time kernel attribute set-up
     SB_TRY(decode_body(m, kv));
