@@ -992,6 +992,7 @@ int strictb200_kv_reset(strictb200_kv* kv) {
   SB_CUDA(cudaMemsetAsync(kv->d_lens, 0, (size_t)kv->B * 4, ctx->stream));
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
   std::fill(kv->h_lens.begin(), kv->h_lens.end(), 0);
+  kv->plan_until = 0;  // the next decode step plans the attention's key chunks for the new lengths
   return STRICTB200_OK;
 }
 
@@ -1022,6 +1023,7 @@ int strictb200_kv_fill_synthetic(strictb200_kv* kv, uint64_t seed, int len) {
   SB_CUDA(cudaMemcpyAsync(kv->d_lens, h.data(), (size_t)kv->B * 4, cudaMemcpyHostToDevice, ctx->stream));
   SB_CUDA(cudaStreamSynchronize(ctx->stream));
   kv->h_lens = h;
+  kv->plan_until = 0;
   return STRICTB200_OK;
 }
 
@@ -1093,6 +1095,7 @@ int strictb200_prefill(strictb200_model* m, strictb200_kv* kv, const int32_t* h_
     for (int j = 0; j < nb; j++) kv->h_lens[b0 + j] += h_lens[b0 + j];
     b0 += nb;
   }
+  kv->plan_until = 0;  // the lengths jumped: the next decode step plans the attention's key chunks for them
   SB_CUDA(cudaMemcpyAsync(kv->d_lens, kv->h_lens.data(), (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
   SB_CUDA(cudaMemcpyAsync(h_next, d_next, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
   SB_TRY(sb_sync(ctx, "prefill"));
